@@ -1,0 +1,141 @@
+"""Generate the golden fixtures in this directory from the reference package.
+
+Run once, on a machine where the reference checkout is available:
+
+    REFERENCE_SRC=/path/to/blackwell-moe/src python tests/golden/make_golden.py
+
+The reference is imported unmodified and executed on CPU; inputs and outputs
+are stored bit-exactly (bf16 as uint16, e4m3 as uint8) in ``*.npz`` files so
+that the tests never need the reference checkout.  Nothing at test or run
+time imports this script.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+sys.dont_write_bytecode = True
+REF = os.environ.get("REFERENCE_SRC", "/root/reference/src")
+sys.path.insert(0, REF)
+OUT = Path(__file__).resolve().parent
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    if t.dtype == torch.float8_e4m3fn:
+        return t.contiguous().view(torch.uint8).numpy()
+    return t.contiguous().numpy()
+
+
+def gen(seed: int):
+    return torch.Generator().manual_seed(seed)
+
+
+def router_cases():
+    from blackwell_moe.kernels.routing import top_k_router_ref
+    out = {}
+    # shapes of tests/test_router.py:7 and tests/test_correctness.py:13-14
+    for i, (T, D, E, K) in enumerate([(32, 256, 8, 2), (128, 512, 16, 4), (64, 256, 16, 4), (48, 384, 64, 6)]):
+        g = gen(100 + i)
+        x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+        w = (torch.randn(D, E, generator=g) * 0.05).to(torch.bfloat16)
+        wt, idx = top_k_router_ref(x, w, K)
+        out.update({f"x{i}": bits(x), f"w{i}": bits(w), f"weights{i}": wt.numpy(), f"indices{i}": idx.numpy(),
+                    f"k{i}": np.int32(K)})
+    out["n"] = np.int32(4)
+    np.savez_compressed(OUT / "router.npz", **out)
+
+
+def quant_cases():
+    from blackwell_moe.kernels.fp8_quant import quant_fp8_e4m3, dequant_fp8_e4m3
+    from blackwell_moe.kernels.fp8_moe import to_fp8_e4m3
+    from blackwell_moe.kernels.permute import permute_tokens
+    g = gen(200)
+    x = (torch.randn(64, 256, generator=g) * 0.2).to(torch.bfloat16)
+    q, s = quant_fp8_e4m3(x)
+    q2, s2 = to_fp8_e4m3(x)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and float(s) == float(s2)
+    dq = dequant_fp8_e4m3(q, s)
+    tiny = torch.full((4, 16), 1e-6).to(torch.bfloat16)          # exercises the 1e-4 amax clamp
+    qt, st = quant_fp8_e4m3(tiny)
+    ids = torch.randint(0, 16, (96 * 4,), generator=g).to(torch.int32)
+    xp = torch.randn(96, 32, generator=g).to(torch.bfloat16)
+    x_perm, offsets, inverse_idx = permute_tokens(xp, ids, 16)
+    np.savez_compressed(OUT / "quant_permute.npz", x=bits(x), q=bits(q), scale=s.numpy(), dq=bits(dq),
+                        tiny=bits(tiny), qt=bits(qt), st=st.numpy(),
+                        ids=ids.numpy(), xp=bits(xp), x_perm=bits(x_perm), offsets=offsets.numpy(),
+                        inverse_idx=inverse_idx.numpy())
+
+
+def forward_cases():
+    from blackwell_moe.kernels.reference import moe_forward_bf16
+    from blackwell_moe.kernels.fp8_quant import quant_fp8_e4m3
+    from blackwell_moe.kernels.fp8_moe_torch import fp8_moe_forward_torch
+    # (T, D, E, K, H): scripts/verify_v3.py:12 shape, and a top-6 / non-power-of-two-H shape
+    for name, (T, D, E, K, H), xs in [("fwd_a", (64, 256, 8, 2, 128), 1.0), ("fwd_b", (40, 128, 12, 6, 176), 0.1)]:
+        g = gen(300 + len(name) + T)
+        x = (torch.randn(T, D, generator=g) * xs).to(torch.bfloat16)
+        wg = (torch.randn(D, E, generator=g) * 0.02).to(torch.bfloat16)
+        eg = (torch.randn(E, D, H, generator=g) * 0.02).to(torch.bfloat16)
+        eu = (torch.randn(E, D, H, generator=g) * 0.02).to(torch.bfloat16)
+        ed = (torch.randn(E, H, D, generator=g) * 0.02).to(torch.bfloat16)
+        y_bf16 = moe_forward_bf16(x, wg, eg, eu, ed, K)
+        qs = [[quant_fp8_e4m3(w[i]) for i in range(E)] for w in (eg, eu, ed)]
+        eg8, eu8, ed8 = (torch.stack([q for q, _ in row]) for row in qs)
+        sg, su, sd = (torch.stack([s for _, s in row]) for row in qs)
+        y_fp8 = fp8_moe_forward_torch(x, wg, eg8, eu8, ed8, sg, su, sd, K)
+        np.savez_compressed(OUT / f"{name}.npz", x=bits(x), wg=bits(wg), eg=bits(eg), eu=bits(eu), ed=bits(ed),
+                            eg8=bits(eg8), eu8=bits(eu8), ed8=bits(ed8), sg=sg.numpy(), su=su.numpy(),
+                            sd=sd.numpy(), y_bf16=bits(y_bf16), y_fp8=bits(y_fp8), k=np.int32(K))
+
+
+def block_and_shared_cases():
+    from blackwell_moe.runtime.qwen_patch import _dequant_block_fp8
+    from blackwell_moe.runtime.shared_expert_fp8 import FP8SharedExpert
+    g = gen(400)
+    w = (torch.randn(256, 384, generator=g) * 0.5).clamp(-448, 448).to(torch.float8_e4m3fn)
+    s = (torch.rand(2, 3, generator=g) * 1e-3 + 1e-4).to(torch.float32)
+    deq = _dequant_block_fp8(w, s)
+    w2 = (torch.randn(200, 130, generator=g) * 0.5).to(torch.float8_e4m3fn)      # ragged edges
+    s2 = (torch.rand(2, 2, generator=g) * 1e-3 + 1e-4).to(torch.float32)
+    deq2 = _dequant_block_fp8(w2, s2)
+
+    D, Hs, T = 128, 192, 24
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = torch.nn.Linear(D, Hs, bias=False)
+            self.up_proj = torch.nn.Linear(D, Hs, bias=False)
+            self.down_proj = torch.nn.Linear(Hs, D, bias=False)
+
+    torch.manual_seed(401)
+    mlp = MLP()
+    with torch.no_grad():
+        for p in mlp.parameters():
+            p.copy_(torch.randn(p.shape, generator=g) * 0.05)
+    sh = FP8SharedExpert(mlp)
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    y = sh(x)
+    np.savez_compressed(
+        OUT / "block_shared.npz", w=bits(w), s=s.numpy(), deq=bits(deq), w2=bits(w2), s2=s2.numpy(), deq2=bits(deq2),
+        sx=bits(x), sy=bits(y),
+        s_wg=bits(sh.w_gate.contiguous()), s_wu=bits(sh.w_up.contiguous()), s_wd=bits(sh.w_down.contiguous()),
+        s_sg=sh.s_gate.numpy(), s_su=sh.s_up.numpy(), s_sd=sh.s_down.numpy())
+
+
+if __name__ == "__main__":
+    import blackwell_moe
+    print("reference version", blackwell_moe.__version__, "torch", torch.__version__)
+    router_cases()
+    quant_cases()
+    forward_cases()
+    block_and_shared_cases()
+    for f in sorted(OUT.glob("*.npz")):
+        print(f.name, f.stat().st_size)
