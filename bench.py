@@ -1,0 +1,333 @@
+"""MoE-block forward benchmark (tokens/s) on 1..8 B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--tokens T]
+    python bench.py --impl reference ...        # the bf16 CPU path on the host cores
+
+One "step" is one forward of the MoE block over one batch of T synthetic tokens
+per GPU.  Default workload: the Mixtral-8x7B-shape block (hidden 4096,
+intermediate 14336, 8 experts, top-2, per-tensor E4M3 weights) at T=16384
+prefill tokens.  With N > 1 the experts are sharded over the ranks (expert
+parallel, all-to-all over NCCL) and every rank brings its own T tokens, so the
+job is weak-scaled.  Rank 0 prints ONE JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (D, H, E, K, default T)
+    "mixtral-8x7b": (4096, 14336, 8, 2, 16384),
+    "deepseek-v2-lite": (2048, 1408, 64, 6, 4096),
+    "toy": (1024, 2048, 16, 2, 256),
+}
+KERNELS_PER_FORWARD = 11  # router, 3 plan, 2 segment-scale, gather-quant, gate/up GEMM, requant, down GEMM, combine
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixtral-8x7b", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's prefill size)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- inputs
+def synth_weights(D, H, E, dev, seed, experts=None, keep_bf16=False):
+    """Random-init weights of the workload's architecture: bf16 ~N(0, 0.02^2), quantised per
+    expert matrix to E4M3 (scale 448/amax) exactly as the reference's bench does
+    (src/blackwell_moe/bench/cli.py:39-70).  Generated expert by expert on the device."""
+    import blackwell_moe_b200 as bw
+    experts = range(E) if experts is None else experts
+    g = torch.Generator(device=dev)
+    out = {"q_gate": [], "q_up": [], "q_down": [], "s_gate": [], "s_up": [], "s_down": []}
+    bf = {"gate": [], "up": [], "down": []}
+    for e in experts:
+        for name, shape in (("gate", (D, H)), ("up", (D, H)), ("down", (H, D))):
+            g.manual_seed(seed * 100003 + e * 7 + {"gate": 0, "up": 1, "down": 2}[name])
+            w = (torch.randn(shape, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            q, s = bw.quant_fp8_e4m3(w)
+            out["q_" + name].append(q), out["s_" + name].append(s)
+            if keep_bf16:
+                bf[name].append(w.cpu())
+    res = {k: torch.stack(v).contiguous() for k, v in out.items()}
+    for k in ("s_gate", "s_up", "s_down"):
+        res[k] = res[k].to(torch.float32)
+    if keep_bf16:
+        res.update({"bf_" + k: torch.stack(v) for k, v in bf.items()})
+    return res
+
+
+def synth_activations(T, D, E, dev, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn((T, D), generator=g, device=dev).to(torch.bfloat16)
+    w_gate = (torch.randn((D, E), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    return x, w_gate
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_bf16_tokens_per_s(D, H, E, K, sample_tokens, steps, warmup, seed=0):
+    """The bf16 MoE forward restated from the reference (src/blackwell_moe/kernels/reference.py:9-39)
+    on the host cores, on `sample_tokens` tokens of the workload."""
+    import oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(sample_tokens, D, generator=g).to(torch.bfloat16)
+    w_gate = (torch.randn(D, E, generator=g) * 0.02).to(torch.bfloat16)
+    ws = [(torch.randn(E, a, b, generator=g) * 0.02).to(torch.bfloat16) for a, b in ((D, H), (D, H), (H, D))]
+    for _ in range(warmup):
+        oracle.moe_forward_bf16(x, w_gate, *ws, top_k=K)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.moe_forward_bf16(x, w_gate, *ws, top_k=K)
+    dt = (time.perf_counter() - t0) / steps
+    return sample_tokens / dt, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    D, H, E, K, T_default = WORKLOADS[args.workload]
+    T = args.tokens or T_default
+    sample = min(T, 256)
+    tps, dt = cpu_bf16_tokens_per_s(D, H, E, K, sample, max(1, args.steps), max(1, min(args.warmup, 2)))
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "MoE-block tokens/s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload} D={D} H={H} E={E} top_k={K} T={T}"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {T} tokens per step, bf16 path restated from reference.py:9-39"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def time_region(fn, steps, stream):
+    """CUDA-event time of `steps` calls on the current stream, in seconds."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop) / 1e3
+
+
+def run_ours(args):
+    import blackwell_moe_b200 as bw
+    from blackwell_moe_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    D, H, E, K, T_default = WORKLOADS[args.workload]
+    T = args.tokens or T_default
+    stream = torch.cuda.current_stream(dev)
+    x, w_gate = synth_activations(T, D, E, dev, seed=1234 + rank)
+
+    if world == 1:
+        W = synth_weights(D, H, E, dev, seed=7)
+        wargs = (w_gate, W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"])
+        step = lambda: bw.fp8_moe_forward(x, *wargs, top_k=K)            # noqa: E731
+    else:
+        from blackwell_moe_b200.ep import ExpertParallelMoE
+        assert E % world == 0, f"E={E} experts do not shard over {world} ranks"
+        mine = range(rank * (E // world), (rank + 1) * (E // world))
+        _, w_gate = synth_activations(1, D, E, dev, seed=1234)           # router replicated
+        W = synth_weights(D, H, E, dev, seed=7, experts=mine)
+        ep = ExpertParallelMoE(w_gate, W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"],
+                               num_experts=E, top_k=K, group=dist.group.WORLD)
+        step = lambda: ep.forward(x)                                     # noqa: E731
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    with ClockSampler(local) as clocks:
+        secs = time_region(step, args.steps, stream)
+        barrier()
+    if dist is not None:
+        t = torch.tensor([secs], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t)
+    tokens_total = T * world * args.steps
+    value = tokens_total / secs
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the region ----
+    x_host = x.cpu().pin_memory()
+    if world == 1:
+        e2e_step = lambda: bw.fp8_moe_forward(x_host, *wargs, top_k=K)   # noqa: E731
+    else:
+        e2e_step = lambda: ep.forward(x_host)                            # noqa: E731
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_secs = time_region(e2e_step, args.steps, stream)
+    barrier()
+    if dist is not None:
+        t = torch.tensor([e2e_secs], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_secs = float(t)
+    e2e_value = tokens_total / e2e_secs
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- dominant kernel alone: grouped gate+up GEMM, timed with events on its stream ----
+    roofline = None
+    if world == 1:
+        lib = bw.lib()
+        step()
+        M = T * K
+        ws = bw.moe._workspaces[(dev.index, stream.cuda_stream)]
+
+        def view(sel):
+            p, n = C.c_void_p(), C.c_size_t()
+            _lib.check(lib.bwmoe_workspace_view(ws.data_ptr(), T, D, H, E, K, sel, C.byref(p), C.byref(n)))
+            return p.value
+        amax_h = torch.zeros(E, device=dev, dtype=torch.float32)
+        scratch = torch.empty(max(256, lib.bwmoe_gemm_scratch_bytes(M, E)), device=dev, dtype=torch.uint8)
+
+        def gateup():
+            _lib.check(lib.bwmoe_gateup_swiglu(view(8), view(1), view(6), W["q_gate"].data_ptr(), W["q_up"].data_ptr(),
+                                               W["s_gate"].data_ptr(), W["s_up"].data_ptr(), M, D, H, E, view(10),
+                                               amax_h.data_ptr(), view(0), scratch.data_ptr(), stream.cuda_stream))
+        for _ in range(3):
+            gateup()
+        torch.cuda.synchronize(dev)
+        k_secs = time_region(gateup, args.steps, stream) / args.steps
+        flops = 4.0 * M * D * H
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        bf16_sus = peaks.get("bf16_tflops_sustained")
+        peak = 2.0 * bf16_sus if bf16_sus else 2.0 * 1400.0
+        achieved = flops / k_secs / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": None, "kernel": "grouped_gemm_kernel<GATE_UP>",
+                    "kernel_ms": k_secs * 1e3, "flops_per_launch": flops,
+                    "peak_basis": ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it has no FP8 entry)"
+                                   if bf16_sus else "2 x 1400 TFLOP/s fallback (sustained bf16 of the profiling recipe)")}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample = min(T, 256)
+        tps, dt = cpu_bf16_tokens_per_s(D, H, E, K, sample, steps=3, warmup=1)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"{sample} of {T} tokens, 3 timed passes of the bf16 path restated from reference.py:9-39"}
+
+    line = {
+        "metric": "MoE-block tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": f"{args.workload} D={D} H={H} E={E} top_k={K} T={T} per GPU",
+                   "parallelism": "single GPU" if world == 1 else f"ep{world} (experts sharded, tokens per rank fixed)",
+                   "l2": "inputs larger than L2 (weights %.0f MB per step)" % (3.0 * E * D * H / world / 1e6)},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 2 * world,
+                "d2h_bytes_per_step": T * D * 2 * world, "ms_per_step": e2e_secs / args.steps * 1e3},
+        "gpu_launches": KERNELS_PER_FORWARD * args.steps,
+        "clocks": clocks.summary(),
+    }
+    if roofline is not None:
+        line["roofline"] = roofline
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

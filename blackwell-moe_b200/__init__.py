@@ -1,0 +1,32 @@
+"""B200-native FP8 MoE-block forward behind the reference's Python API.
+
+``fp8_moe_forward`` / ``top_k_router`` keep the signatures of
+``blackwell_moe.kernels.fp8_moe.fp8_moe_forward`` and
+``blackwell_moe.kernels.routing.top_k_router``; the work is done by
+hand-written sm_100a CUDA kernels in ``libbwmoe.so`` reached through a C ABI
+(``include/bwmoe.h``).  There is no CPU or PyTorch fallback: if the library is
+missing or no B200 is present the calls raise.
+"""
+
+from .quant import FP8_MAX_E4M3, dequant_fp8_e4m3, quant_fp8_e4m3, quantize_expert_weights
+from .moe import (
+    fp8_moe_forward,
+    fp8_moe_forward_routed,
+    moe_stage_views,
+    top_k_router,
+)
+from ._lib import lib, library_path, BwmoeError
+
+# The reference exports the same forward under several version names
+# (src/blackwell_moe/__init__.py:14-15); all of them map to the one CUDA path.
+fp8_moe_forward_v3 = fp8_moe_forward
+fp8_moe_forward_v4 = fp8_moe_forward
+fp8_moe_forward_small_e = fp8_moe_forward
+
+__version__ = "0.1.0"
+
+__all__ = [
+    "FP8_MAX_E4M3", "BwmoeError", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_routed",
+    "fp8_moe_forward_small_e", "fp8_moe_forward_v3", "fp8_moe_forward_v4", "lib", "library_path",
+    "moe_stage_views", "quant_fp8_e4m3", "quantize_expert_weights", "top_k_router",
+]

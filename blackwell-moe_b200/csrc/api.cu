@@ -1,0 +1,325 @@
+// extern "C" surface of libbwmoe.so: argument checks, workspace layout, and the
+// composition of the stage kernels into the whole-block forward.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace bwmoe {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int sm_count() {
+  // per-device cache; the library may be used from one process per GPU or several devices
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+namespace {
+
+constexpr size_t kAlign = 1024;
+inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+// Workspace layout.  The first block (status .. amax_h) is cleared by one memset per call.
+struct Layout {
+  size_t status, amax_x, amax_h, zero_end;
+  size_t offsets, scale_x, scale_h, topk_idx, topk_w, row_amax, pos, row_slot, row_expert;
+  size_t plan_scratch, gemm_scratch, xq, h, hq, y, total;
+};
+
+bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
+  if (T <= 0 || D <= 0 || H <= 0 || E <= 0 || K <= 0 || E > 256 || K > E || K > 32) return false;
+  if ((long long)T * K >= (1ll << 31)) return false;
+  const size_t M = (size_t)T * K;
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = o;
+    o = align_up(o + bytes);
+    return at;
+  };
+  L->status = take(16);
+  L->amax_x = take(sizeof(float) * E);
+  L->amax_h = take(sizeof(float) * E);
+  L->zero_end = o;
+  L->offsets = take(sizeof(int32_t) * (E + 1));
+  L->scale_x = take(sizeof(float) * E);
+  L->scale_h = take(sizeof(float) * E);
+  L->topk_idx = take(sizeof(int32_t) * M);
+  L->topk_w = take(sizeof(float) * M);
+  L->row_amax = take(sizeof(float) * T);
+  L->pos = take(sizeof(int32_t) * M);
+  L->row_slot = take(sizeof(int32_t) * M);
+  L->row_expert = take(sizeof(int32_t) * M);
+  L->plan_scratch = take(plan_scratch_bytes(T, E, K));
+  L->gemm_scratch = take(gemm_scratch_bytes((int)M, E));
+  L->xq = take(M * D);
+  L->h = take(M * H * 2);
+  L->hq = take(M * H);
+  L->y = take(M * D * 2);
+  L->total = o;
+  return true;
+}
+
+template <class T>
+T* at(void* ws, size_t off) {
+  return reinterpret_cast<T*>(static_cast<uint8_t*>(ws) + off);
+}
+
+int check_forward_args(const char* who, const void* x, const void* wg, const void* wu, const void* wd,
+                       const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                       void* out, void* ws, size_t ws_bytes, Layout* L, size_t extra) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && H > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "%s: T=%d D=%d H=%d E=%d K=%d",
+                who, T, D, H, E, K);
+  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
+  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "%s: E=%d > 256 experts", who, E);
+  BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "%s: top_k=%d must be <= min(E,32)", who, K);
+  BWMOE_REQUIRE(x && wg && wu && wd && sg && su && sd && out, BWMOE_ERR_NULL, "%s: null pointer", who);
+  BWMOE_REQUIRE(make_layout(T, D, H, E, K, L), BWMOE_ERR_BAD_SHAPE, "%s: shape not representable", who);
+  BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L->total + extra, BWMOE_ERR_WORKSPACE,
+                "%s: workspace of %zu bytes given, %zu needed", who, ws_bytes, L->total + extra);
+  BWMOE_REQUIRE(aligned16(x) && aligned16(out) && aligned16(wg) && aligned16(wu) && aligned16(wd) &&
+                    (reinterpret_cast<uintptr_t>(ws) % 256 == 0),
+                BWMOE_ERR_BAD_ALIGN, "%s: tensors must be 16-byte and the workspace 256-byte aligned", who);
+  return BWMOE_OK;
+}
+
+// permute plan -> quantise -> gate/up -> requant -> down -> combine, given routing in the workspace
+int run_pipeline(const void* x, const float* weights, const int32_t* indices, const float* row_amax,
+                 const void* wg, const void* wu, const void* wd, const float* sg, const float* su,
+                 const float* sd, int T, int D, int H, int E, int K, void* out, void* ws, const Layout& L,
+                 cudaStream_t st) {
+  const int M = T * K;
+  int32_t* status = at<int32_t>(ws, L.status);
+  int32_t* offsets = at<int32_t>(ws, L.offsets);
+  int32_t* pos = at<int32_t>(ws, L.pos);
+  int32_t* row_slot = at<int32_t>(ws, L.row_slot);
+  int32_t* row_expert = at<int32_t>(ws, L.row_expert);
+  float* amax_x = at<float>(ws, L.amax_x);
+  float* amax_h = at<float>(ws, L.amax_h);
+  float* scale_x = at<float>(ws, L.scale_x);
+  float* scale_h = at<float>(ws, L.scale_h);
+  int rc;
+  if ((rc = launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, amax_x, status,
+                        at<void>(ws, L.plan_scratch), st)))
+    return rc;
+  if ((rc = launch_segment_scales(amax_x, offsets, E, scale_x, st))) return rc;
+  if ((rc = launch_gather_quant(x, row_slot, row_expert, scale_x, M, D, K, at<void>(ws, L.xq), st))) return rc;
+  if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
+                          amax_h, status, at<void>(ws, L.gemm_scratch), st)))
+    return rc;
+  if ((rc = launch_segment_scales(amax_h, offsets, E, scale_h, st))) return rc;
+  if ((rc = launch_requant(at<void>(ws, L.h), row_expert, scale_h, M, H, at<void>(ws, L.hq), st))) return rc;
+  if ((rc = launch_down(at<void>(ws, L.hq), offsets, scale_h, wd, sd, M, D, H, E, at<void>(ws, L.y), status,
+                        at<void>(ws, L.gemm_scratch), st)))
+    return rc;
+  return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st);
+}
+
+// max|x| per row, for callers that bring their own routing
+__global__ void row_amax_kernel(const __nv_bfloat16* __restrict__ x, int T, int D, float* __restrict__ row_amax) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  float m = 0.f;
+  for (int d = lane; d < D; d += 32) m = fmaxf(m, fabsf(__bfloat162float(x[(size_t)t * D + d])));
+  for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if (lane == 0) row_amax[t] = m;
+}
+
+}  // namespace
+}  // namespace bwmoe
+
+using namespace bwmoe;
+
+extern "C" {
+
+int bwmoe_version(void) { return BWMOE_VERSION; }
+
+int bwmoe_last_error(char* buf, size_t len) {
+  const size_t n = strlen(g_error);
+  if (buf != nullptr && len > 0) {
+    const size_t c = std::min(n, len - 1);
+    memcpy(buf, g_error, c);
+    buf[c] = '\0';
+  }
+  return (int)n;
+}
+
+size_t bwmoe_workspace_bytes(int T, int D, int H, int E, int K) {
+  Layout L;
+  if (D % 16 != 0 || H % 16 != 0 || !make_layout(T, D, H, E, K, &L)) return 0;
+  return L.total;
+}
+
+size_t bwmoe_workspace_bytes_host(int T, int D, int H, int E, int K) {
+  const size_t base = bwmoe_workspace_bytes(T, D, H, E, K);
+  return base == 0 ? 0 : base + 2 * align_up((size_t)T * D * 2);
+}
+
+int bwmoe_workspace_view(void* ws, int T, int D, int H, int E, int K, int which, void** ptr, size_t* bytes) {
+  Layout L;
+  BWMOE_REQUIRE(ws && ptr && bytes, BWMOE_ERR_NULL, "workspace_view: null pointer");
+  BWMOE_REQUIRE(make_layout(T, D, H, E, K, &L), BWMOE_ERR_BAD_SHAPE, "workspace_view: bad shape");
+  const size_t M = (size_t)T * K;
+  size_t off = 0, n = 0;
+  switch (which) {
+    case BWMOE_WS_STATUS: off = L.status, n = 16; break;
+    case BWMOE_WS_OFFSETS: off = L.offsets, n = 4 * (size_t)(E + 1); break;
+    case BWMOE_WS_TOPK_IDX: off = L.topk_idx, n = 4 * M; break;
+    case BWMOE_WS_TOPK_W: off = L.topk_w, n = 4 * M; break;
+    case BWMOE_WS_POS: off = L.pos, n = 4 * M; break;
+    case BWMOE_WS_ROW_SLOT: off = L.row_slot, n = 4 * M; break;
+    case BWMOE_WS_SCALE_X: off = L.scale_x, n = 4 * (size_t)E; break;
+    case BWMOE_WS_SCALE_H: off = L.scale_h, n = 4 * (size_t)E; break;
+    case BWMOE_WS_XQ: off = L.xq, n = M * D; break;
+    case BWMOE_WS_HQ: off = L.hq, n = M * H; break;
+    case BWMOE_WS_H: off = L.h, n = 2 * M * H; break;
+    case BWMOE_WS_Y: off = L.y, n = 2 * M * D; break;
+    case BWMOE_WS_ROW_EXPERT: off = L.row_expert, n = 4 * M; break;
+    default: return set_error(BWMOE_ERR_UNSUPPORTED, "workspace_view: unknown selector %d", which);
+  }
+  *ptr = static_cast<uint8_t*>(ws) + off;
+  *bytes = n;
+  return BWMOE_OK;
+}
+
+int bwmoe_read_status(void* ws, void* stream, int32_t* status) {
+  BWMOE_REQUIRE(ws && status, BWMOE_ERR_NULL, "read_status: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemcpyAsync(status, ws, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  BWMOE_CUDA_OK(cudaStreamSynchronize(st));
+  return BWMOE_OK;
+}
+
+int bwmoe_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights, int32_t* indices,
+                 float* row_amax, void* stream) {
+  return launch_router(x, wg, T, D, E, K, weights, indices, row_amax, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                      const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                      void* out, void* ws, size_t ws_bytes, void* stream) {
+  Layout L;
+  if (int rc = check_forward_args("moe_forward", x, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, ws_bytes, &L, 0))
+    return rc;
+  BWMOE_REQUIRE(w_gate != nullptr, BWMOE_ERR_NULL, "moe_forward: w_gate is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* weights = at<float>(ws, L.topk_w);
+  int32_t* indices = at<int32_t>(ws, L.topk_idx);
+  float* row_amax = at<float>(ws, L.row_amax);
+  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, row_amax, st)) return rc;
+  return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
+}
+
+int bwmoe_moe_forward_routed(const void* x, const float* weights, const int32_t* indices, const void* wg,
+                             const void* wu, const void* wd, const float* sg, const float* su, const float* sd,
+                             int T, int D, int H, int E, int K, void* out, void* ws, size_t ws_bytes,
+                             void* stream) {
+  Layout L;
+  if (int rc = check_forward_args("moe_forward_routed", x, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws,
+                                  ws_bytes, &L, 0))
+    return rc;
+  BWMOE_REQUIRE(weights && indices, BWMOE_ERR_NULL, "moe_forward_routed: routing is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* row_amax = at<float>(ws, L.row_amax);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  // keep a copy of the routing in the workspace so that the views stay meaningful
+  BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_idx), indices, sizeof(int32_t) * (size_t)T * K,
+                                cudaMemcpyDeviceToDevice, st));
+  BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_w), weights, sizeof(float) * (size_t)T * K,
+                                cudaMemcpyDeviceToDevice, st));
+  return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
+}
+
+int bwmoe_moe_forward_host(const void* h_x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                           const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                           void* h_out, void* ws, size_t ws_bytes, void* stream) {
+  Layout L;
+  const size_t act = align_up((size_t)T * D * 2);
+  // the device copies of x and out live behind the regular workspace
+  BWMOE_REQUIRE(h_x && h_out, BWMOE_ERR_NULL, "moe_forward_host: null host pointer");
+  BWMOE_REQUIRE(make_layout(T, D, H, E, K, &L), BWMOE_ERR_BAD_SHAPE, "moe_forward_host: bad shape");
+  BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L.total + 2 * act, BWMOE_ERR_WORKSPACE,
+                "moe_forward_host: workspace of %zu bytes given, %zu needed", ws_bytes, L.total + 2 * act);
+  void* d_x = static_cast<uint8_t*>(ws) + L.total;
+  void* d_out = static_cast<uint8_t*>(ws) + L.total + act;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemcpyAsync(d_x, h_x, (size_t)T * D * 2, cudaMemcpyHostToDevice, st));
+  if (int rc = bwmoe_moe_forward(d_x, w_gate, wg, wu, wd, sg, su, sd, T, D, H, E, K, d_out, ws, L.total, stream))
+    return rc;
+  BWMOE_CUDA_OK(cudaMemcpyAsync(h_out, d_out, (size_t)T * D * 2, cudaMemcpyDeviceToHost, st));
+  BWMOE_CUDA_OK(cudaStreamSynchronize(st));
+  return BWMOE_OK;
+}
+
+size_t bwmoe_plan_scratch_bytes(int T, int E, int K) {
+  if (T <= 0 || E <= 0 || K <= 0) return 0;
+  return plan_scratch_bytes(T, E, K);
+}
+
+int bwmoe_permute_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
+                       int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
+                       void* scratch, void* stream) {
+  return launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, seg_amax, status, scratch,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales, void* stream) {
+  return launch_segment_scales(seg_amax, offsets, E, scales, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert, const float* scales,
+                       int M, int D, int K, void* xq, void* stream) {
+  return launch_gather_quant(x, row_slot, row_expert, scales, M, D, K, xq, static_cast<cudaStream_t>(stream));
+}
+
+size_t bwmoe_gemm_scratch_bytes(int M, int E) {
+  if (M <= 0 || E <= 0) return 0;
+  return gemm_scratch_bytes(M, E);
+}
+
+int bwmoe_gateup_swiglu(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
+                        const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
+                        int32_t* status, void* scratch, void* stream) {
+  return launch_gateup(xq, offsets, sx, wg, wu, sg, su, M, D, H, E, h, amax_h, status, scratch,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H, void* hq,
+                  void* stream) {
+  return launch_requant(h, row_expert, scales_h, M, H, hq, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd, int M,
+               int D, int H, int E, void* y, int32_t* status, void* scratch, void* stream) {
+  return launch_down(hq, offsets, sh, wd, sd, M, D, H, E, y, status, scratch, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K, void* out,
+                  void* stream) {
+  return launch_combine(y, pos, weights, T, D, K, out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,80 @@
+// Shared helpers for the libbwmoe kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bwmoe.h"
+
+namespace bwmoe {
+
+// ---- host-side error plumbing --------------------------------------------
+int set_error(int code, const char* fmt, ...);
+#define BWMOE_CUDA_OK(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t e__ = (expr);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return ::bwmoe::set_error(BWMOE_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+#define BWMOE_REQUIRE(cond, code, ...) \
+  do {                                 \
+    if (!(cond)) return ::bwmoe::set_error(code, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+int sm_count();
+
+// ---- arithmetic shared by several kernels ---------------------------------
+constexpr float kFp8Max = 448.0f;
+// The reference clamps amax in the tensor's own dtype (bf16), so the floor is
+// bf16(1e-4) = 0x38D2, not the fp32 literal.
+constexpr float kAmaxFloor = 0.00010013580322265625f;
+
+__device__ __forceinline__ float scale_from_amax(float amax) {
+  return __fdiv_rn(kFp8Max, fmaxf(amax, kAmaxFloor));
+}
+
+// e4m3(clamp(v, +-448)), round-to-nearest-even, as torch's cast after the clamp.
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  v = fminf(fmaxf(v, -kFp8Max), kFp8Max);
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ uint16_t to_e4m3x2(float lo, float hi) {
+  lo = fminf(fmaxf(lo, -kFp8Max), kFp8Max);
+  hi = fminf(fmaxf(hi, -kFp8Max), kFp8Max);
+  return static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// non-negative floats order like their bit patterns: atomicMax on the uint view.
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+  atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+// ---- launchers implemented in the individual .cu files ---------------------
+int launch_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
+                  int32_t* indices, float* row_amax, cudaStream_t st);
+size_t plan_scratch_bytes(int T, int E, int K);
+int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
+                int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
+                void* scratch, cudaStream_t st);
+int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,
+                          cudaStream_t st);
+int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert,
+                        const float* scales, int M, int D, int K, void* xq, cudaStream_t st);
+int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
+                   void* hq, cudaStream_t st);
+int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
+                   void* out, cudaStream_t st);
+size_t gemm_scratch_bytes(int M, int E);
+int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
+                  const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
+                  int32_t* status, void* scratch, cudaStream_t st);
+int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
+                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st);
+
+}  // namespace bwmoe

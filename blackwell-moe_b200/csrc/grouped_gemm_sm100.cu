@@ -1,0 +1,495 @@
+// Grouped FP8 (E4M3) GEMMs of the MoE block on the 5th-generation tensor cores.
+//
+// One persistent, warp-specialised kernel template serves both projections:
+//   GATE_UP : [rows of expert e] x (Wg[e] | Wu[e])  ->  h = silu(gate) * up   (bf16) + segment amax
+//   DOWN    : [rows of expert e] x Wd[e]            ->  y                     (bf16)
+// Takes over the roles of the reference's Triton kernels _fused_gate_up_kernel
+// (src/blackwell_moe/kernels/grouped_fp8_gateup.py:42-101) and _grouped_fp8_gemm_kernel
+// (src/blackwell_moe/kernels/grouped_fp8.py:36-89), and of F.silu(gate)*up
+// (src/blackwell_moe/kernels/fp8_moe_v3.py:60).
+//
+// Structure per CTA (192 threads, one CTA per SM):
+//   warp 0      : TMA producer - activations (K-major) and weights (N-major, as the
+//                 caller's [E,K,N] layout dictates) into a 4-stage 128B-swizzled ring
+//   warp 1      : tcgen05.mma issuer, kind::f8f6f4, M=128 N=256 K=32, fp32 accumulators
+//                 in tensor memory, two 256-column buffers so that the epilogue of tile i
+//                 overlaps the main loop of tile i+1
+//   warps 2..5  : epilogue - tcgen05.ld, dequantise, SwiGLU / bf16 rounding, global store
+// A tile is 128 permuted rows of ONE expert x 256 accumulator columns (GATE_UP: 128 gate +
+// 128 up columns -> 128 h columns; DOWN: 256 output columns).  Tiles are ordered expert-major,
+// then column block, then row block, so that concurrently running CTAs share weight tiles
+// and an expert's activations stay in L2 while its weights stream through once.
+//
+// Every barrier wait is bounded: when a wait runs out the kernel sets
+// BWMOE_STATUS_WAIT_TIMEOUT in the status word, tells the other warps to stop, waits for
+// copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace bwmoe {
+namespace {
+
+constexpr int BM = 128;            // rows per tile
+constexpr int BK = 128;            // K elements (= bytes) per pipeline stage
+constexpr int BN_HALF = 128;       // accumulator columns per weight box
+constexpr int BN = 2 * BN_HALF;    // accumulator columns per tile
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;               // 16 KiB
+constexpr int B_HALF_BYTES = BK * BN_HALF;     // 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + 2 * B_HALF_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+// tcgen05 instruction descriptor: D=f32, A=B=e4m3, A K-major, B MN-major, N=256, M=128
+constexpr uint32_t IDESC = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct GemmParams {
+  const int32_t* offsets;   // [E+1]
+  const float* scale_a;     // [E] activation scale per segment
+  const float* scale_b0;    // [E] weight scale (gate, or down)
+  const float* scale_b1;    // [E] weight scale (up); unused for DOWN
+  void* out;                // GATE_UP: h bf16 [M, N_out];  DOWN: y bf16 [M, N_out]
+  float* seg_amax;          // GATE_UP: [E] amax of h per segment
+  int32_t* status;
+  int E, Kdim, N_out, n_tiles;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (after flagging) when the limit is hit or another warp gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicOr(status, BWMOE_STATUS_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                            int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (16-byte units; version 1; 128-byte swizzle = layout type 2).
+// K-major operand: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// MN-major operand: 128 N-elements contiguous per K row; the next 128 N-elements lie
+// B_HALF_BYTES further (leading offset); 8-K-row groups are 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_nmajor(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)(B_HALF_BYTES >> 4) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// tile index -> (expert, first row, end of segment, column block); every role walks the
+// same monotone sequence, so a forward-moving expert cursor suffices.
+struct TileCursor {
+  const int* cum;       // smem [E+1]: tiles before expert e
+  const int32_t* offsets;
+  int E, n_tiles, e;
+  __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx) {
+    while (e < E && tile >= cum[e + 1]) ++e;
+    if (e >= E) return false;
+    const int seg0 = offsets[e], seg1 = offsets[e + 1];
+    const int m_tiles = (seg1 - seg0 + BM - 1) / BM;
+    const int within = tile - cum[e];
+    n_idx = within / m_tiles;
+    row0 = seg0 + (within % m_tiles) * BM;
+    row_end = seg1;
+    expert = e;
+    return true;
+  }
+};
+
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_cum[257];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
+  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &s_abort;
+
+  // ---- set-up ----
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    int run = 0;
+    for (int e = 0; e < p.E; ++e) {
+      s_cum[e] = run;
+      const int rows = p.offsets[e + 1] - p.offsets[e];
+      run += ((rows + BM - 1) / BM) * p.n_tiles;
+    }
+    s_cum[p.E] = run;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const int total_tiles = s_cum[p.E];
+  const int k_blocks = (p.Kdim + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        int e, row0, row_end, n_idx;
+        if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+        const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status))) break;
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(sa, &map_a, full, kb * BK, row0);
+          tma_load_3d(sa + A_BYTES, &map_b0, full, n0, kb * BK, e);
+          if (GATE_UP) tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b1, full, n0, kb * BK, e);
+          else         tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b0, full, n0 + BN_HALF, kb * BK, e);
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1u, use = local >> 1;
+        // wait until the epilogue has drained this accumulator buffer (first use passes at once)
+        if (!(ok = mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
+          tc_fence_after();
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            // A: +32 bytes along K inside the swizzle atom; B: +32 K rows = 4096 bytes
+            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          mma_commit(bar_empty + 8 * stage);          // frees the stage when these MMAs retire
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+        if (ok) mma_commit(bar_tfull + 8 * buf);       // accumulator complete
+      }
+    }
+  } else {
+    // ===================== epilogue (warps 2..5) =====================
+    const int quarter = warp & 3;                      // TMEM lane group this warp may read
+    const int r_in_tile = quarter * 32 + lane;
+    TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+    uint32_t local = 0;
+    bool ok = true;
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      int e, row0, row_end, n_idx;
+      if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+      const uint32_t buf = local & 1u, use = local >> 1;
+      ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      const int row = row0 + r_in_tile;
+      const bool row_ok = row < row_end;
+      const float sa = p.scale_a[e];
+      if constexpr (GATE_UP) {
+        const float inv_g = 1.0f / (sa * p.scale_b0[e]);
+        const float inv_u = 1.0f / (sa * p.scale_b1[e]);
+        const int n0 = n_idx * BN_HALF;
+        float amax = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN_HALF / 32; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld32(t_row + c * 32, g);
+          tmem_ld32(t_row + BN_HALF + c * 32, u);
+          tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float hv[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              // the reference's bf16 rounding points: gate, up, silu(gate), product
+              const float gate = bf16_round(__uint_as_float(g[2 * j + q]) * inv_g);
+              const float up = bf16_round(__uint_as_float(u[2 * j + q]) * inv_u);
+              const float act = bf16_round(silu_f(gate));
+              hv[q] = bf16_round(act * up);
+              amax = fmaxf(amax, fabsf(hv[q]));
+            }
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[0], hv[1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+          if (row_ok) {
+            __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (n0 + c * 32 + v * 8 < p.N_out)
+                reinterpret_cast<uint4*>(dst)[v] =
+                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+          }
+        }
+        // rows past the segment and columns past H hold other data / zero fill: exclude them
+        // (zero-filled columns give h = 0, which cannot raise the maximum)
+        if (!row_ok) amax = 0.f;
+        for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0 && amax > 0.f) atomic_max_nonneg(p.seg_amax + e, amax);
+      } else {
+        const float inv = 1.0f / (sa * p.scale_b0[e]);
+        const int n0 = n_idx * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld32(t_row + c * 32, a);
+          tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[2 * j]) * inv,
+                                                      __uint_as_float(a[2 * j + 1]) * inv);
+            packed[j] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+          if (row_ok) {
+            __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (n0 + c * 32 + v * 8 < p.N_out)
+                reinterpret_cast<uint4*>(dst)[v] =
+                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+          }
+        }
+      }
+      // hand the accumulator buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+    }
+  }
+
+  // ---- teardown ----
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// activations [rows, kdim] e4m3 row-major: box 128 (K) x 128 (rows), 128-byte swizzle
+int make_map_a(CUtensorMap* map, const void* base, int rows, int kdim) {
+  auto fn = encode_fn();
+  BWMOE_REQUIRE(fn != nullptr, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)kdim, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kdim};
+  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  BWMOE_REQUIRE(r == CUDA_SUCCESS, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled(A: rows=%d k=%d) failed: %d", rows,
+                kdim, (int)r);
+  return BWMOE_OK;
+}
+// weights [E, kdim, n] e4m3, n contiguous: box 128 (N) x 128 (K) x 1, 128-byte swizzle
+int make_map_b(CUtensorMap* map, const void* base, int E, int kdim, int n) {
+  auto fn = encode_fn();
+  BWMOE_REQUIRE(fn != nullptr, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)kdim, (cuuint64_t)E};
+  cuuint64_t strides[2] = {(cuuint64_t)n, (cuuint64_t)n * (cuuint64_t)kdim};
+  cuuint32_t box[3] = {BN_HALF, BK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  BWMOE_REQUIRE(r == CUDA_SUCCESS, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled(B: E=%d k=%d n=%d) failed: %d", E,
+                kdim, n, (int)r);
+  return BWMOE_OK;
+}
+
+template <bool GATE_UP>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const GemmParams& p,
+                int M, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(grouped_gemm_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  BWMOE_CUDA_OK(attr_err);
+  const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
+  const int grid = (int)std::min<long long>(sm_count(), max_tiles);
+  grouped_gemm_kernel<GATE_UP><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int check_common(const char* who, const void* a, const void* b, int M, int D, int H, int E) {
+  BWMOE_REQUIRE(M > 0 && D > 0 && H > 0 && E > 0, BWMOE_ERR_BAD_SHAPE, "%s: M=%d D=%d H=%d E=%d", who, M, D, H, E);
+  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
+  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "%s: E=%d > 256", who, E);
+  BWMOE_REQUIRE(aligned16(a) && aligned16(b), BWMOE_ERR_BAD_ALIGN, "%s: pointers must be 16-byte aligned", who);
+  return BWMOE_OK;
+}
+
+}  // namespace
+
+size_t gemm_scratch_bytes(int /*M*/, int /*E*/) { return 256; }
+
+int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
+                  const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
+                  int32_t* status, void* /*scratch*/, cudaStream_t st) {
+  BWMOE_REQUIRE(xq && offsets && sx && wg && wu && sg && su && h && amax_h && status, BWMOE_ERR_NULL,
+                "gateup: null pointer");
+  if (int rc = check_common("gateup", xq, h, M, D, H, E)) return rc;
+  BWMOE_REQUIRE(aligned16(wg) && aligned16(wu), BWMOE_ERR_BAD_ALIGN, "gateup: weights must be 16-byte aligned");
+  CUtensorMap ma, mg, mu;
+  if (int rc = make_map_a(&ma, xq, M, D)) return rc;
+  if (int rc = make_map_b(&mg, wg, E, D, H)) return rc;
+  if (int rc = make_map_b(&mu, wu, E, D, H)) return rc;
+  GemmParams p{offsets, sx, sg, su, h, amax_h, status, E, D, H, ceil_div(H, BN_HALF)};
+  return launch_gemm<true>(ma, mg, mu, p, M, st);
+}
+
+int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
+                int M, int D, int H, int E, void* y, int32_t* status, void* /*scratch*/, cudaStream_t st) {
+  BWMOE_REQUIRE(hq && offsets && sh && wd && sd && y && status, BWMOE_ERR_NULL, "down: null pointer");
+  if (int rc = check_common("down", hq, y, M, D, H, E)) return rc;
+  BWMOE_REQUIRE(aligned16(wd), BWMOE_ERR_BAD_ALIGN, "down: weights must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  if (int rc = make_map_a(&ma, hq, M, H)) return rc;
+  if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;
+  GemmParams p{offsets, sh, sd, nullptr, y, nullptr, status, E, H, D, ceil_div(D, BN)};
+  return launch_gemm<false>(ma, mb, mb, p, M, st);
+}
+
+}  // namespace bwmoe

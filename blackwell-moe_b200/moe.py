@@ -1,0 +1,187 @@
+"""Host-side mirror of the reference's MoE-block API on top of libbwmoe.so.
+
+Signatures, argument meaning and error behaviour follow
+``fp8_moe_forward`` (src/blackwell_moe/kernels/fp8_moe.py:111-121) and
+``top_k_router`` (src/blackwell_moe/kernels/routing.py:61-66): pure functions
+that return fresh tensors and never modify their inputs.  PyTorch is used for
+device memory and streams only.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_FP8 = torch.float8_e4m3fn
+_workspaces: dict = {}
+
+
+def _require_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("libbwmoe works on CUDA tensors only (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors on different devices: {t.device} vs {dev}")
+    return dev
+
+
+def _contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _workspace(dev, nbytes: int) -> torch.Tensor:
+    """One grow-only workspace per (device, stream): calls on one stream are
+    ordered, so they can share it; different streams get their own."""
+    key = (dev.index, _stream(dev))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+def top_k_router(hidden: torch.Tensor, gate_w: torch.Tensor, k: int):
+    """Return ``(weights[T,k] fp32, indices[T,k] int32)``: softmax over all
+    experts, top-k, renormalised; equal logits go to the lower expert id."""
+    assert hidden.dim() == 2 and gate_w.dim() == 2 and hidden.shape[1] == gate_w.shape[0], \
+        (hidden.shape, gate_w.shape)
+    assert hidden.dtype == torch.bfloat16 and gate_w.dtype == torch.bfloat16, (hidden.dtype, gate_w.dtype)
+    dev = _require_cuda(hidden, gate_w)
+    T, D = hidden.shape
+    E = gate_w.shape[1]
+    hidden, gate_w = _contig(hidden, "hidden"), _contig(gate_w, "gate_w")
+    with torch.cuda.device(dev):
+        w_out = torch.empty((T, k), device=dev, dtype=torch.float32)
+        i_out = torch.empty((T, k), device=dev, dtype=torch.int32)
+        _lib.check(_lib.lib().bwmoe_router(hidden.data_ptr(), gate_w.data_ptr(), T, D, E, k,
+                                           w_out.data_ptr(), i_out.data_ptr(), None, _stream(dev)))
+    return w_out, i_out
+
+
+def _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down):
+    assert x.dim() == 2, x.shape
+    T, D = x.shape
+    assert experts_w_gate.dim() == 3 and experts_w_gate.shape[1] == D, (experts_w_gate.shape, D)
+    E, _, H = experts_w_gate.shape
+    assert tuple(experts_w_up.shape) == (E, D, H), experts_w_up.shape
+    assert tuple(experts_w_down.shape) == (E, H, D), experts_w_down.shape
+    for s in (scales_gate, scales_up, scales_down):
+        assert s.numel() == E and s.dtype == torch.float32, (s.shape, s.dtype)
+    for w in (experts_w_gate, experts_w_up, experts_w_down):
+        assert w.dtype == _FP8, w.dtype
+    assert x.dtype == torch.bfloat16, x.dtype
+    return T, D, H, E
+
+
+def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
+                    scales_gate, scales_up, scales_down, top_k: int = 8) -> torch.Tensor:
+    """FP8 MoE-block forward: ``x[T,D] bf16 -> out[T,D] bf16``.
+
+    ``x`` on the GPU: everything stays on the device and the result is a new
+    CUDA tensor.  ``x`` in (pinned) host memory: the library copies it in,
+    runs the block and copies the result back into a new pinned host tensor
+    (weights must still be CUDA tensors)."""
+    T, D, H, E = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down,
+                                scales_gate, scales_up, scales_down)
+    assert w_gate.shape == (D, E) and w_gate.dtype == torch.bfloat16, (w_gate.shape, w_gate.dtype)
+    weights = [_contig(t, "weight tensor") for t in (w_gate, experts_w_gate, experts_w_up, experts_w_down,
+                                                     scales_gate, scales_up, scales_down)]
+    dev = _require_cuda(*weights)
+    lib = _lib.lib()
+    x = _contig(x, "x")
+    with torch.cuda.device(dev):
+        ptrs = [t.data_ptr() for t in weights]
+        if x.is_cuda:
+            _require_cuda(x, w_gate)
+            need = lib.bwmoe_workspace_bytes(T, D, H, E, top_k)
+            if need == 0:
+                raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={top_k} "
+                                 "(D and H must be multiples of 16, E <= 256, top_k <= min(E, 32))")
+            ws = _workspace(dev, need)
+            out = torch.empty_like(x)
+            _lib.check(lib.bwmoe_moe_forward(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
+                                             ws.data_ptr(), ws.numel(), _stream(dev)))
+            return out
+        need = lib.bwmoe_workspace_bytes_host(T, D, H, E, top_k)
+        if need == 0:
+            raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={top_k}")
+        ws = _workspace(dev, need)
+        out = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+        _lib.check(lib.bwmoe_moe_forward_host(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
+                                              ws.data_ptr(), ws.numel(), _stream(dev)))
+        return out
+
+
+def fp8_moe_forward_routed(x, router_weights, expert_indices, experts_w_gate, experts_w_up, experts_w_down,
+                           scales_gate, scales_up, scales_down) -> torch.Tensor:
+    """Same block with caller-supplied routing (``router_weights[T,K] fp32``,
+    ``expert_indices[T,K] int32`` into the E weight slots) - the entry point an
+    expert-residency cache uses after remapping expert ids to slots
+    (src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-55)."""
+    T, D, H, E = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down,
+                                scales_gate, scales_up, scales_down)
+    assert router_weights.shape == expert_indices.shape and router_weights.shape[0] == T
+    K = router_weights.shape[1]
+    tensors = [_contig(t, "tensor") for t in (x, router_weights.to(torch.float32), expert_indices.to(torch.int32),
+                                              experts_w_gate, experts_w_up, experts_w_down,
+                                              scales_gate, scales_up, scales_down)]
+    dev = _require_cuda(*tensors)
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        need = lib.bwmoe_workspace_bytes(T, D, H, E, K)
+        if need == 0:
+            raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={K}")
+        ws = _workspace(dev, need)
+        out = torch.empty_like(x)
+        _lib.check(lib.bwmoe_moe_forward_routed(*[t.data_ptr() for t in tensors], T, D, H, E, K,
+                                                out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)))
+    return out
+
+
+_VIEWS = {
+    "status": (0, torch.int32), "offsets": (1, torch.int32), "indices": (2, torch.int32),
+    "weights": (3, torch.float32), "pos": (4, torch.int32), "row_slot": (5, torch.int32),
+    "scale_x": (6, torch.float32), "scale_h": (7, torch.float32), "xq": (8, torch.uint8),
+    "hq": (9, torch.uint8), "h": (10, torch.bfloat16), "y": (11, torch.bfloat16),
+    "row_expert": (12, torch.int32),
+}
+
+
+def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int) -> dict:
+    """Copies of the intermediates the last forward of this shape on the current
+    stream left in its workspace (routing, permutation, FP8 codes, scales) and
+    the device status word.  For stage-level checks; synchronises."""
+    dev = torch.device(dev)
+    lib = _lib.lib()
+    ws = _workspaces[(dev.index, _stream(dev))]
+    out = {}
+    torch.cuda.synchronize(dev)
+    for name, (sel, dtype) in _VIEWS.items():
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        _lib.check(lib.bwmoe_workspace_view(ws.data_ptr(), T, D, H, E, K, sel, C.byref(ptr), C.byref(nbytes)))
+        off = ptr.value - ws.data_ptr()
+        out[name] = ws[off:off + nbytes.value].clone().view(dtype)
+    M = T * K
+    out["indices"] = out["indices"].view(T, K)
+    out["weights"] = out["weights"].view(T, K)
+    out["xq"] = out["xq"].view(M, D).view(_FP8)
+    out["hq"] = out["hq"].view(M, H).view(_FP8)
+    out["h"] = out["h"].view(M, H)
+    out["y"] = out["y"].view(M, D)
+    return out

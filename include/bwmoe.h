@@ -1,0 +1,228 @@
+/*
+ * bwmoe.h -- C ABI of libbwmoe.so: the FP8 Mixture-of-Experts block forward
+ * for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - every pointer named d_* is a DEVICE pointer owned by the caller; h_* is a
+ *     HOST pointer.  The library allocates no device memory, frees nothing and
+ *     keeps no pointer after a call returns (bwmoe_moe_forward_host is the one
+ *     documented exception: it uses a caller-provided device workspace too).
+ *   - all work is enqueued on `stream` (a cudaStream_t passed as void*); no call
+ *     synchronises the device except bwmoe_moe_forward_host and bwmoe_read_status.
+ *   - every function returns 0 on success or a negative BWMOE_ERR_* code;
+ *     bwmoe_last_error() gives the thread-local message of the last failure.
+ *   - shapes: T tokens, D hidden, H expert intermediate, E experts, K = top_k,
+ *     M = T*K permuted rows.  Tensors are dense row-major:
+ *       x[T,D] bf16, w_gate[D,E] bf16, experts_w_gate/up[E,D,H] e4m3,
+ *       experts_w_down[E,H,D] e4m3, scales_*[E] fp32 (forward multipliers
+ *       448/amax: dequantisation divides by them), out[T,D] bf16.
+ *   - device-side anomalies (a bounded wait that ran out, an expert id out of
+ *     range) never trap: they set a status word in the workspace which
+ *     bwmoe_read_status returns.
+ *
+ * "replaces" comments cite the reference implementation (paths relative to the
+ * reference project's root) whose role each entry point takes over.
+ */
+#ifndef BWMOE_H_
+#define BWMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BWMOE_VERSION 100
+
+enum {
+  BWMOE_OK = 0,
+  BWMOE_ERR_BAD_SHAPE = -1,   /* a dimension is zero/negative or violates a divisibility rule */
+  BWMOE_ERR_BAD_ALIGN = -2,   /* a pointer is not 16-byte aligned */
+  BWMOE_ERR_WORKSPACE = -3,   /* workspace null or smaller than bwmoe_workspace_bytes() */
+  BWMOE_ERR_UNSUPPORTED = -4, /* valid request the kernels do not cover (e.g. E > 256) */
+  BWMOE_ERR_CUDA = -5,        /* a CUDA runtime/driver call failed (message has the detail) */
+  BWMOE_ERR_NULL = -6,        /* a required pointer is null */
+  BWMOE_ERR_DEVICE_STATUS = -7 /* a kernel reported an anomaly through the status word */
+};
+
+/* Bits of the device status word (bwmoe_read_status). */
+enum {
+  BWMOE_STATUS_WAIT_TIMEOUT = 1, /* a bounded barrier wait inside a GEMM kernel gave up */
+  BWMOE_STATUS_BAD_EXPERT = 2    /* an expert id outside [0,E) was met while planning */
+};
+
+/* Selectors for bwmoe_workspace_view: intermediates kept in the workspace after
+ * a forward, exposed so that tests can check each stage bit for bit. */
+enum {
+  BWMOE_WS_STATUS = 0,     /* int32[4]                                   */
+  BWMOE_WS_OFFSETS = 1,    /* int32[E+1]  segment offsets                */
+  BWMOE_WS_TOPK_IDX = 2,   /* int32[T*K]  routing indices                */
+  BWMOE_WS_TOPK_W = 3,     /* float[T*K]  routing weights                */
+  BWMOE_WS_POS = 4,        /* int32[M]    slot (t*K+k) -> permuted row   */
+  BWMOE_WS_ROW_SLOT = 5,   /* int32[M]    permuted row -> slot           */
+  BWMOE_WS_SCALE_X = 6,    /* float[E]    per-segment scale of x         */
+  BWMOE_WS_SCALE_H = 7,    /* float[E]    per-segment scale of h         */
+  BWMOE_WS_XQ = 8,         /* e4m3[M*D]   quantised permuted activations */
+  BWMOE_WS_HQ = 9,         /* e4m3[M*H]   quantised SwiGLU output        */
+  BWMOE_WS_H = 10,         /* bf16[M*H]   SwiGLU output before requant   */
+  BWMOE_WS_Y = 11,         /* bf16[M*D]   down-projection rows           */
+  BWMOE_WS_ROW_EXPERT = 12 /* int32[M]    permuted row -> expert         */
+};
+
+int bwmoe_version(void);
+
+/* Copies the calling thread's last error message (NUL-terminated, truncated to
+ * `len`) and returns its length. */
+int bwmoe_last_error(char* buf, size_t len);
+
+/* Bytes of device workspace one forward of this shape needs (0 on a bad shape). */
+size_t bwmoe_workspace_bytes(int T, int D, int H, int E, int K);
+
+/* Workspace size for bwmoe_moe_forward_host (0 on a bad shape). */
+size_t bwmoe_workspace_bytes_host(int T, int D, int H, int E, int K);
+
+/* Device pointer and byte size of one intermediate inside a workspace. */
+int bwmoe_workspace_view(void* d_workspace, int T, int D, int H, int E, int K, int which,
+                         void** d_ptr, size_t* bytes);
+
+/* Blocks until `stream` is idle and returns the device status word (0 = clean)
+ * in *status. */
+int bwmoe_read_status(void* d_workspace, void* stream, int32_t* status);
+
+/*
+ * Fused gate -> softmax -> top-k -> renormalise.
+ * replaces: top_k_router / _top_k_gate_kernel, src/blackwell_moe/kernels/routing.py:14-79
+ *           (and the torch routing inlined at src/blackwell_moe/kernels/fp8_moe_v3.py:34-37).
+ * Selection is on the exactly-rounded fp32 logits; equal logits go to the lower
+ * expert id.  d_weights[T,K] fp32 sum to 1, d_indices[T,K] int32 are ordered by
+ * decreasing probability.  d_row_amax[T] (optional, may be null) receives
+ * max|x[t,:]|.  Any E in [1,256], any K in [1,min(E,32)].
+ */
+int bwmoe_router(const void* d_x, const void* d_w_gate, int T, int D, int E, int K,
+                 float* d_weights, int32_t* d_indices, float* d_row_amax, void* stream);
+
+/*
+ * Whole block: router -> permute + segment-amax + E4M3 quant -> grouped gate+up
+ * GEMM + SwiGLU -> segment requant -> grouped down GEMM -> weighted combine.
+ * replaces: fp8_moe_forward, src/blackwell_moe/kernels/fp8_moe.py:111-164, and
+ *           fp8_moe_forward_v3, src/blackwell_moe/kernels/fp8_moe_v3.py:19-74.
+ * Requires D % 16 == 0, H % 16 == 0, E <= 256, K <= min(E,32).
+ */
+int bwmoe_moe_forward(const void* d_x, const void* d_w_gate,
+                      const void* d_experts_w_gate, const void* d_experts_w_up,
+                      const void* d_experts_w_down,
+                      const float* d_scales_gate, const float* d_scales_up, const float* d_scales_down,
+                      int T, int D, int H, int E, int K,
+                      void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same block with the routing decided by the caller: d_weights[T,K] fp32 and
+ * d_indices[T,K] int32 index the E expert slots of the weight tensors.
+ * replaces: fp8_moe_forward_fastcache, src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-55,
+ *           and the pipeline half of streaming_moe_forward,
+ *           src/blackwell_moe/runtime/streaming_moe.py:78-106.
+ */
+int bwmoe_moe_forward_routed(const void* d_x, const float* d_weights, const int32_t* d_indices,
+                             const void* d_experts_w_gate, const void* d_experts_w_up,
+                             const void* d_experts_w_down,
+                             const float* d_scales_gate, const float* d_scales_up,
+                             const float* d_scales_down,
+                             int T, int D, int H, int E, int K,
+                             void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * bwmoe_moe_forward for callers that hold activations in host memory: copies
+ * h_x[T,D] to the device (into the workspace), runs the block, copies the result
+ * to h_out[T,D] and waits for it.  Weights stay device-resident.  The workspace
+ * must hold bwmoe_workspace_bytes_host() bytes (the regular workspace plus device
+ * copies of x and out).
+ * replaces: the same call as bwmoe_moe_forward, as made by FP8MoELayer.forward,
+ *           src/blackwell_moe/runtime/deepseek_patch.py:39-53, on host activations.
+ */
+int bwmoe_moe_forward_host(const void* h_x, const void* d_w_gate,
+                           const void* d_experts_w_gate, const void* d_experts_w_up,
+                           const void* d_experts_w_down,
+                           const float* d_scales_gate, const float* d_scales_up,
+                           const float* d_scales_down,
+                           int T, int D, int H, int E, int K,
+                           void* h_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* ---- stage entry points (used by the expert-parallel host code and by tests) ---- */
+
+/*
+ * Plan the permutation: stable counting sort of the T*K slots by expert id.
+ * replaces: the sort/bincount/cumsum of src/blackwell_moe/kernels/fp8_moe_v3.py:39-48
+ *           (permute_tokens, src/blackwell_moe/kernels/permute.py:12-39).
+ * Outputs: d_offsets[E+1], d_pos[M] (slot -> row), d_row_slot[M] (row -> slot),
+ * d_row_expert[M], d_seg_amax[E] (max of d_row_amax over each segment; pass
+ * d_row_amax = null to skip it).  d_scratch needs bwmoe_plan_scratch_bytes().
+ */
+size_t bwmoe_plan_scratch_bytes(int T, int E, int K);
+int bwmoe_permute_plan(const int32_t* d_indices, const float* d_row_amax, int T, int E, int K,
+                       int32_t* d_offsets, int32_t* d_pos, int32_t* d_row_slot,
+                       int32_t* d_row_expert, float* d_seg_amax, int32_t* d_status,
+                       void* d_scratch, void* stream);
+
+/*
+ * scale[e] = 448 / max(amax[e], bf16(1e-4)); 1.0 for an empty segment.
+ * replaces: segment_fp8_scales, src/blackwell_moe/kernels/segment_ops.py:15-65
+ *           (single-tensor form quant_fp8_e4m3, src/blackwell_moe/kernels/fp8_quant.py:24-32).
+ */
+int bwmoe_segment_scales(const float* d_seg_amax, const int32_t* d_offsets, int E, float* d_scales,
+                         void* stream);
+
+/*
+ * Gather rows of x into expert-contiguous order and quantise them to E4M3 with
+ * the per-segment scale: xq[m,:] = e4m3(clamp(x[row_slot[m]/K,:] * scale[row_expert[m]], +-448)).
+ * replaces: x[inverse_idx] + segment_quant_fp8, src/blackwell_moe/kernels/fp8_moe_v3.py:44,51
+ *           and src/blackwell_moe/kernels/segment_ops.py:68-120.
+ */
+int bwmoe_gather_quant(const void* d_x, const int32_t* d_row_slot, const int32_t* d_row_expert,
+                       const float* d_scales, int M, int D, int K, void* d_xq, void* stream);
+
+/*
+ * Grouped gate+up FP8 GEMM with SwiGLU: h[m,:] = silu(gate) * up in bf16 with the
+ * reference's bf16 rounding points, plus d_seg_amax_h[e] = max|h| per segment
+ * (d_seg_amax_h must be zero on entry).  d_scratch needs bwmoe_gemm_scratch_bytes(M, E).
+ * replaces: fused_gate_up_gemm, src/blackwell_moe/kernels/grouped_fp8_gateup.py:42-138,
+ *           and F.silu(gate)*up, src/blackwell_moe/kernels/fp8_moe_v3.py:60.
+ */
+size_t bwmoe_gemm_scratch_bytes(int M, int E);
+int bwmoe_gateup_swiglu(const void* d_xq, const int32_t* d_offsets, const float* d_scales_x,
+                        const void* d_experts_w_gate, const void* d_experts_w_up,
+                        const float* d_scales_gate, const float* d_scales_up,
+                        int M, int D, int H, int E,
+                        void* d_h, float* d_seg_amax_h, int32_t* d_status, void* d_scratch,
+                        void* stream);
+
+/*
+ * Per-segment requantisation of h to E4M3.
+ * replaces: segment_fp8_scales + segment_quant_fp8 on h,
+ *           src/blackwell_moe/kernels/fp8_moe_v3.py:61-62.
+ */
+int bwmoe_requant(const void* d_h, const int32_t* d_row_expert, const float* d_scales_h, int M, int H,
+                  void* d_hq, void* stream);
+
+/*
+ * Grouped down FP8 GEMM: y[m,:] = bf16(acc / (scale_h[e] * scale_down[e])).
+ * replaces: grouped_fp8_gemm, src/blackwell_moe/kernels/grouped_fp8.py:36-128.
+ */
+int bwmoe_down(const void* d_hq, const int32_t* d_offsets, const float* d_scales_h,
+               const void* d_experts_w_down, const float* d_scales_down,
+               int M, int D, int H, int E,
+               void* d_y, int32_t* d_status, void* d_scratch, void* stream);
+
+/*
+ * Weighted combine back to token order, deterministic:
+ * out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ), k ascending.
+ * replaces: flat_w multiply + scatter_add, src/blackwell_moe/kernels/fp8_moe_v3.py:70-73
+ *           and src/blackwell_moe/kernels/scatter.py:25-72.
+ */
+int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights, int T, int D, int K,
+                  void* d_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BWMOE_H_ */

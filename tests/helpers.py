@@ -1,0 +1,75 @@
+"""Seeded synthetic inputs and comparison helpers shared by the tests."""
+
+from __future__ import annotations
+
+import torch
+
+import oracle
+
+BF16, FP8 = torch.bfloat16, torch.float8_e4m3fn
+
+
+def make_inputs(T, D, E, K, H, seed=0, x_scale=1.0, w_scale=0.02, keep_bf16=True):
+    """CPU tensors in the reference bench's order (src/blackwell_moe/bench/cli.py:39-70):
+    x, w_gate, expert weights ~N(0, w_scale^2) quantised per expert matrix."""
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(T, D, generator=g) * x_scale).to(BF16)
+    w_gate = (torch.randn(D, E, generator=g) * w_scale).to(BF16)
+    out = dict(x=x, w_gate=w_gate, k=K)
+    for name, (a, b) in (("gate", (D, H)), ("up", (D, H)), ("down", (H, D))):
+        qs, ss, ws = [], [], []
+        for _ in range(E):
+            w = (torch.randn(a, b, generator=g) * w_scale).to(BF16)
+            q, s = oracle.quant_fp8_e4m3(w)
+            qs.append(q), ss.append(s)
+            if keep_bf16:
+                ws.append(w)
+        out["q_" + name] = torch.stack(qs)
+        out["s_" + name] = torch.stack(ss).to(torch.float32)
+        if keep_bf16:
+            out["bf_" + name] = torch.stack(ws)
+    return out
+
+
+def to_cuda(inp, dev="cuda:0"):
+    return {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
+
+
+def run_cuda_forward(inp, dev="cuda:0"):
+    import blackwell_moe_b200 as bw
+    c = to_cuda(inp, dev)
+    out = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"],
+                             c["s_gate"], c["s_up"], c["s_down"], top_k=inp["k"])
+    T, D = inp["x"].shape
+    E, _, H = inp["q_gate"].shape
+    views = bw.moe_stage_views(dev, T, D, H, E, inp["k"])
+    return out.cpu(), {k: v.cpu() for k, v in views.items()}
+
+
+def run_oracle_forward(inp):
+    inter = {}
+    out = oracle.moe_forward_fp8_recipe(inp["x"], inp["w_gate"], inp["q_gate"], inp["q_up"], inp["q_down"],
+                                        inp["s_gate"], inp["s_up"], inp["s_down"], top_k=inp["k"],
+                                        intermediates=inter)
+    return out, inter
+
+
+def check_against_oracle(inp, out, views, ref_out, inter, tol=1e-2):
+    """Bit-exact routing / permutation / x codes; tolerance on everything behind a GEMM."""
+    E = inp["q_gate"].shape[0]
+    assert int(views["status"][0]) == 0, f"device status {int(views['status'][0])}"
+    assert torch.equal(views["indices"], inter["indices"]), "routing indices differ"
+    torch.testing.assert_close(views["weights"], inter["weights"], rtol=1e-3, atol=1e-4)
+    assert torch.equal(views["offsets"], inter["offsets"]), "segment offsets differ"
+    assert torch.equal(views["row_slot"].long(), inter["sort_perm"]), "permutation differs"
+    M = inter["sort_perm"].numel()
+    assert torch.equal(views["pos"].long()[inter["sort_perm"]], torch.arange(M)), "pos is not the inverse"
+    counts = inter["offsets"][1:] - inter["offsets"][:-1]
+    live = counts > 0
+    assert torch.equal(views["scale_x"][live], inter["sx"][live]), "x segment scales differ"
+    assert torch.equal(views["xq"].view(torch.uint8), inter["xq"].view(torch.uint8)), "x FP8 codes differ"
+    assert oracle.rel_l1(views["h"], inter["h"]) < 5e-3, "SwiGLU output off"
+    torch.testing.assert_close(views["scale_h"][live], inter["sh"][live], rtol=1.6e-2, atol=0)
+    err = oracle.rel_l1(out, ref_out)
+    assert err < tol, f"rel-L1 vs FP8 recipe oracle {err:.4f} >= {tol}"
+    return err

@@ -1,0 +1,62 @@
+"""Router kernel against the canonical oracle (bit-exact indices) and against the
+reference's own outputs stored as fixtures (shapes and tolerances of the
+reference's tests/test_router.py:7-33)."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import from_bits
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _route(x, w, k):
+    import blackwell_moe_b200 as bw
+    wt, idx = bw.top_k_router(x.cuda(), w.cuda(), k)
+    return wt.cpu(), idx.cpu()
+
+
+def test_router_matches_reference_fixtures(golden):
+    g = golden("router")
+    for i in range(int(g["n"])):
+        x, w, k = from_bits(g[f"x{i}"], BF16), from_bits(g[f"w{i}"], BF16), int(g[f"k{i}"])
+        wt, idx = _route(x, w, k)
+        assert np.array_equal(idx.numpy(), g[f"indices{i}"]), "expert indices must match exactly"
+        torch.testing.assert_close(wt, torch.from_numpy(g[f"weights{i}"]), rtol=1e-3, atol=1e-4)
+        torch.testing.assert_close(wt.sum(-1), torch.ones(wt.shape[0]), rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("T,D,E,K", [(1, 4096, 8, 2), (7, 2048, 64, 6), (300, 2048, 128, 8), (2500, 2048, 256, 8),
+                                     (33, 1024, 12, 12), (64, 512, 1, 1), (5000, 4096, 8, 2), (129, 272, 200, 32)])
+def test_router_bit_exact_vs_canonical(T, D, E, K):
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, D, generator=g).to(BF16)
+    w = (torch.randn(D, E, generator=g) * 0.02).to(BF16)
+    wt, idx = _route(x, w, K)
+    wr, ir = oracle.router_canonical(x, w, K)
+    assert torch.equal(idx, ir)
+    torch.testing.assert_close(wt, wr, rtol=1e-3, atol=1e-4)
+
+
+def test_router_ties_go_to_lower_id_and_near_ties_are_resolved_exactly():
+    # exact ties: identical gate columns
+    x = torch.randn(64, 256, generator=torch.Generator().manual_seed(1)).to(BF16)
+    col = (torch.randn(256, 1, generator=torch.Generator().manual_seed(2)) * 0.02).to(BF16)
+    w = col.repeat(1, 16).contiguous()
+    _, idx = _route(x, w, 4)
+    assert torch.equal(idx, torch.arange(4, dtype=torch.int32).repeat(64, 1))
+    # near ties: columns that differ in one low-order element only
+    w2 = w.clone()
+    w2[7, 3] = (w2[7, 3].float() * 1.01).to(BF16)
+    w2[100, 9] = (w2[100, 9].float() * 0.99).to(BF16)
+    wt, idx = _route(x, w2, 5)
+    wr, ir = oracle.router_canonical(x, w2, 5)
+    assert torch.equal(idx, ir)
+    # all-zero activations: every logit equal -> experts 0..K-1, uniform weights
+    z = torch.zeros(3, 256, dtype=BF16)
+    wt, idx = _route(z, w2, 4)
+    assert torch.equal(idx, torch.arange(4, dtype=torch.int32).repeat(3, 1))
+    torch.testing.assert_close(wt, torch.full((3, 4), 0.25))
