@@ -33,8 +33,10 @@ constexpr float kFp8Max = 448.0f;
 // bf16(1e-4) = 0x38D2, not the fp32 literal.
 constexpr float kAmaxFloor = 0.00010013580322265625f;
 
+// The reference writes `448.0 / amax` with a Python scalar on the left, which torch
+// evaluates as reciprocal(amax) * 448 (two roundings); reproduce exactly that.
 __device__ __forceinline__ float scale_from_amax(float amax) {
-  return __fdiv_rn(kFp8Max, fmaxf(amax, kAmaxFloor));
+  return __fmul_rn(__frcp_rn(fmaxf(amax, kAmaxFloor)), kFp8Max);
 }
 
 // e4m3(clamp(v, +-448)), round-to-nearest-even, as torch's cast after the clamp.
