@@ -40,6 +40,7 @@ SIGNATURES = {
     "bwmoe_moe_forward_host": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_plan_scratch_bytes": (_sz, [_i] * 3),
     "bwmoe_permute_plan": (_i, [_ip, _fp, _i, _i, _i, _ip, _ip, _ip, _ip, _fp, _ip, _vp, _vp]),
+    "bwmoe_permute_plan_static": (_i, [_ip, _fp, _i, _i, _i, _ip, _ip, _ip, _ip, _fp, _ip, _vp]),
     "bwmoe_segment_scales": (_i, [_fp, _ip, _i, _fp, _vp]),
     "bwmoe_gather_quant": (_i, [_vp, _ip, _ip, _fp, _i, _i, _i, _vp, _vp]),
     "bwmoe_gemm_scratch_bytes": (_sz, [_i] * 2),

@@ -286,6 +286,15 @@ int bwmoe_permute_plan(const int32_t* indices, const float* row_amax, int T, int
                      static_cast<cudaStream_t>(stream));
 }
 
+int bwmoe_permute_plan_static(const int32_t* indices, const float* row_amax, int T, int E, int K,
+                              int32_t* offsets, int32_t* pos, int32_t* row_slot, int32_t* row_expert,
+                              float* seg_amax, int32_t* status, void* stream) {
+  BWMOE_REQUIRE(indices && offsets && pos && row_slot && row_expert && status, BWMOE_ERR_NULL,
+                "plan_static: null pointer");
+  return launch_plan_static(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, seg_amax, status,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int bwmoe_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales, void* stream) {
   return launch_segment_scales(seg_amax, offsets, E, scales, static_cast<cudaStream_t>(stream));
 }

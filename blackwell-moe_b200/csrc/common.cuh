@@ -64,6 +64,9 @@ size_t plan_scratch_bytes(int T, int E, int K);
 int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
                 int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
                 void* scratch, cudaStream_t st);
+int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
+                       int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
+                       cudaStream_t st);
 int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,
                           cudaStream_t st);
 int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert,

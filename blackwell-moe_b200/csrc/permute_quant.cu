@@ -5,6 +5,8 @@
 // src/blackwell_moe/kernels/fp8_moe_v3.py:39-48, of the Triton segment kernels
 // (src/blackwell_moe/kernels/segment_ops.py:15-120) and of the scatter-add combine
 // (src/blackwell_moe/kernels/scatter.py:25-72).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace bwmoe {
@@ -219,6 +221,45 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
   plan_rank_kernel<<<B, kPlanThreads, smem, st>>>(indices, M, E, block_hist, pos, row_slot, row_expert);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
+}
+
+// ---- allocation-free variant of the permutation plan ------------------------------
+// Scratch for callers that cannot hand the library a scratch buffer: a fixed array
+// that lives in every GPU's memory from the moment the library is loaded there.
+constexpr int kStaticPlanBlocks = 64;                       // 64 * 4096 = 262144 slots at most
+static __device__ __align__(256) int32_t g_static_plan_scratch[kStaticPlanBlocks * kMaxE];   // 64 KiB
+
+int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
+                       int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
+                       cudaStream_t st) {
+  BWMOE_REQUIRE(T > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "plan_static: T=%d E=%d K=%d", T, E, K);
+  BWMOE_REQUIRE(E <= kMaxE, BWMOE_ERR_UNSUPPORTED, "plan_static: E=%d > %d", E, kMaxE);
+  const long long max_slots = (long long)kStaticPlanBlocks * kSlotsPerBlock;
+  BWMOE_REQUIRE((long long)T * K <= max_slots, BWMOE_ERR_UNSUPPORTED,
+                "plan_static: T*K=%lld exceeds the %lld slots the built-in scratch covers; "
+                "use bwmoe_permute_plan with a caller-provided scratch buffer",
+                (long long)T * K, max_slots);
+  // In host code `g_static_plan_scratch` is only a handle for the symbol, not a device
+  // address: ask the runtime where the array lives on the CURRENT device, once per device.
+  static std::mutex mu;
+  static void* dev_ptr[64] = {nullptr};
+  int dev = 0;
+  BWMOE_CUDA_OK(cudaGetDevice(&dev));
+  BWMOE_REQUIRE(dev >= 0 && dev < 64, BWMOE_ERR_UNSUPPORTED, "plan_static: device ordinal %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      BWMOE_CUDA_OK(cudaGetSymbolAddress(&p, g_static_plan_scratch));
+      BWMOE_REQUIRE(p != nullptr, BWMOE_ERR_CUDA, "plan_static: cudaGetSymbolAddress returned null");
+      dev_ptr[dev] = p;
+    }
+    scratch = dev_ptr[dev];
+  }
+  // Nothing in the array has to start at zero: the histogram pass overwrites every entry
+  // the later passes read (blocks 0..B-1 x experts 0..E-1) before they read it.
+  return launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, seg_amax, status, scratch, st);
 }
 
 int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,

@@ -165,6 +165,31 @@ int bwmoe_permute_plan(const int32_t* d_indices, const float* d_row_amax, int T,
                        void* d_scratch, void* stream);
 
 /*
+ * bwmoe_permute_plan without a scratch argument, for callers that have no way to
+ * obtain device memory of their own at the point of the call: code running inside a
+ * framework's allocator callback or out-of-memory handler, a plugin that was handed
+ * only its input and output buffers, a real-time loop that has frozen its memory
+ * pool.  (No counterpart in the reference, which allocates freely through torch.)
+ * The scratch is a 64 KiB array built into the library image; every GPU that loads
+ * the library holds it until the process exits.  Limits and rules:
+ *   - T*K <= 262144 slots and E <= 256; larger requests fail with
+ *     BWMOE_ERR_UNSUPPORTED and a message pointing to bwmoe_permute_plan.
+ *   - inputs and outputs are still the caller's buffers, exactly as in
+ *     bwmoe_permute_plan; results are identical to it.
+ *   - the call allocates and frees nothing, on the host or the device.
+ *   - the first call on each device looks up the array's device address (with that
+ *     device current); make that first call outside any stream capture.
+ *   - all calls on one GPU share the one array and it keeps whatever the last call
+ *     left in it (nothing in it needs clearing between calls); two calls whose kernels
+ *     can overlap on the GPU - different streams without an ordering between them -
+ *     race on it.  Keep calls on one stream, or order them with events.
+ */
+int bwmoe_permute_plan_static(const int32_t* d_indices, const float* d_row_amax, int T, int E, int K,
+                              int32_t* d_offsets, int32_t* d_pos, int32_t* d_row_slot,
+                              int32_t* d_row_expert, float* d_seg_amax, int32_t* d_status,
+                              void* stream);
+
+/*
  * scale[e] = 448 / max(amax[e], bf16(1e-4)); 1.0 for an empty segment.
  * replaces: segment_fp8_scales, src/blackwell_moe/kernels/segment_ops.py:15-65
  *           (single-tensor form quant_fp8_e4m3, src/blackwell_moe/kernels/fp8_quant.py:24-32).
