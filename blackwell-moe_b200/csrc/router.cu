@@ -46,6 +46,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const int DS = kThreads / Epad;       // d-slices; thread (e, ds) sums d = ds, ds+DS, ...
   const int e = tid % Epad, ds = tid / Epad;
   const bool e_ok = e < E;
+  const bool vec_ok = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
 
   float acc[TOK], inner[TOK];
 #pragma unroll
@@ -54,15 +55,34 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   int inner_n = 0;
 
   for (int c0 = 0; c0 < D; c0 += kChunk) {
-    // stage x[tok0..tok0+TOK, c0..c0+kChunk) transposed; lanes run over tokens
-    for (int idx = tid; idx < kChunk * TOK; idx += kThreads) {
-      const int t = idx % TOK, dd = idx / TOK;
-      float v = 0.f;
-      if (tok0 + t < T && c0 + dd < D) v = __bfloat162float(x[(size_t)(tok0 + t) * D + c0 + dd]);
-      xs[dd * TOK + t] = v;
-      // idx % TOK is the same for every iteration of this thread (kThreads % TOK == 0)
-      my_abs += fabsf(v);
-      my_max = fmaxf(my_max, fabsf(v));
+    // stage x[tok0..tok0+TOK, c0..c0+kChunk) transposed to [d][token]; a thread always serves
+    // token tid % TOK, so its running |x| statistics belong to one token
+    if (vec_ok) {
+      // 16-byte loads: lanes run over tokens, each taking 8 consecutive d; two lanes share a 32-byte sector
+      for (int idx = tid; idx < (kChunk / 8) * TOK; idx += kThreads) {
+        const int t = idx % TOK, dd0 = (idx / TOK) * 8;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (tok0 + t < T && c0 + dd0 < D)
+          raw = *reinterpret_cast<const uint4*>(x + (size_t)(tok0 + t) * D + c0 + dd0);
+        const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(pr[j]);
+          xs[(dd0 + 2 * j) * TOK + t] = f.x;
+          xs[(dd0 + 2 * j + 1) * TOK + t] = f.y;
+          my_abs += fabsf(f.x) + fabsf(f.y);
+          my_max = fmaxf(my_max, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+    } else {
+      for (int idx = tid; idx < kChunk * TOK; idx += kThreads) {
+        const int t = idx % TOK, dd = idx / TOK;
+        float v = 0.f;
+        if (tok0 + t < T && c0 + dd < D) v = __bfloat162float(x[(size_t)(tok0 + t) * D + c0 + dd]);
+        xs[dd * TOK + t] = v;
+        my_abs += fabsf(v);
+        my_max = fmaxf(my_max, fabsf(v));
+      }
     }
     __syncthreads();
     const int dlim = min(kChunk, D - c0);

@@ -1,0 +1,167 @@
+"""Expert-parallel MoE-block forward over the ranks of one node.
+
+The reference is single-GPU (its design notes name expert parallelism with an
+NCCL all-to-all as future work); this module adds it around the same CUDA
+stages.  Rank ``r`` of ``G`` owns experts ``[r*E/G, (r+1)*E/G)`` and brings its
+own tokens.  One step:
+
+1. route the local tokens, plan the local permutation (rows sorted by global
+   expert id, hence by destination rank);
+2. exchange per-expert row counts and activation maxima (one small all-gather)
+   so that every rank derives the same per-expert FP8 scale a single GPU
+   would;
+3. quantise the local rows with those scales and send them to the owners of
+   their experts (dispatch all-to-all, FP8 payload);
+4. regroup the received rows into per-expert segments ordered by (source rank,
+   source row) - the order a single GPU would have - and run gate/up + SwiGLU,
+   requant and the down projection on the local experts;
+5. send the bf16 result rows back (combine all-to-all) and do the weighted
+   top-k combine at home.
+
+The result is bit-identical to the single-GPU forward over the concatenated
+tokens.  The index arithmetic (:class:`ExchangePlan`, :func:`dispatch`,
+:func:`combine_back`) is device-agnostic torch code and is tested on CPU with
+``gloo``; the compute stages exist on CUDA only.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+_FP8 = torch.float8_e4m3fn
+
+
+class ExchangePlan:
+    """Split sizes and row maps of one dispatch/combine pair, derived from the
+    ``[G, E]`` matrix of per-rank, per-expert row counts."""
+
+    def __init__(self, counts: torch.Tensor, rank: int):
+        G, E = counts.shape
+        assert E % G == 0, (E, G)
+        self.rank, self.world, self.experts_local = rank, G, E // G
+        el = self.experts_local
+        cpu = counts.cpu().to(torch.int64)                       # the only host copy: split sizes must be ints
+        self.send_splits = cpu[rank].view(G, el).sum(1).tolist()  # rows I send to each rank
+        mine = cpu[:, rank * el:(rank + 1) * el]                 # [G, el] rows each rank sends me, per local expert
+        self.recv_splits = mine.sum(1).tolist()
+        self.rows_local = int(mine.sum())
+        dev = counts.device
+        mine = mine.to(dev)
+        # received order is (source, expert); wanted order is (expert, source)
+        start_src = (torch.cumsum(mine.reshape(-1), 0) - mine.reshape(-1)).view(G, el)
+        sizes_dst = mine.t().reshape(-1)                         # blocks in (expert, source) order
+        start_dst = torch.cumsum(sizes_dst, 0) - sizes_dst
+        block_src = start_src.t().reshape(-1)
+        n = self.rows_local
+        rows = torch.arange(n, device=dev)
+        self.src_of_dst = (torch.repeat_interleave(block_src - start_dst, sizes_dst, output_size=n) + rows)
+        seg = mine.sum(0)
+        self.offsets = torch.zeros(el + 1, dtype=torch.int32, device=dev)
+        self.offsets[1:] = torch.cumsum(seg, 0).to(torch.int32)
+        self.row_expert = torch.repeat_interleave(torch.arange(el, device=dev, dtype=torch.int32), seg, output_size=n)
+
+
+def dispatch(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor:
+    """Send rows (sorted by global expert id) to the expert owners; returns the
+    received rows regrouped into per-local-expert segments."""
+    recv = rows.new_empty((plan.rows_local,) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
+    return recv.index_select(0, plan.src_of_dst)
+
+
+def combine_back(rows_local: torch.Tensor, plan: ExchangePlan, n_home: int, group=None) -> torch.Tensor:
+    """Inverse of :func:`dispatch`: per-expert rows go back to the ranks (and row
+    positions) they came from."""
+    send = torch.empty_like(rows_local)
+    send.index_copy_(0, plan.src_of_dst, rows_local)
+    home = rows_local.new_empty((n_home,) + tuple(rows_local.shape[1:]))
+    dist.all_to_all_single(home, send, plan.send_splits, plan.recv_splits, group=group)
+    return home
+
+
+class ExpertParallelMoE:
+    """Holds this rank's expert shard and runs the expert-parallel forward."""
+
+    def __init__(self, w_gate, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down,
+                 num_experts: int, top_k: int, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.E, self.K = num_experts, top_k
+        assert num_experts % self.world == 0
+        self.el = num_experts // self.world
+        assert experts_w_gate.shape[0] == self.el, "pass this rank's expert shard"
+        self.w_gate = w_gate.contiguous()
+        self.wg, self.wu, self.wd = (t.contiguous() for t in (experts_w_gate, experts_w_up, experts_w_down))
+        self.sg, self.su, self.sd = (t.to(torch.float32).contiguous() for t in (scales_gate, scales_up, scales_down))
+        self.D, self.H = self.wg.shape[1], self.wg.shape[2]
+        self.dev = self.wg.device
+        assert self.w_gate.shape == (self.D, num_experts)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        host_in = not x.is_cuda
+        if host_in:
+            x = x.to(self.dev, non_blocking=True)
+        lib, dev, E, K, D, H, el = _lib.lib(), self.dev, self.E, self.K, self.D, self.H, self.el
+        T = x.shape[0]
+        M = T * K
+        st = torch.cuda.current_stream(dev).cuda_stream
+        i32, f32 = torch.int32, torch.float32
+        new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
+        weights, indices, row_amax = new(T, K, dtype=f32), new(T, K, dtype=i32), new(T, dtype=f32)
+        _lib.check(lib.bwmoe_router(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, weights.data_ptr(),
+                                    indices.data_ptr(), row_amax.data_ptr(), st))
+        offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
+        stats = torch.zeros(2 * E, dtype=f32, device=dev)          # [amax | counts-as-int32 bits]
+        status = torch.zeros(4, dtype=i32, device=dev)
+        scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=torch.uint8)
+        _lib.check(lib.bwmoe_permute_plan(indices.data_ptr(), row_amax.data_ptr(), T, E, K, offsets.data_ptr(),
+                                          pos.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(),
+                                          stats.data_ptr(), status.data_ptr(), scratch.data_ptr(), st))
+        stats[E:].view(i32).copy_(offsets[1:] - offsets[:-1])
+        gathered = new(self.world * 2 * E, dtype=f32)
+        dist.all_gather_into_tensor(gathered, stats, group=self.group)
+        gathered = gathered.view(self.world, 2 * E)
+        amax = gathered[:, :E].amax(0).contiguous()                # exact: a max of the same floats
+        counts = gathered[:, E:].contiguous().view(i32)
+        scale_x = new(E, dtype=f32)
+        _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
+        xq = new(M, D, dtype=torch.uint8)
+        _lib.check(lib.bwmoe_gather_quant(x.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(), scale_x.data_ptr(),
+                                          M, D, K, xq.data_ptr(), st))
+        plan = ExchangePlan(counts, self.rank)
+        xq_local = dispatch(xq, plan, self.group)
+        R = plan.rows_local
+        y_local = new(R, D, dtype=torch.bfloat16)
+        if R > 0:
+            sx_local = scale_x[self.rank * el:(self.rank + 1) * el].contiguous()
+            h = new(R, H, dtype=torch.bfloat16)
+            amax_h = torch.zeros(el, dtype=f32, device=dev)
+            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, el)), dtype=torch.uint8)
+            _lib.check(lib.bwmoe_gateup_swiglu(xq_local.data_ptr(), plan.offsets.data_ptr(), sx_local.data_ptr(),
+                                               self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                               self.su.data_ptr(), R, D, H, el, h.data_ptr(), amax_h.data_ptr(),
+                                               status.data_ptr(), gs.data_ptr(), st))
+            scale_h = new(el, dtype=f32)
+            _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), plan.offsets.data_ptr(), el, scale_h.data_ptr(), st))
+            hq = new(R, H, dtype=torch.uint8)
+            _lib.check(lib.bwmoe_requant(h.data_ptr(), plan.row_expert.data_ptr(), scale_h.data_ptr(), R, H,
+                                         hq.data_ptr(), st))
+            _lib.check(lib.bwmoe_down(hq.data_ptr(), plan.offsets.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
+                                      self.sd.data_ptr(), R, D, H, el, y_local.data_ptr(), status.data_ptr(),
+                                      gs.data_ptr(), st))
+        y_home = combine_back(y_local, plan, M, self.group)
+        out = new(T, D, dtype=torch.bfloat16)
+        _lib.check(lib.bwmoe_combine(y_home.data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K, out.data_ptr(), st))
+        self.last_status = status
+        if host_in:
+            host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+            host.copy_(out, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+            return host
+        return out

@@ -1,0 +1,74 @@
+"""Expert-parallel forward on 2 GPUs (NCCL) against the single-GPU forward.
+
+Needs two CUDA devices; skipped otherwise.  Every rank builds the same seeded
+inputs, keeps its shard of the experts and its slice of the tokens; the
+assembled output must equal the single-GPU result over all tokens bit for bit
+(same per-expert scales, same row order inside each expert segment)."""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import blackwell_moe_b200 as bw
+        from blackwell_moe_b200.ep import ExpertParallelMoE
+        from helpers import make_inputs
+        msgs = []
+        for (T, D, E, K, H) in ((96, 256, 8, 2, 256), (33, 512, 16, 4, 384), (700, 256, 4, 2, 128)):
+            inp = make_inputs(world * T, D, E, K, H, seed=T + E, keep_bf16=False)
+            c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
+            el = E // world
+            sl = slice(rank * el, (rank + 1) * el)
+            ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c["s_gate"][sl],
+                                   c["s_up"][sl], c["s_down"][sl], num_experts=E, top_k=K)
+            out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
+            assert int(ep.last_status[0]) == 0
+            full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
+            dist.all_gather_into_tensor(full, out)
+            ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"],
+                                     c["s_down"], top_k=K)
+            if not torch.equal(full, ref):
+                msgs.append(f"shape {(T, D, E, K, H)}: max diff {(full.float() - ref.float()).abs().max().item()}")
+            host = ep.forward(inp["x"][rank * T:(rank + 1) * T].contiguous().pin_memory())
+            if not torch.equal(host, out.cpu()):
+                msgs.append(f"shape {(T, D, E, K, H)}: host-buffer path differs")
+        ret[rank] = "ok" if not msgs else "; ".join(msgs)
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = traceback.format_exc() + repr(e)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_matches_single_gpu():
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+        for r in range(world):
+            assert ret.get(r) == "ok", f"rank {r}: {ret.get(r)}"
