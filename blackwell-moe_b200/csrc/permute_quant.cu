@@ -133,34 +133,31 @@ __global__ void segment_scales_kernel(const float* __restrict__ seg_amax, const 
   scales[e] = empty ? 1.0f : scale_from_amax(seg_amax[e]);
 }
 
-// ---- row-wise bf16 -> e4m3 with a per-row-selected scale; one warp per row ----
+// ---- row-wise bf16 -> e4m3 with a per-row-selected scale; one thread per 8 elements ----
 // SRC_BY_SLOT: source row = row_slot[m] / K (gather from token order); else source row = m.
 template <bool SRC_BY_SLOT>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot,
                   const int32_t* __restrict__ row_expert, const float* __restrict__ scales, int M, int W,
                   int K, uint8_t* __restrict__ dst) {
-  const int lane = threadIdx.x & 31;
-  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (m >= M) return;
+  const int vec_per_row = W / 8;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (size_t)M * vec_per_row) return;
+  const int m = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
   const float scale = scales[row_expert[m]];
   const size_t srow = SRC_BY_SLOT ? (size_t)(row_slot[m] / K) : (size_t)m;
-  const uint4* in = reinterpret_cast<const uint4*>(src + srow * W);
-  uint2* out = reinterpret_cast<uint2*>(dst + (size_t)m * W);
-  for (int v = lane; v < W / 8; v += 32) {
-    const uint4 raw = in[v];
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    uint32_t lo, hi;
-    {
-      const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
-      lo = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
-    }
-    {
-      const float2 a = __bfloat1622float2(p[2]), b = __bfloat1622float2(p[3]);
-      hi = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
-    }
-    out[v] = make_uint2(lo, hi);
+  const uint4 raw = reinterpret_cast<const uint4*>(src + srow * W)[v];
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  uint32_t lo, hi;
+  {
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+    lo = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
   }
+  {
+    const float2 a = __bfloat1622float2(p[2]), b = __bfloat1622float2(p[3]);
+    hi = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
+  }
+  reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
 }
 
 // ---- out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ) ----
@@ -276,7 +273,7 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
   BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant: M=%d D=%d K=%d", M, D, K);
   BWMOE_REQUIRE(x && row_slot && row_expert && scales && xq, BWMOE_ERR_NULL, "gather_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant: pointers must be 16-byte aligned");
-  quant_rows_kernel<true><<<ceil_div(M, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot,
+  quant_rows_kernel<true><<<(unsigned)(((size_t)M * (D / 8) + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot,
                                                           row_expert, scales, M, D, K,
                                                           static_cast<uint8_t*>(xq));
   BWMOE_CUDA_OK(cudaGetLastError());
@@ -288,7 +285,7 @@ int launch_requant(const void* h, const int32_t* row_expert, const float* scales
   BWMOE_REQUIRE(M > 0 && H > 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "requant: M=%d H=%d", M, H);
   BWMOE_REQUIRE(h && row_expert && scales_h && hq, BWMOE_ERR_NULL, "requant: null pointer");
   BWMOE_REQUIRE(aligned16(h) && aligned16(hq), BWMOE_ERR_BAD_ALIGN, "requant: pointers must be 16-byte aligned");
-  quant_rows_kernel<false><<<ceil_div(M, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
+  quant_rows_kernel<false><<<(unsigned)(((size_t)M * (H / 8) + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
                                                            row_expert, scales_h, M, H, 1,
                                                            static_cast<uint8_t*>(hq));
   BWMOE_CUDA_OK(cudaGetLastError());

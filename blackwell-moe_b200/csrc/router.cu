@@ -5,11 +5,13 @@
 // src/blackwell_moe/kernels/fp8_moe_v3.py:34-37.
 //
 // Selection target: the exact dot products x[t,:].w_gate[:,e] rounded once to fp32,
-// ordered by (value descending, expert id ascending).  The kernel accumulates in
-// fp32 with a two-level blocked sum whose worst-case error is known, and re-evaluates
-// in fp64 only the tokens for which two neighbouring logits among ranks 1..K+1 are
-// closer than that error bound, so the chosen experts and their order equal the
-// exactly-rounded ones for every token.
+// ordered by (value descending, expert id ascending).  bf16 x bf16 products are exact in
+// fp32, so the only error of an fp32 evaluation is in the additions.  The kernel sums
+// blocks of 16 products with plain FMAs and adds the blocks with compensated (Kahan)
+// summation, which bounds the error of a logit by about 20 * 2^-24 * sum|x_d * w_de|.
+// Tokens for which two neighbouring logits among ranks 1..K+1 are closer than twice that
+// bound are re-evaluated in fp64 by the whole block, so the chosen experts and their
+// order equal the exactly-rounded ones for every token.
 #include "common.cuh"
 
 namespace bwmoe {
@@ -17,7 +19,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kChunk = 256;   // D elements staged per step
-constexpr int kInner = 32;    // terms per first-level partial sum
+constexpr int kInner = 16;    // products per plain-FMA block
 constexpr int kMaxEJ = 8;     // E <= 32 * kMaxEJ
 
 struct Cand {
@@ -29,17 +31,246 @@ __device__ __forceinline__ bool ahead(const Cand& a, const Cand& b) {
   return a.v > b.v || (a.v == b.v && a.i < b.i);
 }
 
+// Kahan step: (sum, comp) += y.  Kept out of reach of re-association by the intrinsics.
+__device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
+  const float yc = __fsub_rn(y, comp);
+  const float t = __fadd_rn(sum, yc);
+  comp = __fsub_rn(__fsub_rn(t, sum), yc);
+  sum = t;
+}
+
+// Top-K (+1) selection of one token by one warp.  Writes weights/indices; returns true when
+// two neighbouring selected logits (or the K-th and the best rejected one) are within thr.
+__device__ __forceinline__ bool select_token(const float* lg_row, int E, int K, float thr_rel, float thr_abs,
+                                             float* w_out, int32_t* i_out, int lane) {
+  float v[kMaxEJ];
+  float lmax = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxEJ; ++j) {
+    const int ee = lane + 32 * j;
+    v[j] = ee < E ? lg_row[ee] : -INFINITY;
+    if (ee < E) lmax = fmaxf(lmax, fabsf(v[j]));
+  }
+  for (int off = 16; off; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+  const float thr = thr_abs + lmax * thr_rel;
+  unsigned taken = 0;
+  bool ambiguous = false;
+  float prev = 0.f;
+  Cand chosen = {0.f, 0};   // lane i keeps the i-th selected (value, id)
+  const int rounds = K < E ? K + 1 : K;
+  for (int it = 0; it < rounds; ++it) {
+    Cand best = {-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int j = 0; j < kMaxEJ; ++j) {
+      const Cand c = {v[j], lane + 32 * j};
+      if (!((taken >> j) & 1u) && lane + 32 * j < E && ahead(c, best)) best = c;
+    }
+    for (int off = 16; off; off >>= 1) {
+      const Cand o = {__shfl_xor_sync(0xffffffffu, best.v, off), __shfl_xor_sync(0xffffffffu, best.i, off)};
+      if (ahead(o, best)) best = o;
+    }
+    if ((best.i & 31) == lane) taken |= 1u << (best.i >> 5);
+    if (it > 0 && prev - best.v <= thr) ambiguous = true;
+    prev = best.v;
+    if (it < K && lane == it) chosen = best;
+  }
+  // weights: softmax over the selected logits == softmax over all experts, renormalised
+  const float top = __shfl_sync(0xffffffffu, chosen.v, 0);
+  const float p = lane < K ? expf(chosen.v - top) : 0.f;
+  float z = p;
+  for (int off = 16; off; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
+  if (lane < K) {
+    w_out[lane] = p / z;
+    i_out[lane] = chosen.i;
+  }
+  return ambiguous;
+}
+
+// Exact logits of one token in fp64 by the whole block, then rounded once to fp32.
+// Threads are laid out as (expert octet ev, d-group dg): each loads 8 gate weights (16 bytes)
+// per d.  Needs E % 8 == 0 and w_gate 16-byte aligned; otherwise one expert per thread.
+// The partial sums are combined in a fixed order (shuffle tree, then warp by warp).
+__device__ void exact_logits_block(const __nv_bfloat16* __restrict__ xrow, const __nv_bfloat16* __restrict__ wg,
+                                   int D, int E, float* lg_row, double* dsum /* smem [E] */) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  const bool vec = (E % 8 == 0) && (E / 8 <= 32) && ((reinterpret_cast<uintptr_t>(wg) & 15u) == 0);
+  for (int i = tid; i < E; i += nthreads) dsum[i] = 0.0;
+  __syncthreads();
+  if (vec) {
+    int V = 1;
+    while (V < E / 8) V <<= 1;                 // lanes per d, padded to a power of two
+    const int ev = tid % V, dg = tid / V, NG = nthreads / V;
+    double a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = 0.0;
+    if (ev < E / 8) {
+#pragma unroll 4
+      for (int d = dg; d < D; d += NG) {
+        const double xv = (double)__bfloat162float(xrow[d]);
+        const uint4 raw = *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev);
+        const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(pw[j]);
+          a[2 * j] = fma(xv, (double)f.x, a[2 * j]);
+          a[2 * j + 1] = fma(xv, (double)f.y, a[2 * j + 1]);
+        }
+      }
+    }
+    for (int off = V; off < 32; off <<= 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += __shfl_xor_sync(0xffffffffu, a[j], off);
+    }
+    for (int w = 0; w < nthreads / 32; ++w) {
+      if (warp == w && lane < V && ev < E / 8) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dsum[8 * ev + j] += a[j];
+      }
+      __syncthreads();
+    }
+  } else {
+    int GE = 8;
+    while (GE < E) GE <<= 1;
+    if (GE > nthreads) GE = nthreads;
+    const int ee = tid % GE, dg = tid / GE, NG = nthreads / GE;
+    for (int e0 = 0; e0 < E; e0 += GE) {        // GE < E only when E > blockDim
+      double a = 0.0;
+      if (e0 + ee < E) {
+#pragma unroll 8
+        for (int d = dg; d < D; d += NG)
+          a = fma((double)__bfloat162float(xrow[d]), (double)__bfloat162float(wg[(size_t)d * E + e0 + ee]), a);
+      }
+      for (int g = 0; g < NG; ++g) {
+        if (dg == g && e0 + ee < E) dsum[e0 + ee] += a;
+        __syncthreads();
+      }
+    }
+  }
+  for (int i = tid; i < E; i += nthreads) lg_row[i] = (float)dsum[i];
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------------------
+// One block per token: threads = (expert octet, d-group).  Used when the gate is narrow
+// (E <= 16: the whole w_gate stays in L1) or the batch is small (decode), where tiling
+// tokens buys nothing and what matters is many loads in flight.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
+                    int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
+                    float* __restrict__ row_amax) {
+  __shared__ float part[32][256];     // per-warp partial logits
+  __shared__ float lg[256];
+  __shared__ double dsum[256];
+  __shared__ float s_stat[3][32];
+  __shared__ int s_amb;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int tok = blockIdx.x;
+  const __nv_bfloat16* xrow = x + (size_t)tok * D;
+  int V = 1;
+  while (V < E / 8) V <<= 1;
+  const int ev = tid % V, dg = tid / V, NG = blockDim.x / V;
+  const bool ev_ok = ev < E / 8;
+
+  float acc[8], comp[8], inner[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f, comp[j] = 0.f, inner[j] = 0.f;
+  float wmax = 0.f, xabs = 0.f, xmax = 0.f;
+  int inner_n = 0;
+#pragma unroll 4
+  for (int d = dg; d < D; d += NG) {
+    const float xv = __bfloat162float(xrow[d]);
+    if (ev == 0) {
+      xabs += fabsf(xv);
+      xmax = fmaxf(xmax, fabsf(xv));
+    }
+    if (ev_ok) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev);
+      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(pw[j]);
+        wmax = fmaxf(wmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        inner[2 * j] = fmaf(xv, f.x, inner[2 * j]);
+        inner[2 * j + 1] = fmaf(xv, f.y, inner[2 * j + 1]);
+      }
+    }
+    if (++inner_n == kInner) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        kahan_add(acc[j], comp[j], inner[j]);
+        inner[j] = 0.f;
+      }
+      inner_n = 0;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    kahan_add(acc[j], comp[j], inner[j]);
+    acc[j] = __fsub_rn(acc[j], comp[j]);
+  }
+  // d-groups inside the warp: plain shuffle tree (at most 5 roundings per logit)
+  for (int off = V; off < 32; off <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  }
+  if (lane < V && ev_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part[warp][8 * ev + j] = acc[j];
+  }
+  for (int off = 16; off; off >>= 1) {
+    xabs += __shfl_xor_sync(0xffffffffu, xabs, off);
+    xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
+    wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, off));
+  }
+  if (lane == 0) s_stat[0][warp] = xabs, s_stat[1][warp] = xmax, s_stat[2][warp] = wmax;
+  __syncthreads();
+  // warps: compensated sum in a fixed order
+  for (int e = tid; e < E; e += blockDim.x) {
+    float sm = 0.f, c = 0.f;
+    for (int w = 0; w < nwarps; ++w) kahan_add(sm, c, part[w][e]);
+    lg[e] = __fsub_rn(sm, c);
+  }
+  float a_tok = 0.f, m_tok = 0.f, w_all = 0.f;
+  for (int w = 0; w < nwarps; ++w) {
+    a_tok += s_stat[0][w];
+    m_tok = fmaxf(m_tok, s_stat[1][w]);
+    w_all = fmaxf(w_all, s_stat[2][w]);
+  }
+  __syncthreads();
+  // blocks of kInner FMAs + compensated outer sum (2) + in-warp tree (<=5) + compensated warp sum (2)
+  const float gamma = (float)(kInner + 10) * 5.9604645e-8f * 1.05f;
+  if (warp == 0) {
+    const bool amb = select_token(lg, E, K, 1.0e-6f, 2.f * gamma * w_all * a_tok, weights + (size_t)tok * K,
+                                  indices + (size_t)tok * K, lane);
+    if (lane == 0) {
+      s_amb = amb ? 1 : 0;
+      if (row_amax != nullptr) row_amax[tok] = m_tok;
+    }
+  }
+  __syncthreads();
+  if (!s_amb) return;
+  exact_logits_block(xrow, wg, D, E, lg, dsum);
+  if (warp == 0)
+    select_token(lg, E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, lane);
+}
+
 template <int TOK>
 __global__ void __launch_bounds__(kThreads)
 router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
               int E, int K, int Epad, float* __restrict__ weights, int32_t* __restrict__ indices,
               float* __restrict__ row_amax) {
-  // xs: staged activations [kChunk][TOK] fp32; reused afterwards for the cross-slice reduction
-  __shared__ __align__(16) float xs[kChunk * TOK > kThreads * TOK ? kChunk * TOK : kThreads * TOK];
+  // xs: staged activations [kChunk][TOK] fp32; later reused for the cross-slice reduction
+  // and (as doubles) for the fp64 partial sums
+  __shared__ __align__(16) float xs[kThreads * TOK];
   __shared__ float lg[TOK][256];
   __shared__ float s_abs[TOK], s_max[TOK];
   __shared__ float s_red[kThreads / 32][TOK], s_red2[kThreads / 32][TOK];
   __shared__ float s_wmax[kThreads / 32];
+  __shared__ int s_flag[TOK];
+  __shared__ int s_nflag;
+  static_assert(kChunk == kThreads, "xs is sized for both uses");
+  static_assert(kThreads * TOK * sizeof(float) >= kThreads * sizeof(double), "fp64 partials fit in xs");
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok0 = blockIdx.x * TOK;
@@ -47,18 +278,19 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const int e = tid % Epad, ds = tid / Epad;
   const bool e_ok = e < E;
   const bool vec_ok = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+  if (tid == 0) s_nflag = 0;
 
-  float acc[TOK], inner[TOK];
+  float acc[TOK], comp[TOK], inner[TOK];
 #pragma unroll
-  for (int t = 0; t < TOK; ++t) acc[t] = 0.f, inner[t] = 0.f;
-  float wmax = 0.f, my_abs = 0.f, my_max = 0.f;   // staging-side statistics of x
+  for (int t = 0; t < TOK; ++t) acc[t] = 0.f, comp[t] = 0.f, inner[t] = 0.f;
+  float wmax = 0.f, my_abs = 0.f, my_max = 0.f;   // statistics gathered while staging / streaming
   int inner_n = 0;
 
   for (int c0 = 0; c0 < D; c0 += kChunk) {
     // stage x[tok0..tok0+TOK, c0..c0+kChunk) transposed to [d][token]; a thread always serves
     // token tid % TOK, so its running |x| statistics belong to one token
     if (vec_ok) {
-      // 16-byte loads: lanes run over tokens, each taking 8 consecutive d; two lanes share a 32-byte sector
+      // 16-byte loads: lanes run over tokens, each taking 8 consecutive d
       for (int idx = tid; idx < (kChunk / 8) * TOK; idx += kThreads) {
         const int t = idx % TOK, dd0 = (idx / TOK) * 8;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
@@ -86,6 +318,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
     }
     __syncthreads();
     const int dlim = min(kChunk, D - c0);
+#pragma unroll 4
     for (int dd = ds; dd < dlim; dd += DS) {
       float w = 0.f;
       if (e_ok) w = __bfloat162float(wg[(size_t)(c0 + dd) * E + e]);
@@ -106,30 +339,34 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
       }
       if (++inner_n == kInner) {
 #pragma unroll
-        for (int t = 0; t < TOK; ++t) acc[t] += inner[t], inner[t] = 0.f;
+        for (int t = 0; t < TOK; ++t) {
+          kahan_add(acc[t], comp[t], inner[t]);
+          inner[t] = 0.f;
+        }
         inner_n = 0;
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int t = 0; t < TOK; ++t) acc[t] += inner[t];
+  for (int t = 0; t < TOK; ++t) {
+    kahan_add(acc[t], comp[t], inner[t]);
+    acc[t] = __fsub_rn(acc[t], comp[t]);
+  }
 
-  // ---- cross-slice reduction (fixed order), logits into lg[t][e] ----
+  // ---- cross-slice reduction (fixed order, compensated), logits into lg[t][e] ----
 #pragma unroll
   for (int t = 0; t < TOK; ++t) xs[(ds * TOK + t) * Epad + e] = acc[t];
-  // statistics: |x| sums and maxima per token; max |w_gate|
   {
-    // thread's staged elements all belong to token tid % TOK; lanes l and l+TOK (if TOK<32) share it
+    // |x| sums and maxima per token (lanes l, l+TOK, ... of a warp serve the same token); max |w_gate|
     float a = my_abs, m = my_max;
     for (int off = TOK; off < 32; off <<= 1) {
       a += __shfl_xor_sync(0xffffffffu, a, off);
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
     }
-    if (TOK >= 32 ? true : lane < TOK) {
-      // TOK <= 32 is guaranteed by the launcher
-      s_red[warp][lane % TOK] = a;
-      s_red2[warp][lane % TOK] = m;
+    if (lane < TOK) {
+      s_red[warp][lane] = a;
+      s_red2[warp][lane] = m;
     }
     float wm = wmax;
     for (int off = 16; off; off >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, off));
@@ -138,9 +375,9 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   __syncthreads();
   for (int idx = tid; idx < TOK * Epad; idx += kThreads) {
     const int t = idx / Epad, ee = idx % Epad;
-    float s = 0.f;
-    for (int q = 0; q < DS; ++q) s += xs[(q * TOK + t) * Epad + ee];
-    lg[t][ee] = s;
+    float s = 0.f, c = 0.f;
+    for (int q = 0; q < DS; ++q) kahan_add(s, c, xs[(q * TOK + t) * Epad + ee]);
+    lg[t][ee] = __fsub_rn(s, c);
   }
   if (tid < TOK) {
     float a = 0.f, m = 0.f;
@@ -152,84 +389,38 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   float wm_all = 0.f;
   for (int w = 0; w < kThreads / 32; ++w) wm_all = fmaxf(wm_all, s_wmax[w]);
 
-  // worst-case bound of the blocked fp32 sum: (inner terms + outer blocks + slices) * 2^-24
-  const int per_thread = (D + DS - 1) / DS;
-  const float gamma = (float)(kInner + 8 + (per_thread + kInner - 1) / kInner + DS) * 5.9604645e-8f * 1.02f;
+  // error of one logit <= (kInner + 4) * 2^-24 * sum|x_d w_de|  (plain-FMA blocks; the compensated
+  // additions contribute ~2 ulp of the result, covered by the relative term); a pair of logits
+  // can therefore be mis-ordered only when closer than twice that
+  const float gamma = (float)(kInner + 4) * 5.9604645e-8f * 1.05f;
+  const float thr_rel = 1.0e-6f;   // ~8 ulp of the larger logit: final roundings + fp32 ties after rounding
 
-  // ---- selection: one warp per token ----
+  // ---- selection pass 1: one warp per token ----
   for (int t = warp; t < TOK; t += kThreads / 32) {
     if (tok0 + t >= T) continue;
     const size_t tok = tok0 + t;
-    bool exact = false;
-    Cand chosen = {0.f, 0};     // lane i keeps the i-th selected (value, id)
-    float vals_next = 0.f;
-    for (int pass = 0; pass < 2; ++pass) {
-      float v[kMaxEJ];
-      float lmax = 0.f;
-#pragma unroll
-      for (int j = 0; j < kMaxEJ; ++j) {
-        const int ee = lane + 32 * j;
-        v[j] = ee < E ? lg[t][ee] : -INFINITY;
-        if (ee < E) lmax = fmaxf(lmax, fabsf(v[j]));
-      }
-      for (int off = 16; off; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
-      const float thr = 2.f * gamma * wm_all * s_abs[t] + lmax * 4.8e-7f;
-      unsigned taken = 0;
-      bool ambiguous = false;
-      float prev = 0.f;
-      const int rounds = K < E ? K + 1 : K;
-      for (int it = 0; it < rounds; ++it) {
-        Cand best = {-INFINITY, 0x7fffffff};
-#pragma unroll
-        for (int j = 0; j < kMaxEJ; ++j) {
-          Cand c = {v[j], lane + 32 * j};
-          if (!((taken >> j) & 1u) && lane + 32 * j < E && ahead(c, best)) best = c;
-        }
-        for (int off = 16; off; off >>= 1) {
-          Cand o = {__shfl_xor_sync(0xffffffffu, best.v, off), __shfl_xor_sync(0xffffffffu, best.i, off)};
-          if (ahead(o, best)) best = o;
-        }
-        if ((best.i & 31) == lane) taken |= 1u << (best.i >> 5);
-        if (it > 0 && prev - best.v <= thr) ambiguous = true;
-        prev = best.v;
-        if (it < K) {
-          if (lane == it) chosen = best;
-        } else {
-          vals_next = best.v;
-        }
-      }
-      (void)vals_next;
-      if (!ambiguous || exact) break;
-      // near-tie: exact fp64 logits for this token, lanes over experts
-      double accd[kMaxEJ];
-#pragma unroll
-      for (int j = 0; j < kMaxEJ; ++j) accd[j] = 0.0;
-      for (int d = 0; d < D; ++d) {
-        const double xv = (double)__bfloat162float(x[tok * D + d]);
-#pragma unroll
-        for (int j = 0; j < kMaxEJ; ++j) {
-          const int ee = lane + 32 * j;
-          if (ee < E) accd[j] = fma(xv, (double)__bfloat162float(wg[(size_t)d * E + ee]), accd[j]);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kMaxEJ; ++j) {
-        const int ee = lane + 32 * j;
-        if (ee < E) lg[t][ee] = (float)accd[j];
-      }
-      __syncwarp();
-      exact = true;
+    const float thr_abs = 2.f * gamma * wm_all * s_abs[t];
+    const bool amb = select_token(lg[t], E, K, thr_rel, thr_abs, weights + tok * K, indices + tok * K, lane);
+    if (lane == 0) {
+      if (row_amax != nullptr) row_amax[tok] = s_max[t];
+      if (amb) s_flag[atomicAdd(&s_nflag, 1)] = t;
     }
-    // weights: softmax over the selected logits == softmax over all, renormalised
-    const float top = __shfl_sync(0xffffffffu, chosen.v, 0);
-    float p = lane < K ? expf(chosen.v - top) : 0.f;
-    float z = p;
-    for (int off = 16; off; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
-    if (lane < K) {
-      weights[tok * K + lane] = p / z;
-      indices[tok * K + lane] = chosen.i;
-    }
-    if (row_amax != nullptr && lane == 0) row_amax[tok] = s_max[t];
+  }
+  __syncthreads();
+  const int nflag = s_nflag;
+  if (nflag == 0) return;
+
+  // ---- near-ties: exact fp64 logits, whole block per flagged token ----
+  double* dsum = reinterpret_cast<double*>(xs);          // [E] doubles; xs is free by now
+  for (int f = 0; f < nflag; ++f) {
+    const int t = s_flag[f];
+    exact_logits_block(x + (size_t)(tok0 + t) * D, wg, D, E, lg[t], dsum);
+  }
+  // ---- selection pass 2 on the exact logits ----
+  for (int f = warp; f < nflag; f += kThreads / 32) {
+    const int t = s_flag[f];
+    const size_t tok = tok0 + t;
+    select_token(lg[t], E, K, 0.f, -1.f, weights + tok * K, indices + tok * K, lane);
   }
 }
 
@@ -245,7 +436,11 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
   while (Epad < E) Epad <<= 1;
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(wg);
-  if (T >= 2048) {
+  const bool vec_gate = (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) & 15u) == 0);
+  if (vec_gate && (E <= 16 || T < 1024)) {
+    const int threads = E >= 128 ? 1024 : 256;
+    router_token_kernel<<<T, threads, 0, st>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
+  } else if (T >= 2048) {
     constexpr int TOK = 16;
     router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, st>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
   } else {
