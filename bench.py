@@ -33,7 +33,14 @@ WORKLOADS = {
     "deepseek-v2-lite": (2048, 1408, 64, 6, 4096),
     "toy": (1024, 2048, 16, 2, 256),
 }
-KERNELS_PER_FORWARD = 11  # router, 3 plan, 2 segment-scale, gather-quant, gate/up GEMM, requant, down GEMM, combine
+
+
+def kernels_per_forward(M: int) -> int:
+    """Kernels of ours launched by one single-GPU forward of M = T*K permuted rows."""
+    if M > 1024:   # router, 3 plan passes, segment scales, gather+quant, gate/up GEMM, requant, down GEMM, combine
+        return 10
+    n = 7          # router, one-block plan, gather+quant, gate/up GEMM, requant, down GEMM, combine
+    return n + 2 if M <= 64 else n   # split-K adds one fixed-order summation pass behind each GEMM
 
 
 def parse():
@@ -273,7 +280,7 @@ def run_ours(args):
             _lib.check(lib.bwmoe_workspace_view(ws.data_ptr(), T, D, H, E, K, sel, C.byref(p), C.byref(n)))
             return p.value
         amax_h = torch.zeros(E, device=dev, dtype=torch.float32)
-        scratch = torch.empty(max(256, lib.bwmoe_gemm_scratch_bytes(M, E)), device=dev, dtype=torch.uint8)
+        scratch = torch.empty(max(256, lib.bwmoe_gemm_scratch_bytes(M, D, H, E)), device=dev, dtype=torch.uint8)
 
         def gateup():
             _lib.check(lib.bwmoe_gateup_swiglu(view(8), view(1), view(6), W["q_gate"].data_ptr(), W["q_up"].data_ptr(),
@@ -313,7 +320,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (weights %.0f MB per step)" % (3.0 * E * D * H / world / 1e6)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 2 * world,
                 "d2h_bytes_per_step": T * D * 2 * world, "ms_per_step": e2e_secs / args.steps * 1e3},
-        "gpu_launches": KERNELS_PER_FORWARD * args.steps,
+        "gpu_launches": kernels_per_forward(T * K) * args.steps,
         "clocks": clocks.summary(),
     }
     if roofline is not None:

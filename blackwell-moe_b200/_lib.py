@@ -43,7 +43,7 @@ SIGNATURES = {
     "bwmoe_permute_plan_static": (_i, [_ip, _fp, _i, _i, _i, _ip, _ip, _ip, _ip, _fp, _ip, _vp]),
     "bwmoe_segment_scales": (_i, [_fp, _ip, _i, _fp, _vp]),
     "bwmoe_gather_quant": (_i, [_vp, _ip, _ip, _fp, _i, _i, _i, _vp, _vp]),
-    "bwmoe_gemm_scratch_bytes": (_sz, [_i] * 2),
+    "bwmoe_gemm_scratch_bytes": (_sz, [_i] * 4),
     "bwmoe_gateup_swiglu": (_i, [_vp, _ip, _fp, _vp, _vp, _fp, _fp, _i, _i, _i, _i, _vp, _fp, _ip, _vp, _vp]),
     "bwmoe_requant": (_i, [_vp, _ip, _fp, _i, _i, _vp, _vp]),
     "bwmoe_down": (_i, [_vp, _ip, _fp, _vp, _fp, _i, _i, _i, _i, _vp, _ip, _vp, _vp]),

@@ -70,7 +70,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   L->row_slot = take(sizeof(int32_t) * M);
   L->row_expert = take(sizeof(int32_t) * M);
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
-  L->gemm_scratch = take(gemm_scratch_bytes((int)M, E));
+  L->gemm_scratch = take(gemm_scratch_bytes((int)M, D, H, E));
   L->xq = take(M * D);
   L->h = take(M * H * 2);
   L->hq = take(M * H);
@@ -119,15 +119,14 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   float* scale_h = at<float>(ws, L.scale_h);
   int rc;
   if ((rc = launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, amax_x, status,
-                        at<void>(ws, L.plan_scratch), st)))
+                        at<void>(ws, L.plan_scratch), st, scale_x)))
     return rc;
-  if ((rc = launch_segment_scales(amax_x, offsets, E, scale_x, st))) return rc;
   if ((rc = launch_gather_quant(x, row_slot, row_expert, scale_x, M, D, K, at<void>(ws, L.xq), st))) return rc;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
                           amax_h, status, at<void>(ws, L.gemm_scratch), st)))
     return rc;
-  if ((rc = launch_segment_scales(amax_h, offsets, E, scale_h, st))) return rc;
-  if ((rc = launch_requant(at<void>(ws, L.h), row_expert, scale_h, M, H, at<void>(ws, L.hq), st))) return rc;
+  // scale_h is derived from amax_h inside the requantisation kernel
+  if ((rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h))) return rc;
   if ((rc = launch_down(at<void>(ws, L.hq), offsets, scale_h, wd, sd, M, D, H, E, at<void>(ws, L.y), status,
                         at<void>(ws, L.gemm_scratch), st)))
     return rc;
@@ -304,9 +303,9 @@ int bwmoe_gather_quant(const void* x, const int32_t* row_slot, const int32_t* ro
   return launch_gather_quant(x, row_slot, row_expert, scales, M, D, K, xq, static_cast<cudaStream_t>(stream));
 }
 
-size_t bwmoe_gemm_scratch_bytes(int M, int E) {
-  if (M <= 0 || E <= 0) return 0;
-  return gemm_scratch_bytes(M, E);
+size_t bwmoe_gemm_scratch_bytes(int M, int D, int H, int E) {
+  if (M <= 0 || D <= 0 || H <= 0 || E <= 0) return 0;
+  return gemm_scratch_bytes(M, D, H, E);
 }
 
 int bwmoe_gateup_swiglu(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,

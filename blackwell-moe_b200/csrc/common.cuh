@@ -63,7 +63,7 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
 size_t plan_scratch_bytes(int T, int E, int K);
 int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
                 int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
-                void* scratch, cudaStream_t st);
+                void* scratch, cudaStream_t st, float* scales_out = nullptr);
 int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
                        int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
                        cudaStream_t st);
@@ -72,10 +72,10 @@ int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, 
 int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert,
                         const float* scales, int M, int D, int K, void* xq, cudaStream_t st);
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
-                   void* hq, cudaStream_t st);
+                   void* hq, cudaStream_t st, float* scales_from_amax_out = nullptr);
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
                    void* out, cudaStream_t st);
-size_t gemm_scratch_bytes(int M, int E);
+size_t gemm_scratch_bytes(int M, int D, int H, int E);
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
                   int32_t* status, void* scratch, cudaStream_t st);

@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -59,6 +60,10 @@ struct GemmParams {
   float* seg_amax;          // GATE_UP: [E] amax of h per segment
   int32_t* status;
   int E, Kdim, N_out, n_tiles;
+  // split-K mode (RAW kernels): every tile covers `k_per_split` K blocks and dumps its fp32
+  // accumulators into slab `split` of `partial` ([split_k][M][ldp] floats) for a later fixed-order sum
+  int split_k, k_per_split, M, ldp;
+  float* partial;
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -174,13 +179,15 @@ struct TileCursor {
   const int* cum;       // smem [E+1]: tiles before expert e
   const int32_t* offsets;
   int E, n_tiles, e;
-  __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx) {
+  __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx, int& split) {
     while (e < E && tile >= cum[e + 1]) ++e;
     if (e >= E) return false;
     const int seg0 = offsets[e], seg1 = offsets[e + 1];
     const int m_tiles = (seg1 - seg0 + BM - 1) / BM;
     const int within = tile - cum[e];
-    n_idx = within / m_tiles;
+    const int rest = within / m_tiles;
+    n_idx = rest % n_tiles;
+    split = rest / n_tiles;
     row0 = seg0 + (within % m_tiles) * BM;
     row_end = seg1;
     expert = e;
@@ -190,7 +197,7 @@ struct TileCursor {
 
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
-template <bool GATE_UP>
+template <bool GATE_UP, bool RAW>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
@@ -208,15 +215,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   volatile int* abort_flag = &s_abort;
 
   // ---- set-up ----
+  // tiles before each expert: every thread fetches the segments it owns, warp 0 scans
+  for (int e = threadIdx.x; e < 256; e += NUM_THREADS) {
+    int t = 0;
+    if (e < p.E) {
+      const int rows = p.offsets[e + 1] - p.offsets[e];
+      t = ((rows + BM - 1) / BM) * p.n_tiles * p.split_k;
+    }
+    s_cum[e + 1] = t;
+  }
   if (threadIdx.x == 0) {
     s_abort = 0;
-    int run = 0;
-    for (int e = 0; e < p.E; ++e) {
-      s_cum[e] = run;
-      const int rows = p.offsets[e + 1] - p.offsets[e];
-      run += ((rows + BM - 1) / BM) * p.n_tiles;
-    }
-    s_cum[p.E] = run;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
@@ -226,6 +235,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(bar_tempty + 8 * b, 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // inclusive scan of s_cum[1..256]: 8 values per lane, then a shuffle scan of the lane totals
+    int v[8], run = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      run += s_cum[1 + lane * 8 + j];
+      v[j] = run;
+    }
+    int incl = run;
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    const int base = incl - run;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_cum[1 + lane * 8 + j] = base + v[j];
+    if (lane == 0) s_cum[0] = 0;
   }
   if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
   tc_fence_before();
@@ -242,10 +270,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        int e, row0, row_end, n_idx;
-        if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+        int e, row0, row_end, n_idx, split;
+        if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
         const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb0 = split * p.k_per_split, kb1 = min(k_blocks, kb0 + p.k_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status))) break;
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
           const uint32_t full = bar_full + 8 * stage;
@@ -263,13 +292,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
+      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+        int e, row0, row_end, n_idx, split;
+        if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
+        const int kb0 = split * p.k_per_split, kb1 = min(k_blocks, kb0 + p.k_per_split);
         const uint32_t buf = local & 1u, use = local >> 1;
         // wait until the epilogue has drained this accumulator buffer (first use passes at once)
         if (!(ok = mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -277,7 +310,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // A: +32 bytes along K inside the swizzle atom; B: +32 K rows = 4096 bytes
-            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, (kb | k) != 0 ? 1u : 0u);
+            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           mma_commit(bar_empty + 8 * stage);          // frees the stage when these MMAs retire
           if (++stage == STAGES) stage = 0, phase ^= 1u;
@@ -294,8 +327,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
-      int e, row0, row_end, n_idx;
-      if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+      int e, row0, row_end, n_idx, split;
+      if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
       const uint32_t buf = local & 1u, use = local >> 1;
       ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
@@ -304,8 +337,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       const int row = row0 + r_in_tile;
       const bool row_ok = row < row_end;
-      const float sa = p.scale_a[e];
-      if constexpr (GATE_UP) {
+      if constexpr (RAW) {
+        // split-K: raw fp32 accumulators into this split's slab; GATE_UP puts the up half at column H + n
+        const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
+        float* dst_row = p.partial + ((size_t)split * p.M + row) * p.ldp;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld32(t_row + c * 32, a);
+          tmem_ld_wait();
+          int col = n0 + c * 32;
+          if (GATE_UP && c >= BN_HALF / 32) col = p.N_out + n0 + (c - BN_HALF / 32) * 32;
+          const int lim = (GATE_UP && c >= BN_HALF / 32) ? 2 * p.N_out : p.N_out;
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              if (col + v * 4 < lim)
+                reinterpret_cast<uint4*>(dst_row + col)[v] = make_uint4(a[4 * v], a[4 * v + 1], a[4 * v + 2], a[4 * v + 3]);
+            }
+          }
+        }
+      } else if constexpr (GATE_UP) {
+        const float sa = p.scale_a[e];
         const float inv_g = 1.0f / (sa * p.scale_b0[e]);
         const float inv_u = 1.0f / (sa * p.scale_b1[e]);
         const int n0 = n_idx * BN_HALF;
@@ -348,6 +401,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
         if (lane == 0 && amax > 0.f) atomic_max_nonneg(p.seg_amax + e, amax);
       } else {
+        const float sa = p.scale_a[e];
         const float inv = 1.0f / (sa * p.scale_b0[e]);
         const int n0 = n_idx * BN;
 #pragma unroll 1
@@ -436,19 +490,114 @@ int make_map_b(CUtensorMap* map, const void* base, int E, int kdim, int n) {
   return BWMOE_OK;
 }
 
-template <bool GATE_UP>
+// ---- split-K post-passes (small batches only) ---------------------------------------
+__device__ __forceinline__ int expert_of_row(const int32_t* __restrict__ offsets, int E, int row) {
+  int lo = 0, hi = E;                       // largest e with offsets[e] <= row
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// h = silu(gate) * up from the summed split-K slabs, with the same bf16 rounding points as the
+// fused epilogue, plus the per-segment amax.  One thread per (row, 4 columns).
+__global__ void __launch_bounds__(256)
+swiglu_from_partials_kernel(const float* __restrict__ partial, int S, int M, int H, const int32_t* __restrict__ offsets,
+                            int E, const float* __restrict__ sx, const float* __restrict__ sg,
+                            const float* __restrict__ su, __nv_bfloat16* __restrict__ h, float* __restrict__ seg_amax) {
+  const int vec_per_row = H / 4;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = gid < (size_t)M * vec_per_row;
+  const int m = live ? (int)(gid / vec_per_row) : 0, v = live ? (int)(gid % vec_per_row) : 0;
+  const int e = expert_of_row(offsets, E, m);
+  float amax = 0.f;
+  if (live) {
+    float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < S; ++s) {            // fixed order: deterministic
+      const float* row = partial + ((size_t)s * M + m) * (2 * H);
+      const float4 a = reinterpret_cast<const float4*>(row)[v];
+      const float4 b = reinterpret_cast<const float4*>(row + H)[v];
+      g[0] += a.x, g[1] += a.y, g[2] += a.z, g[3] += a.w;
+      u[0] += b.x, u[1] += b.y, u[2] += b.z, u[3] += b.w;
+    }
+    const float inv_g = 1.0f / (sx[e] * sg[e]), inv_u = 1.0f / (sx[e] * su[e]);
+    float hv[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float gate = bf16_round(g[q] * inv_g);
+      const float up = bf16_round(u[q] * inv_u);
+      hv[q] = bf16_round(bf16_round(silu_f(gate)) * up);
+      amax = fmaxf(amax, fabsf(hv[q]));
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(hv[0], hv[1]), hi = __floats2bfloat162_rn(hv[2], hv[3]);
+    reinterpret_cast<uint2*>(h + (size_t)m * H)[v] =
+        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+  // one atomic per warp when the whole warp works on one expert (the common case), else per thread
+  const int key = live ? e : -1;
+  const int key0 = __shfl_sync(0xffffffffu, key, 0);
+  if (__all_sync(0xffffffffu, key == key0)) {
+    float mx = amax;
+    for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((threadIdx.x & 31) == 0 && key0 >= 0 && mx > 0.f) atomic_max_nonneg(seg_amax + key0, mx);
+  } else if (live && amax > 0.f) {
+    atomic_max_nonneg(seg_amax + e, amax);
+  }
+}
+
+// y = bf16(sum of slabs * 1/(s_h * s_d)); one thread per (row, 4 columns)
+__global__ void __launch_bounds__(256)
+down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D, const int32_t* __restrict__ offsets,
+                          int E, const float* __restrict__ sh, const float* __restrict__ sd,
+                          __nv_bfloat16* __restrict__ y) {
+  const int vec_per_row = D / 4;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (size_t)M * vec_per_row) return;
+  const int m = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
+  const int e = expert_of_row(offsets, E, m);
+  float a[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < S; ++s) {
+    const float4 t = reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v];
+    a[0] += t.x, a[1] += t.y, a[2] += t.z, a[3] += t.w;
+  }
+  const float inv = 1.0f / (sh[e] * sd[e]);
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a[0] * inv, a[1] * inv), hi = __floats2bfloat162_rn(a[2] * inv, a[3] * inv);
+  reinterpret_cast<uint2*>(y + (size_t)m * D)[v] =
+      make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+// Split-K is for small batches, where a few experts x column blocks cannot occupy every SM:
+// the K loop of each tile is cut so that about four waves of tiles exist.
+constexpr int kSplitMaxRows = 64;
+constexpr int kSplitMax = 8;
+struct SplitPlan {
+  int split_k, k_per_split;
+};
+SplitPlan choose_split(int M, int E, int k_blocks, int n_tiles) {
+  SplitPlan sp{1, k_blocks};
+  if (M > kSplitMaxRows) return sp;
+  const long long tiles = (long long)std::min(M, E) * n_tiles;      // one row tile per active expert, at most
+  int S = (int)std::min<long long>(kSplitMax, (4ll * sm_count() + tiles - 1) / tiles);
+  S = std::max(1, std::min(S, k_blocks / 2));
+  sp.k_per_split = ceil_div(k_blocks, S);
+  sp.split_k = ceil_div(k_blocks, sp.k_per_split);
+  return sp;
+}
+
+template <bool GATE_UP, bool RAW>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const GemmParams& p,
                 int M, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(grouped_gemm_kernel<GATE_UP, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES);
   });
   BWMOE_CUDA_OK(attr_err);
-  const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
+  const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(sm_count(), max_tiles);
-  grouped_gemm_kernel<GATE_UP><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  grouped_gemm_kernel<GATE_UP, RAW><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -463,11 +612,14 @@ int check_common(const char* who, const void* a, const void* b, int M, int D, in
 
 }  // namespace
 
-size_t gemm_scratch_bytes(int /*M*/, int /*E*/) { return 256; }
+size_t gemm_scratch_bytes(int M, int D, int H, int /*E*/) {
+  if (M > kSplitMaxRows) return 256;
+  return (size_t)kSplitMax * M * std::max(2 * H, D) * sizeof(float) + 256;
+}
 
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
-                  int32_t* status, void* /*scratch*/, cudaStream_t st) {
+                  int32_t* status, void* scratch, cudaStream_t st) {
   BWMOE_REQUIRE(xq && offsets && sx && wg && wu && sg && su && h && amax_h && status, BWMOE_ERR_NULL,
                 "gateup: null pointer");
   if (int rc = check_common("gateup", xq, h, M, D, H, E)) return rc;
@@ -476,20 +628,40 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
   if (int rc = make_map_a(&ma, xq, M, D)) return rc;
   if (int rc = make_map_b(&mg, wg, E, D, H)) return rc;
   if (int rc = make_map_b(&mu, wu, E, D, H)) return rc;
-  GemmParams p{offsets, sx, sg, su, h, amax_h, status, E, D, H, ceil_div(H, BN_HALF)};
-  return launch_gemm<true>(ma, mg, mu, p, M, st);
+  const int k_blocks = ceil_div(D, BK), n_tiles = ceil_div(H, BN_HALF);
+  const SplitPlan sp = choose_split(M, E, k_blocks, n_tiles);
+  GemmParams p{offsets, sx, sg, su, h, amax_h, status, E, D, H, n_tiles, sp.split_k, sp.k_per_split, M, 2 * H, nullptr};
+  if (sp.split_k == 1) return launch_gemm<true, false>(ma, mg, mu, p, M, st);
+  BWMOE_REQUIRE(scratch != nullptr && aligned16(scratch), BWMOE_ERR_WORKSPACE, "gateup: scratch buffer required");
+  p.partial = static_cast<float*>(scratch);
+  if (int rc = launch_gemm<true, true>(ma, mg, mu, p, M, st)) return rc;
+  const size_t n = (size_t)M * (H / 4);
+  swiglu_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<__nv_bfloat16*>(h), amax_h);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
 }
 
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
-                int M, int D, int H, int E, void* y, int32_t* status, void* /*scratch*/, cudaStream_t st) {
+                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st) {
   BWMOE_REQUIRE(hq && offsets && sh && wd && sd && y && status, BWMOE_ERR_NULL, "down: null pointer");
   if (int rc = check_common("down", hq, y, M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(wd), BWMOE_ERR_BAD_ALIGN, "down: weights must be 16-byte aligned");
   CUtensorMap ma, mb;
   if (int rc = make_map_a(&ma, hq, M, H)) return rc;
   if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;
-  GemmParams p{offsets, sh, sd, nullptr, y, nullptr, status, E, H, D, ceil_div(D, BN)};
-  return launch_gemm<false>(ma, mb, mb, p, M, st);
+  const int k_blocks = ceil_div(H, BK), n_tiles = ceil_div(D, BN);
+  const SplitPlan sp = choose_split(M, E, k_blocks, n_tiles);
+  GemmParams p{offsets, sh, sd, nullptr, y, nullptr, status, E, H, D, n_tiles, sp.split_k, sp.k_per_split, M, D, nullptr};
+  if (sp.split_k == 1) return launch_gemm<false, false>(ma, mb, mb, p, M, st);
+  BWMOE_REQUIRE(scratch != nullptr && aligned16(scratch), BWMOE_ERR_WORKSPACE, "down: scratch buffer required");
+  p.partial = static_cast<float*>(scratch);
+  if (int rc = launch_gemm<false, true>(ma, mb, mb, p, M, st)) return rc;
+  const size_t n = (size_t)M * (D / 4);
+  down_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.partial, sp.split_k, M, D, offsets, E, sh,
+                                                                        sd, static_cast<__nv_bfloat16*>(y));
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
 }
 
 }  // namespace bwmoe

@@ -125,6 +125,66 @@ plan_rank_kernel(const int32_t* __restrict__ indices, int M, int E, const int32_
   }
 }
 
+// ---- all three passes in one block, for at most 1024 slots (decode-sized batches) ----
+// Also emits the per-segment quantisation scale when asked to (scales_out != nullptr).
+__global__ void __launch_bounds__(kPlanThreads)
+plan_small_kernel(const int32_t* __restrict__ indices, const float* __restrict__ row_amax, int M, int E, int K,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ pos, int32_t* __restrict__ row_slot,
+                  int32_t* __restrict__ row_expert, float* __restrict__ seg_amax, float* __restrict__ scales_out,
+                  int32_t* __restrict__ status) {
+  extern __shared__ int cnt[];            // [32 warps][E] per-warp counts -> exclusive prefixes
+  __shared__ int start[kMaxE + 1];
+  __shared__ unsigned int amax[kMaxE];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) cnt[i] = 0;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) amax[e] = 0u;
+  __syncthreads();
+  const int s = threadIdx.x;
+  int e = -1;
+  if (s < M) {
+    e = indices[s];
+    if (e < 0 || e >= E) {
+      atomicOr(status, BWMOE_STATUS_BAD_EXPERT);
+      e = -1;
+    } else if (row_amax != nullptr) {
+      atomicMax(&amax[e], __float_as_uint(row_amax[s / K]));
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) cnt[warp * E + e] = __popc(peers);
+  __syncthreads();
+  for (int ee = threadIdx.x; ee < E; ee += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = cnt[w * E + ee];
+      cnt[w * E + ee] = run;
+      run += c;
+    }
+    start[ee + 1] = run;                 // count of expert ee, turned into an offset below
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    start[0] = 0;
+    for (int i = 0; i < E; ++i) start[i + 1] += start[i];
+  }
+  __syncthreads();
+  for (int ee = threadIdx.x; ee <= E; ee += blockDim.x) offsets[ee] = start[ee];
+  for (int ee = threadIdx.x; ee < E; ee += blockDim.x) {
+    const float a = __uint_as_float(amax[ee]);
+    if (seg_amax != nullptr) seg_amax[ee] = a;
+    if (scales_out != nullptr) scales_out[ee] = start[ee + 1] > start[ee] ? scale_from_amax(a) : 1.0f;
+  }
+  if (e >= 0) {
+    const int p = start[e] + cnt[warp * E + e] + rank_in_warp;
+    pos[s] = p;
+    row_slot[p] = s;
+    row_expert[p] = e;
+  } else if (s < M) {
+    pos[s] = -1;
+  }
+}
+
 __global__ void segment_scales_kernel(const float* __restrict__ seg_amax, const int32_t* __restrict__ offsets,
                                       int E, float* __restrict__ scales) {
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
@@ -133,31 +193,53 @@ __global__ void segment_scales_kernel(const float* __restrict__ seg_amax, const 
   scales[e] = empty ? 1.0f : scale_from_amax(seg_amax[e]);
 }
 
-// ---- row-wise bf16 -> e4m3 with a per-row-selected scale; one thread per 8 elements ----
+// ---- row-wise bf16 -> e4m3 with a per-row-selected scale; one thread per 8 elements, one block per row chunk ----
 // SRC_BY_SLOT: source row = row_slot[m] / K (gather from token order); else source row = m.
-template <bool SRC_BY_SLOT>
+// FROM_AMAX: `scales` holds the segment amax; the scale is derived here and published to scales_out.
+constexpr int kQuantVecs = 4;   // 16-byte vectors in flight per thread
+template <bool SRC_BY_SLOT, bool FROM_AMAX>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot,
-                  const int32_t* __restrict__ row_expert, const float* __restrict__ scales, int M, int W,
-                  int K, uint8_t* __restrict__ dst) {
+                  const int32_t* __restrict__ row_expert, const float* __restrict__ scales,
+                  float* __restrict__ scales_out, int M, int W, int K, uint8_t* __restrict__ dst) {
+  // a block serves one chunk of one row: blockIdx.x = row * chunks_per_row + chunk (one uniform
+  // division); a thread converts up to kQuantVecs vectors, all loaded before the first is used
   const int vec_per_row = W / 8;
-  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gid >= (size_t)M * vec_per_row) return;
-  const int m = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
-  const float scale = scales[row_expert[m]];
+  const unsigned per_block = blockDim.x * kQuantVecs;
+  const unsigned chunks_per_row = (vec_per_row + per_block - 1) / per_block;
+  const int m = (int)(blockIdx.x / chunks_per_row);
+  const int v0 = (int)(blockIdx.x % chunks_per_row) * per_block + threadIdx.x;
+  const int expert = row_expert[m];
+  float scale = scales[expert];
+  if (FROM_AMAX) {
+    scale = scale_from_amax(scale);
+    if (v0 == 0) scales_out[expert] = scale;     // every row of the segment writes the same value
+  }
   const size_t srow = SRC_BY_SLOT ? (size_t)(row_slot[m] / K) : (size_t)m;
-  const uint4 raw = reinterpret_cast<const uint4*>(src + srow * W)[v];
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  uint32_t lo, hi;
-  {
-    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
-    lo = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
+  const uint4* in = reinterpret_cast<const uint4*>(src + srow * W);
+  uint2* out = reinterpret_cast<uint2*>(dst + (size_t)m * W);
+  uint4 raw[kQuantVecs];
+#pragma unroll
+  for (int i = 0; i < kQuantVecs; ++i) {
+    const int v = v0 + i * blockDim.x;
+    raw[i] = v < vec_per_row ? in[v] : make_uint4(0u, 0u, 0u, 0u);
   }
-  {
-    const float2 a = __bfloat1622float2(p[2]), b = __bfloat1622float2(p[3]);
-    hi = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
+#pragma unroll
+  for (int i = 0; i < kQuantVecs; ++i) {
+    const int v = v0 + i * blockDim.x;
+    if (v >= vec_per_row) break;
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    uint32_t lo, hi;
+    {
+      const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+      lo = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
+    }
+    {
+      const float2 a = __bfloat1622float2(p[2]), b = __bfloat1622float2(p[3]);
+      hi = (uint32_t)to_e4m3x2(a.x * scale, a.y * scale) | ((uint32_t)to_e4m3x2(b.x * scale, b.y * scale) << 16);
+    }
+    out[v] = make_uint2(lo, hi);
   }
-  reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
 }
 
 // ---- out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ) ----
@@ -193,6 +275,16 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
 
 }  // namespace
 
+inline int quant_block_threads(int vec_per_row) {
+  int t = 32;
+  while (t < 256 && t * kQuantVecs < vec_per_row) t <<= 1;
+  return t;
+}
+inline unsigned quant_grid(int M, int vec_per_row, int threads) {
+  const int per_block = threads * kQuantVecs;
+  return (unsigned)((size_t)M * ((vec_per_row + per_block - 1) / per_block));
+}
+
 size_t plan_scratch_bytes(int T, int E, int K) {
   const long long M = (long long)T * K;
   const long long B = (M + kSlotsPerBlock - 1) / kSlotsPerBlock;
@@ -201,13 +293,19 @@ size_t plan_scratch_bytes(int T, int E, int K) {
 
 int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
                 int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,
-                void* scratch, cudaStream_t st) {
+                void* scratch, cudaStream_t st, float* scales_out) {
   BWMOE_REQUIRE(T > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "plan: T=%d E=%d K=%d", T, E, K);
   BWMOE_REQUIRE(E <= kMaxE, BWMOE_ERR_UNSUPPORTED, "plan: E=%d > %d", E, kMaxE);
   BWMOE_REQUIRE((long long)T * K < (1ll << 31), BWMOE_ERR_UNSUPPORTED, "plan: T*K too large");
   BWMOE_REQUIRE(indices && offsets && pos && row_slot && row_expert && status && scratch, BWMOE_ERR_NULL,
                 "plan: null pointer");
   const int M = T * K;
+  if (M <= kPlanThreads) {
+    plan_small_kernel<<<1, kPlanThreads, (size_t)32 * E * sizeof(int), st>>>(
+        indices, row_amax, M, E, K, offsets, pos, row_slot, row_expert, seg_amax, scales_out, status);
+    BWMOE_CUDA_OK(cudaGetLastError());
+    return BWMOE_OK;
+  }
   const int B = ceil_div(M, kSlotsPerBlock);
   int32_t* block_hist = static_cast<int32_t*>(scratch);
   if (seg_amax != nullptr) BWMOE_CUDA_OK(cudaMemsetAsync(seg_amax, 0, sizeof(float) * E, st));
@@ -217,6 +315,7 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
   const size_t smem = (size_t)33 * E * sizeof(int);
   plan_rank_kernel<<<B, kPlanThreads, smem, st>>>(indices, M, E, block_hist, pos, row_slot, row_expert);
   BWMOE_CUDA_OK(cudaGetLastError());
+  if (scales_out != nullptr) return launch_segment_scales(seg_amax, offsets, E, scales_out, st);
   return BWMOE_OK;
 }
 
@@ -256,7 +355,8 @@ int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int
   }
   // Nothing in the array has to start at zero: the histogram pass overwrites every entry
   // the later passes read (blocks 0..B-1 x experts 0..E-1) before they read it.
-  return launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, seg_amax, status, scratch, st);
+  return launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, seg_amax, status, scratch, st,
+                     nullptr);
 }
 
 int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,
@@ -273,21 +373,27 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
   BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant: M=%d D=%d K=%d", M, D, K);
   BWMOE_REQUIRE(x && row_slot && row_expert && scales && xq, BWMOE_ERR_NULL, "gather_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant: pointers must be 16-byte aligned");
-  quant_rows_kernel<true><<<(unsigned)(((size_t)M * (D / 8) + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot,
-                                                          row_expert, scales, M, D, K,
-                                                          static_cast<uint8_t*>(xq));
+  const int threads = quant_block_threads(D / 8);
+  quant_rows_kernel<true, false><<<quant_grid(M, D / 8, threads), threads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), row_slot, row_expert, scales, nullptr, M, D, K, static_cast<uint8_t*>(xq));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
 
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
-                   void* hq, cudaStream_t st) {
+                   void* hq, cudaStream_t st, float* scales_from_amax_out) {
   BWMOE_REQUIRE(M > 0 && H > 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "requant: M=%d H=%d", M, H);
   BWMOE_REQUIRE(h && row_expert && scales_h && hq, BWMOE_ERR_NULL, "requant: null pointer");
   BWMOE_REQUIRE(aligned16(h) && aligned16(hq), BWMOE_ERR_BAD_ALIGN, "requant: pointers must be 16-byte aligned");
-  quant_rows_kernel<false><<<(unsigned)(((size_t)M * (H / 8) + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
-                                                           row_expert, scales_h, M, H, 1,
-                                                           static_cast<uint8_t*>(hq));
+  const int threads = quant_block_threads(H / 8);
+  const unsigned grid = quant_grid(M, H / 8, threads);
+  if (scales_from_amax_out != nullptr)   // scales_h holds the segment amax; scales are derived and published
+    quant_rows_kernel<false, true><<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr, row_expert,
+                                                         scales_h, scales_from_amax_out, M, H, 1,
+                                                         static_cast<uint8_t*>(hq));
+  else
+    quant_rows_kernel<false, false><<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr, row_expert,
+                                                          scales_h, nullptr, M, H, 1, static_cast<uint8_t*>(hq));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

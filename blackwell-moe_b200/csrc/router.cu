@@ -163,6 +163,7 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   __shared__ float lg[256];
   __shared__ double dsum[256];
   __shared__ float s_stat[3][32];
+  __shared__ float s_wsq[256];        // squared column norms of w_gate
   __shared__ int s_amb;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int tok = blockIdx.x;
@@ -172,16 +173,18 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const int ev = tid % V, dg = tid / V, NG = blockDim.x / V;
   const bool ev_ok = ev < E / 8;
 
-  float acc[8], comp[8], inner[8];
+  float acc[8], comp[8], inner[8], wsq[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f, comp[j] = 0.f, inner[j] = 0.f;
-  float wmax = 0.f, xabs = 0.f, xmax = 0.f;
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f, comp[j] = 0.f, inner[j] = 0.f, wsq[j] = 0.f;
+  float xsq = 0.f, xmax = 0.f;
   int inner_n = 0;
+  for (int e = tid; e < 256; e += blockDim.x) s_wsq[e] = 0.f;
+  __syncthreads();
 #pragma unroll 4
   for (int d = dg; d < D; d += NG) {
     const float xv = __bfloat162float(xrow[d]);
     if (ev == 0) {
-      xabs += fabsf(xv);
+      xsq = fmaf(xv, xv, xsq);
       xmax = fmaxf(xmax, fabsf(xv));
     }
     if (ev_ok) {
@@ -190,7 +193,8 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(pw[j]);
-        wmax = fmaxf(wmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        wsq[2 * j] = fmaf(f.x, f.x, wsq[2 * j]);
+        wsq[2 * j + 1] = fmaf(f.y, f.y, wsq[2 * j + 1]);
         inner[2 * j] = fmaf(xv, f.x, inner[2 * j]);
         inner[2 * j + 1] = fmaf(xv, f.y, inner[2 * j + 1]);
       }
@@ -212,18 +216,23 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   // d-groups inside the warp: plain shuffle tree (at most 5 roundings per logit)
   for (int off = V; off < 32; off <<= 1) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+    for (int j = 0; j < 8; ++j) {
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+      wsq[j] += __shfl_xor_sync(0xffffffffu, wsq[j], off);
+    }
   }
   if (lane < V && ev_ok) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) part[warp][8 * ev + j] = acc[j];
+    for (int j = 0; j < 8; ++j) {
+      part[warp][8 * ev + j] = acc[j];
+      atomicAdd(&s_wsq[8 * ev + j], wsq[j]);     // only feeds the tie threshold: order does not matter
+    }
   }
   for (int off = 16; off; off >>= 1) {
-    xabs += __shfl_xor_sync(0xffffffffu, xabs, off);
+    xsq += __shfl_xor_sync(0xffffffffu, xsq, off);
     xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
-    wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, off));
   }
-  if (lane == 0) s_stat[0][warp] = xabs, s_stat[1][warp] = xmax, s_stat[2][warp] = wmax;
+  if (lane == 0) s_stat[0][warp] = xsq, s_stat[1][warp] = xmax;
   __syncthreads();
   // warps: compensated sum in a fixed order
   for (int e = tid; e < E; e += blockDim.x) {
@@ -231,17 +240,19 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     for (int w = 0; w < nwarps; ++w) kahan_add(sm, c, part[w][e]);
     lg[e] = __fsub_rn(sm, c);
   }
-  float a_tok = 0.f, m_tok = 0.f, w_all = 0.f;
+  float x_sq = 0.f, m_tok = 0.f, w_sq = 0.f;
   for (int w = 0; w < nwarps; ++w) {
-    a_tok += s_stat[0][w];
+    x_sq += s_stat[0][w];
     m_tok = fmaxf(m_tok, s_stat[1][w]);
-    w_all = fmaxf(w_all, s_stat[2][w]);
   }
+  for (int e = 0; e < E; ++e) w_sq = fmaxf(w_sq, s_wsq[e]);
+  // Cauchy-Schwarz: sum_d |x_d w_de| <= |x|_2 * |w_e|_2
+  const float xw_bound = sqrtf(x_sq) * sqrtf(w_sq) * 1.001f;
   __syncthreads();
   // blocks of kInner FMAs + compensated outer sum (2) + in-warp tree (<=5) + compensated warp sum (2)
   const float gamma = (float)(kInner + 10) * 5.9604645e-8f * 1.05f;
   if (warp == 0) {
-    const bool amb = select_token(lg, E, K, 1.0e-6f, 2.f * gamma * w_all * a_tok, weights + (size_t)tok * K,
+    const bool amb = select_token(lg, E, K, 1.0e-6f, 2.f * gamma * xw_bound, weights + (size_t)tok * K,
                                   indices + (size_t)tok * K, lane);
     if (lane == 0) {
       s_amb = amb ? 1 : 0;
@@ -255,6 +266,135 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     select_token(lg, E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, lane);
 }
 
+// ---------------------------------------------------------------------------------------
+// One warp per token, for narrow gates (E <= 16) and large batches: w_gate (<= 128 KiB at
+// D=4096) is served by L1, every lane streams its share of the row, no block-level barrier
+// sits on the main path.  Lanes are laid out as (expert octet, d-group) like the block kernel.
+// ---------------------------------------------------------------------------------------
+constexpr int kWarpTokWarps = 8;
+__global__ void __launch_bounds__(kWarpTokWarps * 32)
+router_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
+                   int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
+                   float* __restrict__ row_amax) {
+  __shared__ float lg[kWarpTokWarps][16];
+  __shared__ float s_wnorm;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tok = blockIdx.x * kWarpTokWarps + warp;
+  const bool tok_ok = tok < T;
+  const __nv_bfloat16* xrow = x + (size_t)(tok_ok ? tok : 0) * D;
+  const int V = E > 8 ? 2 : 1;
+  const int ev = lane % V, dg = lane / V, NG = 32 / V;
+  const bool want_wsq = warp == 0;          // column norms of w_gate: once per block
+
+  float acc[8], comp[8], inner[8], wsq[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f, comp[j] = 0.f, inner[j] = 0.f, wsq[j] = 0.f;
+  float xsq = 0.f, xmax = 0.f;
+  int inner_n = 0;
+  // each step: 8 consecutive d (one 16-byte load of x) against 8 rows of this lane's expert octet
+#pragma unroll 2
+  for (int d0 = dg * 8; d0 < D; d0 += NG * 8) {
+    // x streams past L1 (read once); w_gate is re-read by every warp and should stay in L1
+    const uint4 xraw = __ldcg(reinterpret_cast<const uint4*>(xrow + d0));
+    uint4 wraw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wraw[i] = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)(d0 + i) * E + 8 * ev));
+    const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 xp2 = __bfloat1622float2(px[i >> 1]);
+      const float xv = (i & 1) ? xp2.y : xp2.x;
+      xsq = fmaf(xv, xv, xsq);
+      xmax = fmaxf(xmax, fabsf(xv));
+      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&wraw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(pw[j]);
+        if (want_wsq) {
+          wsq[2 * j] = fmaf(f.x, f.x, wsq[2 * j]);
+          wsq[2 * j + 1] = fmaf(f.y, f.y, wsq[2 * j + 1]);
+        }
+        inner[2 * j] = fmaf(xv, f.x, inner[2 * j]);
+        inner[2 * j + 1] = fmaf(xv, f.y, inner[2 * j + 1]);
+      }
+    }
+    inner_n += 8;
+    if (inner_n == kInner) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        kahan_add(acc[j], comp[j], inner[j]);
+        inner[j] = 0.f;
+      }
+      inner_n = 0;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    kahan_add(acc[j], comp[j], inner[j]);
+    acc[j] = __fsub_rn(acc[j], comp[j]);
+  }
+  for (int off = V; off < 32; off <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  }
+  if (V == 2) {                       // both octets count the same x: halve the duplicated statistics
+    xsq *= 0.5f;
+  }
+  for (int off = 16; off; off >>= 1) {
+    xsq += __shfl_xor_sync(0xffffffffu, xsq, off);
+    xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
+  }
+  if (want_wsq) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      for (int off = V; off < 32; off <<= 1) wsq[j] += __shfl_xor_sync(0xffffffffu, wsq[j], off);
+      m = fmaxf(m, wsq[j]);
+    }
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));    // the other octet when V == 2
+    if (lane == 0) s_wnorm = sqrtf(m) * 1.001f;
+  }
+  if (lane < V) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lg[warp][8 * ev + j] = acc[j];
+  }
+  __syncthreads();
+  if (!tok_ok) return;
+  // blocks of kInner FMAs + compensated outer sum (2) + shuffle tree (<= 5)
+  const float gamma = (float)(kInner + 8) * 5.9604645e-8f * 1.05f;
+  const float thr_abs = 2.f * gamma * s_wnorm * sqrtf(xsq) * 1.001f;
+  const bool amb = select_token(lg[warp], E, K, 1.0e-6f, thr_abs, weights + (size_t)tok * K,
+                                indices + (size_t)tok * K, lane);
+  if (lane == 0 && row_amax != nullptr) row_amax[tok] = xmax;
+  if (!amb) return;
+  // near-tie: exact fp64 logits by this warp alone, same lane layout
+  double a[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = 0.0;
+#pragma unroll 4
+  for (int d = dg; d < D; d += NG) {
+    const double xv = (double)__bfloat162float(xrow[d]);
+    const uint4 raw = *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev);
+    const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(pw[j]);
+      a[2 * j] = fma(xv, (double)f.x, a[2 * j]);
+      a[2 * j + 1] = fma(xv, (double)f.y, a[2 * j + 1]);
+    }
+  }
+  for (int off = V; off < 32; off <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] += __shfl_xor_sync(0xffffffffu, a[j], off);
+  }
+  if (lane < V) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lg[warp][8 * ev + j] = (float)a[j];
+  }
+  __syncwarp();
+  select_token(lg[warp], E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, lane);
+}
+
 template <int TOK>
 __global__ void __launch_bounds__(kThreads)
 router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
@@ -266,7 +406,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   __shared__ float lg[TOK][256];
   __shared__ float s_abs[TOK], s_max[TOK];
   __shared__ float s_red[kThreads / 32][TOK], s_red2[kThreads / 32][TOK];
-  __shared__ float s_wmax[kThreads / 32];
+  __shared__ float s_wsq[256];         // squared column norms of w_gate
   __shared__ int s_flag[TOK];
   __shared__ int s_nflag;
   static_assert(kChunk == kThreads, "xs is sized for both uses");
@@ -279,11 +419,12 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const bool e_ok = e < E;
   const bool vec_ok = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
   if (tid == 0) s_nflag = 0;
+  s_wsq[tid] = 0.f;
 
   float acc[TOK], comp[TOK], inner[TOK];
 #pragma unroll
   for (int t = 0; t < TOK; ++t) acc[t] = 0.f, comp[t] = 0.f, inner[t] = 0.f;
-  float wmax = 0.f, my_abs = 0.f, my_max = 0.f;   // statistics gathered while staging / streaming
+  float wsq = 0.f, my_abs = 0.f, my_max = 0.f;    // statistics gathered while staging / streaming
   int inner_n = 0;
 
   for (int c0 = 0; c0 < D; c0 += kChunk) {
@@ -302,7 +443,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
           const float2 f = __bfloat1622float2(pr[j]);
           xs[(dd0 + 2 * j) * TOK + t] = f.x;
           xs[(dd0 + 2 * j + 1) * TOK + t] = f.y;
-          my_abs += fabsf(f.x) + fabsf(f.y);
+          my_abs = fmaf(f.x, f.x, fmaf(f.y, f.y, my_abs));
           my_max = fmaxf(my_max, fmaxf(fabsf(f.x), fabsf(f.y)));
         }
       }
@@ -312,7 +453,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
         float v = 0.f;
         if (tok0 + t < T && c0 + dd < D) v = __bfloat162float(x[(size_t)(tok0 + t) * D + c0 + dd]);
         xs[dd * TOK + t] = v;
-        my_abs += fabsf(v);
+        my_abs = fmaf(v, v, my_abs);
         my_max = fmaxf(my_max, fabsf(v));
       }
     }
@@ -322,7 +463,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
     for (int dd = ds; dd < dlim; dd += DS) {
       float w = 0.f;
       if (e_ok) w = __bfloat162float(wg[(size_t)(c0 + dd) * E + e]);
-      wmax = fmaxf(wmax, fabsf(w));
+      wsq = fmaf(w, w, wsq);
       const float* xr = xs + dd * TOK;
       if constexpr (TOK % 4 == 0) {
 #pragma unroll
@@ -358,7 +499,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 #pragma unroll
   for (int t = 0; t < TOK; ++t) xs[(ds * TOK + t) * Epad + e] = acc[t];
   {
-    // |x| sums and maxima per token (lanes l, l+TOK, ... of a warp serve the same token); max |w_gate|
+    // squared norms and maxima of x per token (lanes l, l+TOK, ... of a warp serve the same token)
     float a = my_abs, m = my_max;
     for (int off = TOK; off < 32; off <<= 1) {
       a += __shfl_xor_sync(0xffffffffu, a, off);
@@ -368,9 +509,7 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
       s_red[warp][lane] = a;
       s_red2[warp][lane] = m;
     }
-    float wm = wmax;
-    for (int off = 16; off; off >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, off));
-    if (lane == 0) s_wmax[warp] = wm;
+    if (e_ok) atomicAdd(&s_wsq[e], wsq);           // only feeds the tie threshold: order does not matter
   }
   __syncthreads();
   for (int idx = tid; idx < TOK * Epad; idx += kThreads) {
@@ -386,8 +525,9 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
     s_max[tid] = m;
   }
   __syncthreads();
-  float wm_all = 0.f;
-  for (int w = 0; w < kThreads / 32; ++w) wm_all = fmaxf(wm_all, s_wmax[w]);
+  float w_sq = 0.f;
+  for (int i = 0; i < E; ++i) w_sq = fmaxf(w_sq, s_wsq[i]);
+  const float w_norm = sqrtf(w_sq) * 1.001f;
 
   // error of one logit <= (kInner + 4) * 2^-24 * sum|x_d w_de|  (plain-FMA blocks; the compensated
   // additions contribute ~2 ulp of the result, covered by the relative term); a pair of logits
@@ -399,7 +539,8 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   for (int t = warp; t < TOK; t += kThreads / 32) {
     if (tok0 + t >= T) continue;
     const size_t tok = tok0 + t;
-    const float thr_abs = 2.f * gamma * wm_all * s_abs[t];
+    // Cauchy-Schwarz: sum_d |x_d w_de| <= |x|_2 * |w_e|_2 (s_abs holds the squared norm of x)
+    const float thr_abs = 2.f * gamma * w_norm * sqrtf(s_abs[t]);
     const bool amb = select_token(lg[t], E, K, thr_rel, thr_abs, weights + tok * K, indices + tok * K, lane);
     if (lane == 0) {
       if (row_amax != nullptr) row_amax[tok] = s_max[t];
@@ -437,7 +578,11 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(wg);
   const bool vec_gate = (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) & 15u) == 0);
-  if (vec_gate && (E <= 16 || T < 1024)) {
+  const bool vec_x = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+  if (vec_gate && vec_x && E <= 16 && T >= 1024) {
+    router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, st>>>(xp, wp, T, D, E, K, weights,
+                                                                                 indices, row_amax);
+  } else if (vec_gate && T < 1024) {
     const int threads = E >= 128 ? 1024 : 256;
     router_token_kernel<<<T, threads, 0, st>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
   } else if (T >= 2048) {

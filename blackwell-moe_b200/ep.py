@@ -142,7 +142,7 @@ class ExpertParallelMoE:
             sx_local = scale_x[self.rank * el:(self.rank + 1) * el].contiguous()
             h = new(R, H, dtype=torch.bfloat16)
             amax_h = torch.zeros(el, dtype=f32, device=dev)
-            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, el)), dtype=torch.uint8)
+            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, D, H, el)), dtype=torch.uint8)
             _lib.check(lib.bwmoe_gateup_swiglu(xq_local.data_ptr(), plan.offsets.data_ptr(), sx_local.data_ptr(),
                                                self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
                                                self.su.data_ptr(), R, D, H, el, h.data_ptr(), amax_h.data_ptr(),

@@ -209,11 +209,12 @@ int bwmoe_gather_quant(const void* d_x, const int32_t* d_row_slot, const int32_t
 /*
  * Grouped gate+up FP8 GEMM with SwiGLU: h[m,:] = silu(gate) * up in bf16 with the
  * reference's bf16 rounding points, plus d_seg_amax_h[e] = max|h| per segment
- * (d_seg_amax_h must be zero on entry).  d_scratch needs bwmoe_gemm_scratch_bytes(M, E).
+ * (d_seg_amax_h must be zero on entry).  d_scratch needs bwmoe_gemm_scratch_bytes(M, D, H, E)
+ * bytes (small batches split the K loop and sum fp32 partials from it in a fixed order).
  * replaces: fused_gate_up_gemm, src/blackwell_moe/kernels/grouped_fp8_gateup.py:42-138,
  *           and F.silu(gate)*up, src/blackwell_moe/kernels/fp8_moe_v3.py:60.
  */
-size_t bwmoe_gemm_scratch_bytes(int M, int E);
+size_t bwmoe_gemm_scratch_bytes(int M, int D, int H, int E);
 int bwmoe_gateup_swiglu(const void* d_xq, const int32_t* d_offsets, const float* d_scales_x,
                         const void* d_experts_w_gate, const void* d_experts_w_up,
                         const float* d_scales_gate, const float* d_scales_up,
