@@ -8,7 +8,8 @@ hand-written sm_100a CUDA kernels in ``libbwmoe.so`` reached through a C ABI
 missing or no B200 is present the calls raise.
 """
 
-from .quant import FP8_MAX_E4M3, dequant_fp8_e4m3, quant_fp8_e4m3, quantize_expert_weights
+from .quant import (FP8_MAX_E4M3, dequant_fp8_e4m3, quant_fp8_block_128, quant_fp8_e4m3, quantize_expert_weights,
+                    quantize_expert_weights_block)
 from .moe import (
     fp8_moe_forward,
     fp8_moe_forward_routed,
@@ -28,5 +29,6 @@ __version__ = "0.1.0"
 __all__ = [
     "FP8_MAX_E4M3", "BwmoeError", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_routed",
     "fp8_moe_forward_small_e", "fp8_moe_forward_v3", "fp8_moe_forward_v4", "lib", "library_path",
-    "moe_stage_views", "quant_fp8_e4m3", "quantize_expert_weights", "top_k_router",
+    "moe_stage_views", "quant_fp8_block_128", "quant_fp8_e4m3", "quantize_expert_weights",
+    "quantize_expert_weights_block", "top_k_router",
 ]

@@ -38,6 +38,12 @@ SIGNATURES = {
     "bwmoe_moe_forward": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed": (_i, [_vp, _fp, _ip] + [_vp] * 3 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_host": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
+    "bwmoe_workspace_bytes_block": (_sz, [_i] * 5),
+    "bwmoe_workspace_view_block": (_i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_sz)]),
+    "bwmoe_moe_forward_block": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
+    "bwmoe_gather_quant_group": (_i, [_vp, _ip, _i, _i, _i, _vp, _fp, _vp]),
+    "bwmoe_gateup_swiglu_block": (_i, [_vp, _fp, _ip, _vp, _vp, _fp, _fp, _i, _i, _i, _i, _vp, _fp, _ip, _vp]),
+    "bwmoe_down_block": (_i, [_vp, _fp, _ip, _vp, _fp, _i, _i, _i, _i, _vp, _ip, _vp]),
     "bwmoe_plan_scratch_bytes": (_sz, [_i] * 3),
     "bwmoe_permute_plan": (_i, [_ip, _fp, _i, _i, _i, _ip, _ip, _ip, _ip, _fp, _ip, _vp, _vp]),
     "bwmoe_permute_plan_static": (_i, [_ip, _fp, _i, _i, _i, _ip, _ip, _ip, _ip, _fp, _ip, _vp]),

@@ -79,6 +79,41 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   return true;
 }
 
+// Workspace of the block-scale recipe: no bf16 h, no segment statistics; per-row group scales instead.
+struct BlockLayout {
+  size_t status, zero_end, offsets, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, plan_scratch;
+  size_t xq, x_inv, hq, h_inv, y, total;
+};
+
+bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
+  if (T <= 0 || D <= 0 || H <= 0 || E <= 0 || K <= 0 || E > 256 || K > E || K > 32) return false;
+  if ((long long)T * K >= (1ll << 31)) return false;
+  const size_t M = (size_t)T * K;
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = o;
+    o = align_up(o + bytes);
+    return at;
+  };
+  L->status = take(16);
+  L->zero_end = o;
+  L->offsets = take(sizeof(int32_t) * (E + 1));
+  L->topk_idx = take(sizeof(int32_t) * M);
+  L->topk_w = take(sizeof(float) * M);
+  L->row_amax = take(sizeof(float) * T);
+  L->pos = take(sizeof(int32_t) * M);
+  L->row_slot = take(sizeof(int32_t) * M);
+  L->row_expert = take(sizeof(int32_t) * M);
+  L->plan_scratch = take(plan_scratch_bytes(T, E, K));
+  L->xq = take(M * D);
+  L->x_inv = take(sizeof(float) * M * ((D + 127) / 128));
+  L->hq = take(M * H);
+  L->h_inv = take(sizeof(float) * M * ((H + 127) / 128));
+  L->y = take(M * D * 2);
+  L->total = o;
+  return true;
+}
+
 template <class T>
 T* at(void* ws, size_t off) {
   return reinterpret_cast<T*>(static_cast<uint8_t*>(ws) + off);
@@ -271,6 +306,97 @@ int bwmoe_moe_forward_host(const void* h_x, const void* w_gate, const void* wg, 
   BWMOE_CUDA_OK(cudaMemcpyAsync(h_out, d_out, (size_t)T * D * 2, cudaMemcpyDeviceToHost, st));
   BWMOE_CUDA_OK(cudaStreamSynchronize(st));
   return BWMOE_OK;
+}
+
+size_t bwmoe_workspace_bytes_block(int T, int D, int H, int E, int K) {
+  BlockLayout L;
+  if (D % 16 != 0 || H % 16 != 0 || !make_block_layout(T, D, H, E, K, &L)) return 0;
+  return L.total;
+}
+
+int bwmoe_workspace_view_block(void* ws, int T, int D, int H, int E, int K, int which, void** ptr, size_t* bytes) {
+  BlockLayout L;
+  BWMOE_REQUIRE(ws && ptr && bytes, BWMOE_ERR_NULL, "workspace_view_block: null pointer");
+  BWMOE_REQUIRE(make_block_layout(T, D, H, E, K, &L), BWMOE_ERR_BAD_SHAPE, "workspace_view_block: bad shape");
+  const size_t M = (size_t)T * K;
+  size_t off = 0, n = 0;
+  switch (which) {
+    case BWMOE_WS_STATUS: off = L.status, n = 16; break;
+    case BWMOE_WS_OFFSETS: off = L.offsets, n = 4 * (size_t)(E + 1); break;
+    case BWMOE_WS_TOPK_IDX: off = L.topk_idx, n = 4 * M; break;
+    case BWMOE_WS_TOPK_W: off = L.topk_w, n = 4 * M; break;
+    case BWMOE_WS_POS: off = L.pos, n = 4 * M; break;
+    case BWMOE_WS_ROW_SLOT: off = L.row_slot, n = 4 * M; break;
+    case BWMOE_WS_ROW_EXPERT: off = L.row_expert, n = 4 * M; break;
+    case BWMOE_WS_XQ: off = L.xq, n = M * D; break;
+    case BWMOE_WS_HQ: off = L.hq, n = M * H; break;
+    case BWMOE_WS_Y: off = L.y, n = 2 * M * D; break;
+    case BWMOE_WS_X_INV: off = L.x_inv, n = 4 * M * ((D + 127) / 128); break;
+    case BWMOE_WS_H_INV: off = L.h_inv, n = 4 * M * ((H + 127) / 128); break;
+    default: return set_error(BWMOE_ERR_UNSUPPORTED, "workspace_view_block: selector %d not part of this recipe", which);
+  }
+  *ptr = static_cast<uint8_t*>(ws) + off;
+  *bytes = n;
+  return BWMOE_OK;
+}
+
+int bwmoe_moe_forward_block(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                            const float* inv_g, const float* inv_u, const float* inv_d, int T, int D, int H, int E,
+                            int K, void* out, void* ws, size_t ws_bytes, void* stream) {
+  BlockLayout L;
+  BWMOE_REQUIRE(T > 0 && D > 0 && H > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE,
+                "moe_forward_block: T=%d D=%d H=%d E=%d K=%d", T, D, H, E, K);
+  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE,
+                "moe_forward_block: D=%d and H=%d must be multiples of 16", D, H);
+  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "moe_forward_block: E=%d > 256 experts", E);
+  BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "moe_forward_block: top_k=%d must be <= min(E,32)", K);
+  BWMOE_REQUIRE(x && w_gate && wg && wu && wd && inv_g && inv_u && inv_d && out, BWMOE_ERR_NULL,
+                "moe_forward_block: null pointer");
+  BWMOE_REQUIRE(make_block_layout(T, D, H, E, K, &L), BWMOE_ERR_BAD_SHAPE, "moe_forward_block: shape not representable");
+  BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L.total, BWMOE_ERR_WORKSPACE,
+                "moe_forward_block: workspace of %zu bytes given, %zu needed", ws_bytes, L.total);
+  BWMOE_REQUIRE(aligned16(x) && aligned16(out) && aligned16(wg) && aligned16(wu) && aligned16(wd) &&
+                    (reinterpret_cast<uintptr_t>(ws) % 256 == 0),
+                BWMOE_ERR_BAD_ALIGN, "moe_forward_block: tensors must be 16-byte and the workspace 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = T * K;
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* weights = at<float>(ws, L.topk_w);
+  int32_t* indices = at<int32_t>(ws, L.topk_idx);
+  int32_t* status = at<int32_t>(ws, L.status);
+  int32_t* offsets = at<int32_t>(ws, L.offsets);
+  int rc;
+  if ((rc = launch_router(x, w_gate, T, D, E, K, weights, indices, nullptr, st))) return rc;
+  if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
+                        at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
+    return rc;
+  if ((rc = launch_gather_quant_group(x, at<int32_t>(ws, L.row_slot), M, D, K, at<void>(ws, L.xq),
+                                      at<float>(ws, L.x_inv), st)))
+    return rc;
+  if ((rc = launch_gateup_block(at<void>(ws, L.xq), at<float>(ws, L.x_inv), offsets, wg, wu, inv_g, inv_u, M, D, H, E,
+                                at<void>(ws, L.hq), at<float>(ws, L.h_inv), status, st)))
+    return rc;
+  if ((rc = launch_down_block(at<void>(ws, L.hq), at<float>(ws, L.h_inv), offsets, wd, inv_d, M, D, H, E,
+                              at<void>(ws, L.y), status, st)))
+    return rc;
+  return launch_combine(at<void>(ws, L.y), at<int32_t>(ws, L.pos), weights, T, D, K, out, st);
+}
+
+int bwmoe_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,
+                             void* stream) {
+  return launch_gather_quant_group(x, row_slot, M, D, K, xq, x_inv, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_gateup_swiglu_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg,
+                              const void* wu, const float* inv_g, const float* inv_u, int M, int D, int H, int E,
+                              void* hq, float* h_inv, int32_t* status, void* stream) {
+  return launch_gateup_block(xq, x_inv, offsets, wg, wu, inv_g, inv_u, M, D, H, E, hq, h_inv, status,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_down_block(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd, const float* inv_d,
+                     int M, int D, int H, int E, void* y, int32_t* status, void* stream) {
+  return launch_down_block(hq, h_inv, offsets, wd, inv_d, M, D, H, E, y, status, static_cast<cudaStream_t>(stream));
 }
 
 size_t bwmoe_plan_scratch_bytes(int T, int E, int K) {

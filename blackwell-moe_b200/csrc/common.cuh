@@ -82,4 +82,13 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
                 int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st);
 
+// 128x128 block-scale recipe
+int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,
+                              cudaStream_t st);
+int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
+                        const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
+                        int32_t* status, cudaStream_t st);
+int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
+                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st);
+
 }  // namespace bwmoe

@@ -1,0 +1,425 @@
+// Grouped FP8 GEMMs for the 128x128 block-scale recipe (weights: one inverse scale per
+// 128x128 block; activations: one per token per 128 consecutive K elements).
+//
+// The reference has no FP8 kernel for this recipe: its Qwen path dequantises block-FP8 weights
+// to bf16 (src/blackwell_moe/runtime/qwen_patch.py:30-40) and runs F.linear per expert
+// (qwen_patch.py:108-129).  This kernel keeps the operands in FP8 on the tensor cores and
+// applies the scales where the recipe puts them: every 128-wide K block is multiplied on its
+// own (tcgen05.mma into a fresh tensor-memory buffer), and the epilogue warps fold the block's
+// partial sums into fp32 register accumulators with  acc += partial * (a_inv[row,kb] * w_inv[kb,nb]).
+// Two tensor-memory buffers alternate, so the tensor pipe multiplies block kb+1 while block kb
+// is being folded in.
+//
+//   GATE_UP : hq = e4m3(h * s), h = silu(gate) * up with the bf16 rounding points of the
+//             per-tensor recipe; s per token per 128 columns of h, computed in the epilogue
+//             (a tile's 128 h columns are exactly one group) - no bf16 intermediate is written
+//   DOWN    : y = bf16(acc)
+//
+// CTA = 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue (two warps per
+// tensor-memory lane quarter; each thread owns one row and 2 x 64 accumulator columns).
+// Every barrier wait is bounded exactly as in the per-tensor kernel.
+#include "sm100_gemm.cuh"
+
+namespace bwmoe {
+namespace {
+using namespace sm100;
+
+constexpr int NUM_THREADS_BLK = 320;
+constexpr float kGroupAmaxFloor = 1e-4f;
+
+struct BlockGemmParams {
+  const int32_t* offsets;   // [E+1]
+  const float* a_inv;       // [M, k_blocks] activation inverse scales
+  const float* w0_inv;      // [E, k_blocks, nb] gate (or down) block scales
+  const float* w1_inv;      // [E, k_blocks, nb] up block scales (GATE_UP only)
+  void* out;                // GATE_UP: hq e4m3 [M, N_out];  DOWN: y bf16 [M, N_out]
+  float* out_inv;           // GATE_UP: [M, nb] inverse scales of hq
+  int32_t* status;
+  int E, Kdim, N_out, n_tiles, k_blocks, nb;
+};
+
+struct Cursor {
+  const int* cum;
+  const int32_t* offsets;
+  int E, n_tiles, e;
+  __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx) {
+    while (e < E && tile >= cum[e + 1]) ++e;
+    if (e >= E) return false;
+    const int seg0 = offsets[e], seg1 = offsets[e + 1];
+    const int m_tiles = (seg1 - seg0 + BM - 1) / BM;
+    const int within = tile - cum[e];
+    n_idx = within / m_tiles;
+    row0 = seg0 + (within % m_tiles) * BM;
+    row_end = seg1;
+    expert = e;
+    return true;
+  }
+};
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(NUM_THREADS_BLK, 1)
+block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                  const __grid_constant__ CUtensorMap map_b1, const BlockGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_cum[257];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ float s_amax[2][2][BM];     // [tile parity][column half][row]
+  __shared__ int s_seq[2][BM];           // tiles whose amax each (half, row) thread has published
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
+  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &s_abort;
+
+  for (int e = threadIdx.x; e < 256; e += NUM_THREADS_BLK) {
+    int t = 0;
+    if (e < p.E) {
+      const int rows = p.offsets[e + 1] - p.offsets[e];
+      t = ((rows + BM - 1) / BM) * p.n_tiles;
+    }
+    s_cum[e + 1] = t;
+  }
+  for (int i = threadIdx.x; i < 2 * BM; i += NUM_THREADS_BLK) (&s_seq[0][0])[i] = 0;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 8);      // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int v[8], run = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      run += s_cum[1 + lane * 8 + j];
+      v[j] = run;
+    }
+    int incl = run;
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    const int base = incl - run;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_cum[1 + lane * 8 + j] = base + v[j];
+    if (lane == 0) s_cum[0] = 0;
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const int total_tiles = s_cum[p.E];
+  const int k_blocks = p.k_blocks;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      Cursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        int e, row0, row_end, n_idx;
+        if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+        const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status))) break;
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(sa, &map_a, full, kb * BK, row0);
+          tma_load_3d(sa + A_BYTES, &map_b0, full, n0, kb * BK, e);
+          if (GATE_UP) tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b1, full, n0, kb * BK, e);
+          else         tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b0, full, n0 + BN_HALF, kb * BK, e);
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer: one fresh accumulator per K block =====================
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t buf = it & 1u, use = it >> 1;
+          if (!(ok = mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
+          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)
+            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, k > 0 ? 1u : 0u);
+          mma_commit(bar_empty + 8 * stage);
+          mma_commit(bar_tfull + 8 * buf);
+          if (++stage == STAGES) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== epilogue: fold K blocks into registers, then finish the tile =====================
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                 // which 2 x 64 columns this warp owns
+    const int r_in_tile = quarter * 32 + lane;
+    // accumulator column offsets of this thread's two 64-column chunks
+    const int colA = GATE_UP ? half * 64 : half * 128;
+    const int colB = GATE_UP ? BN_HALF + half * 64 : half * 128 + 64;
+    Cursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+    uint32_t it = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      int e, row0, row_end, n_idx;
+      if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
+      const int row = row0 + r_in_tile;
+      const bool row_ok = row < row_end;
+      const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
+      // weight-scale block column of each chunk
+      const int nbA = GATE_UP ? n_idx : min(n0 / 128 + half, p.nb - 1);
+      const float* wA = p.w0_inv + (size_t)e * k_blocks * p.nb + nbA;
+      const float* wB = GATE_UP ? p.w1_inv + (size_t)e * k_blocks * p.nb + nbA : wA;
+      const float* ai = p.a_inv + (size_t)(row_ok ? row : row0) * k_blocks;
+      float accA[64], accB[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) accA[j] = 0.f, accB[j] = 0.f;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const uint32_t buf = it & 1u, use = it >> 1;
+        const float a = ai[kb];
+        const float sA = a * wA[(size_t)kb * p.nb], sB = a * wB[(size_t)kb * p.nb];
+        ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_row + colA, r0);
+          tmem_ld32(t_row + colA + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            accA[j] = fmaf(__uint_as_float(r0[j]), sA, accA[j]);
+            accA[32 + j] = fmaf(__uint_as_float(r1[j]), sA, accA[32 + j]);
+          }
+        }
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_row + colB, r0);
+          tmem_ld32(t_row + colB + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            accB[j] = fmaf(__uint_as_float(r0[j]), sB, accB[j]);
+            accB[32 + j] = fmaf(__uint_as_float(r1[j]), sB, accB[32 + j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      }
+      if (!ok) break;
+      if constexpr (GATE_UP) {
+        // h for this thread's 64 columns; the row's group amax needs the other half too
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float gate = bf16_round(accA[j]);
+          const float up = bf16_round(accB[j]);
+          accA[j] = bf16_round(bf16_round(silu_f(gate)) * up);
+          amax = fmaxf(amax, fabsf(accA[j]));
+        }
+        // publish this half's maximum, then wait (bounded) for the thread that owns the other half of
+        // the row.  The parity buffer cannot be overwritten early: its owner reaches tile local+2 only
+        // after it has seen this thread's sequence number for tile local+1.
+        s_amax[local & 1u][half][r_in_tile] = amax;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&s_seq[half][r_in_tile]) = (int)local + 1;
+        {
+          const volatile int* other = &s_seq[half ^ 1][r_in_tile];
+          bool seen = *other > (int)local;
+          if (!seen) {
+            const unsigned long long t0 = global_ns();
+            for (uint32_t spin = 1; !(seen = *other > (int)local); ++spin) {
+              if ((spin & 255u) == 0u) {
+                if (*abort_flag) break;
+                if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  atomicOr(p.status, BWMOE_STATUS_WAIT_TIMEOUT);
+                  break;
+                }
+              }
+            }
+          }
+          ok = __all_sync(0xffffffffu, seen);
+          if (!ok) break;
+        }
+        __threadfence_block();
+        amax = fmaxf(amax, *reinterpret_cast<volatile float*>(&s_amax[local & 1u][half ^ 1][r_in_tile]));
+        amax = fmaxf(amax, kGroupAmaxFloor);
+        const float s = __fmul_rn(__frcp_rn(amax), kFp8Max);   // torch evaluates 448 / amax this way
+        if (row_ok) {
+          uint8_t* dst = static_cast<uint8_t*>(p.out) + (size_t)row * p.N_out + n0 + half * 64;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (n0 + half * 64 + v * 16 < p.N_out) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = v * 16 + q * 4;
+                w[q] = (uint32_t)to_e4m3x2(accA[j] * s, accA[j + 1] * s) |
+                       ((uint32_t)to_e4m3x2(accA[j + 2] * s, accA[j + 3] * s) << 16);
+              }
+              reinterpret_cast<uint4*>(dst)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+          if (half == 0) p.out_inv[(size_t)row * p.nb + n_idx] = __fdiv_rn(amax, kFp8Max);
+        }
+      } else {
+        if (row_ok) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out + n0 + half * 128;
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            if (n0 + half * 128 + v * 8 < p.N_out) {
+              const float* src = v < 8 ? accA + v * 8 : accB + (v - 8) * 8;
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(src[2 * q], src[2 * q + 1]);
+                w[q] = *reinterpret_cast<uint32_t*>(&b2);
+              }
+              reinterpret_cast<uint4*>(dst)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <bool GATE_UP>
+int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1,
+                      const BlockGemmParams& p, int M, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(block_gemm_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  BWMOE_CUDA_OK(attr_err);
+  const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
+  const int grid = (int)std::min<long long>(sm_count(), max_tiles);
+  block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+// ---- per-token, per-128-element activation quantisation (gather from token order) ----
+// q = e4m3(clamp(x * s)), s = 448 / max(amax, 1e-4) (torch's reciprocal-then-multiply),
+// inv = max(amax, 1e-4) / 448.  One thread per 8 elements, 16 threads per group.
+__global__ void __launch_bounds__(256)
+quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot, int M, int W,
+                        int K, uint8_t* __restrict__ dst, float* __restrict__ inv_out) {
+  const int groups = (W + 127) / 128;
+  const unsigned threads_per_row = groups * 16;
+  const unsigned chunks_per_row = (threads_per_row + blockDim.x - 1) / blockDim.x;
+  const int m = (int)(blockIdx.x / chunks_per_row);
+  const int v = (int)(blockIdx.x % chunks_per_row) * blockDim.x + threadIdx.x;      // 8-element vector index
+  const bool live = v * 8 < W;
+  const size_t srow = row_slot != nullptr ? (size_t)(row_slot[m] / K) : (size_t)m;
+  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+  if (live) raw = reinterpret_cast<const uint4*>(src + srow * W)[v];
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float f[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(p[j]);
+    f[2 * j] = t.x, f[2 * j + 1] = t.y;
+    amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+  }
+  for (int off = 8; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, 16));
+  amax = fmaxf(amax, kGroupAmaxFloor);
+  const float s = __fmul_rn(__frcp_rn(amax), kFp8Max);
+  if (!live) return;
+  const uint32_t lo = (uint32_t)to_e4m3x2(f[0] * s, f[1] * s) | ((uint32_t)to_e4m3x2(f[2] * s, f[3] * s) << 16);
+  const uint32_t hi = (uint32_t)to_e4m3x2(f[4] * s, f[5] * s) | ((uint32_t)to_e4m3x2(f[6] * s, f[7] * s) << 16);
+  reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
+  if ((v & 15) == 0) inv_out[(size_t)m * groups + (v >> 4)] = __fdiv_rn(amax, kFp8Max);
+}
+
+int check_block(const char* who, int M, int D, int H, int E) {
+  BWMOE_REQUIRE(M > 0 && D > 0 && H > 0 && E > 0, BWMOE_ERR_BAD_SHAPE, "%s: M=%d D=%d H=%d E=%d", who, M, D, H, E);
+  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
+  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "%s: E=%d > 256", who, E);
+  return BWMOE_OK;
+}
+
+}  // namespace
+
+int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,
+                              cudaStream_t st) {
+  BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant_group: M=%d D=%d K=%d", M, D, K);
+  BWMOE_REQUIRE(x && xq && x_inv, BWMOE_ERR_NULL, "gather_quant_group: null pointer");
+  BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant_group: pointers must be 16-byte aligned");
+  const int threads_per_row = ceil_div(D, 128) * 16;
+  const int threads = threads_per_row >= 256 ? 256 : ((threads_per_row + 31) / 32) * 32;
+  const unsigned grid = (unsigned)((size_t)M * ceil_div(threads_per_row, threads));
+  quant_group_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
+                                                    static_cast<uint8_t*>(xq), x_inv);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
+                        const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
+                        int32_t* status, cudaStream_t st) {
+  BWMOE_REQUIRE(xq && x_inv && offsets && wg && wu && inv_g && inv_u && hq && h_inv && status, BWMOE_ERR_NULL,
+                "gateup_block: null pointer");
+  if (int rc = check_block("gateup_block", M, D, H, E)) return rc;
+  BWMOE_REQUIRE(aligned16(xq) && aligned16(hq) && aligned16(wg) && aligned16(wu), BWMOE_ERR_BAD_ALIGN,
+                "gateup_block: pointers must be 16-byte aligned");
+  CUtensorMap ma, mg, mu;
+  if (int rc = make_map_a(&ma, xq, M, D)) return rc;
+  if (int rc = make_map_b(&mg, wg, E, D, H)) return rc;
+  if (int rc = make_map_b(&mu, wu, E, D, H)) return rc;
+  BlockGemmParams p{offsets, x_inv, inv_g, inv_u, hq, h_inv, status, E, D, H, ceil_div(H, BN_HALF),
+                    ceil_div(D, BK), ceil_div(H, 128)};
+  return launch_block_gemm<true>(ma, mg, mu, p, M, st);
+}
+
+int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
+                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st) {
+  BWMOE_REQUIRE(hq && h_inv && offsets && wd && inv_d && y && status, BWMOE_ERR_NULL, "down_block: null pointer");
+  if (int rc = check_block("down_block", M, D, H, E)) return rc;
+  BWMOE_REQUIRE(aligned16(hq) && aligned16(y) && aligned16(wd), BWMOE_ERR_BAD_ALIGN,
+                "down_block: pointers must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  if (int rc = make_map_a(&ma, hq, M, H)) return rc;
+  if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;
+  BlockGemmParams p{offsets, h_inv, inv_d, nullptr, y, nullptr, status, E, H, D, ceil_div(D, BN),
+                    ceil_div(H, BK), ceil_div(D, 128)};
+  return launch_block_gemm<false>(ma, mb, mb, p, M, st);
+}
+
+}  // namespace bwmoe

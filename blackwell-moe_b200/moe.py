@@ -81,8 +81,13 @@ def _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate,
     E, _, H = experts_w_gate.shape
     assert tuple(experts_w_up.shape) == (E, D, H), experts_w_up.shape
     assert tuple(experts_w_down.shape) == (E, H, D), experts_w_down.shape
+    block = scales_gate.dim() == 3
+    if block:   # 128x128 block scales, HF `weight_scale_inv` convention, [E, ceil(in/128), ceil(out/128)]
+        nd, nh = (D + 127) // 128, (H + 127) // 128
+        assert tuple(scales_gate.shape) == (E, nd, nh) and tuple(scales_up.shape) == (E, nd, nh), scales_gate.shape
+        assert tuple(scales_down.shape) == (E, nh, nd), scales_down.shape
     for s in (scales_gate, scales_up, scales_down):
-        assert s.numel() == E and s.dtype == torch.float32, (s.shape, s.dtype)
+        assert (block or s.numel() == E) and s.dtype == torch.float32, (s.shape, s.dtype)
     for w in (experts_w_gate, experts_w_up, experts_w_down):
         assert w.dtype == _FP8, w.dtype
     assert x.dtype == torch.bfloat16, x.dtype
@@ -92,6 +97,10 @@ def _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate,
 def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
                     scales_gate, scales_up, scales_down, top_k: int = 8) -> torch.Tensor:
     """FP8 MoE-block forward: ``x[T,D] bf16 -> out[T,D] bf16``.
+
+    ``scales_*`` of shape ``[E]`` select the reference's per-tensor recipe (forward
+    multipliers ``448/amax``); of shape ``[E, ceil(in/128), ceil(out/128)]`` the
+    128x128 block-scale recipe (inverse scales, as in HF ``weight_scale_inv``).
 
     ``x`` on the GPU: everything stays on the device and the result is a new
     CUDA tensor.  ``x`` in (pinned) host memory: the library copies it in,
@@ -107,6 +116,18 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
     x = _contig(x, "x")
     with torch.cuda.device(dev):
         ptrs = [t.data_ptr() for t in weights]
+        if scales_gate.dim() == 3:
+            if not x.is_cuda:
+                raise ValueError("the block-scale recipe takes CUDA activations")
+            _require_cuda(x, w_gate)
+            need = lib.bwmoe_workspace_bytes_block(T, D, H, E, top_k)
+            if need == 0:
+                raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={top_k}")
+            ws = _workspace(dev, need)
+            out = torch.empty_like(x)
+            _lib.check(lib.bwmoe_moe_forward_block(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
+                                                   ws.data_ptr(), ws.numel(), _stream(dev)))
+            return out
         if x.is_cuda:
             _require_cuda(x, w_gate)
             need = lib.bwmoe_workspace_bytes(T, D, H, E, top_k)
@@ -163,7 +184,11 @@ _VIEWS = {
 }
 
 
-def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int) -> dict:
+_BLOCK_ONLY = {"x_inv": (13, torch.float32), "h_inv": (14, torch.float32)}
+_TENSOR_ONLY = ("scale_x", "scale_h", "h")
+
+
+def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int, block: bool = False) -> dict:
     """Copies of the intermediates the last forward of this shape on the current
     stream left in its workspace (routing, permutation, FP8 codes, scales) and
     the device status word.  For stage-level checks; synchronises."""
@@ -172,9 +197,16 @@ def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int) -> dict:
     ws = _workspaces[(dev.index, _stream(dev))]
     out = {}
     torch.cuda.synchronize(dev)
-    for name, (sel, dtype) in _VIEWS.items():
+    views = dict(_VIEWS)
+    fn = lib.bwmoe_workspace_view
+    if block:
+        for k in _TENSOR_ONLY:
+            views.pop(k)
+        views.update(_BLOCK_ONLY)
+        fn = lib.bwmoe_workspace_view_block
+    for name, (sel, dtype) in views.items():
         ptr, nbytes = C.c_void_p(), C.c_size_t()
-        _lib.check(lib.bwmoe_workspace_view(ws.data_ptr(), T, D, H, E, K, sel, C.byref(ptr), C.byref(nbytes)))
+        _lib.check(fn(ws.data_ptr(), T, D, H, E, K, sel, C.byref(ptr), C.byref(nbytes)))
         off = ptr.value - ws.data_ptr()
         out[name] = ws[off:off + nbytes.value].clone().view(dtype)
     M = T * K
@@ -182,6 +214,10 @@ def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int) -> dict:
     out["weights"] = out["weights"].view(T, K)
     out["xq"] = out["xq"].view(M, D).view(_FP8)
     out["hq"] = out["hq"].view(M, H).view(_FP8)
-    out["h"] = out["h"].view(M, H)
     out["y"] = out["y"].view(M, D)
+    if block:
+        out["x_inv"] = out["x_inv"].view(M, -1)
+        out["h_inv"] = out["h_inv"].view(M, -1)
+    else:
+        out["h"] = out["h"].view(M, H)
     return out

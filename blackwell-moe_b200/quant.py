@@ -31,3 +31,26 @@ def quantize_expert_weights(w: torch.Tensor):
     ``(q[E,in,out] e4m3, scales[E] fp32)``."""
     qs, ss = zip(*(quant_fp8_e4m3(w[e]) for e in range(w.shape[0])))
     return torch.stack(list(qs)).contiguous(), torch.stack(list(ss)).to(torch.float32).contiguous()
+
+
+def quant_fp8_block_128(w: torch.Tensor):
+    """128x128 block quantisation of one ``[in, out]`` matrix in the convention of HF block-FP8
+    checkpoints, i.e. the inverse of the reference's ``_dequant_block_fp8``
+    (src/blackwell_moe/runtime/qwen_patch.py:30-40): ``w ~= code * scale_inv``.
+    Returns ``(code[in,out] e4m3, scale_inv[ceil(in/128), ceil(out/128)] fp32)``."""
+    R, C = w.shape
+    rb, cb = (R + 127) // 128, (C + 127) // 128
+    wf = torch.zeros(rb * 128, cb * 128, dtype=torch.float32, device=w.device)
+    wf[:R, :C] = w.to(torch.float32)
+    amax = wf.view(rb, 128, cb, 128).abs().amax(dim=(1, 3)).clamp(min=1e-4)
+    # tensor / tensor: an IEEE division on every device (tensor / python-scalar is a reciprocal multiply on CUDA)
+    scale_inv = (amax / torch.full_like(amax, FP8_MAX_E4M3)).to(torch.float32)
+    full = scale_inv.repeat_interleave(128, dim=0)[:R].repeat_interleave(128, dim=1)[:, :C]
+    q = (w.to(torch.float32) / full).clamp(-FP8_MAX_E4M3, FP8_MAX_E4M3).to(torch.float8_e4m3fn)
+    return q, scale_inv
+
+
+def quantize_expert_weights_block(w: torch.Tensor):
+    """:func:`quant_fp8_block_128` over a stack ``[E, in, out]`` -> ``(codes, scale_inv[E, in/128, out/128])``."""
+    qs, ss = zip(*(quant_fp8_block_128(w[e]) for e in range(w.shape[0])))
+    return torch.stack(list(qs)).contiguous(), torch.stack(list(ss)).contiguous()

@@ -67,7 +67,9 @@ enum {
   BWMOE_WS_HQ = 9,         /* e4m3[M*H]   quantised SwiGLU output        */
   BWMOE_WS_H = 10,         /* bf16[M*H]   SwiGLU output before requant   */
   BWMOE_WS_Y = 11,         /* bf16[M*D]   down-projection rows           */
-  BWMOE_WS_ROW_EXPERT = 12 /* int32[M]    permuted row -> expert         */
+  BWMOE_WS_ROW_EXPERT = 12, /* int32[M]   permuted row -> expert         */
+  BWMOE_WS_X_INV = 13,     /* float[M*ceil(D/128)] block recipe: inverse scales of xq */
+  BWMOE_WS_H_INV = 14      /* float[M*ceil(H/128)] block recipe: inverse scales of hq */
 };
 
 int bwmoe_version(void);
@@ -147,6 +149,38 @@ int bwmoe_moe_forward_host(const void* h_x, const void* d_w_gate,
                            const float* d_scales_down,
                            int T, int D, int H, int E, int K,
                            void* h_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The block with 128x128 block-scaled FP8 weights (HF `weight_scale_inv` convention:
+ * w = code * inv, d_inv_*[E, ceil(in/128), ceil(out/128)] fp32, weights still [E,in,out]) and
+ * per-token, per-128-element FP8 activations, multiplied in FP8 with the scales applied per
+ * K block.  SwiGLU and the requantisation of h run in the gate/up epilogue: no 16-bit
+ * intermediate is written.
+ * replaces: the dequantise-to-bf16 + F.linear expert loop of StreamingQwenMoE.forward,
+ *           src/blackwell_moe/runtime/qwen_patch.py:100-136 (weight semantics of
+ *           _dequant_block_fp8, qwen_patch.py:30-40).
+ */
+size_t bwmoe_workspace_bytes_block(int T, int D, int H, int E, int K);
+int bwmoe_workspace_view_block(void* d_workspace, int T, int D, int H, int E, int K, int which,
+                               void** d_ptr, size_t* bytes);
+int bwmoe_moe_forward_block(const void* d_x, const void* d_w_gate,
+                            const void* d_experts_w_gate, const void* d_experts_w_up,
+                            const void* d_experts_w_down,
+                            const float* d_inv_gate, const float* d_inv_up, const float* d_inv_down,
+                            int T, int D, int H, int E, int K,
+                            void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Stages of the block-scale recipe (d_row_slot may be null: rows are then taken in order). */
+int bwmoe_gather_quant_group(const void* d_x, const int32_t* d_row_slot, int M, int D, int K,
+                             void* d_xq, float* d_x_inv, void* stream);
+int bwmoe_gateup_swiglu_block(const void* d_xq, const float* d_x_inv, const int32_t* d_offsets,
+                              const void* d_experts_w_gate, const void* d_experts_w_up,
+                              const float* d_inv_gate, const float* d_inv_up,
+                              int M, int D, int H, int E, void* d_hq, float* d_h_inv,
+                              int32_t* d_status, void* stream);
+int bwmoe_down_block(const void* d_hq, const float* d_h_inv, const int32_t* d_offsets,
+                     const void* d_experts_w_down, const float* d_inv_down,
+                     int M, int D, int H, int E, void* d_y, int32_t* d_status, void* stream);
 
 /* ---- stage entry points (used by the expert-parallel host code and by tests) ---- */
 
