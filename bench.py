@@ -32,7 +32,26 @@ WORKLOADS = {
     "mixtral-8x7b": (4096, 14336, 8, 2, 16384),
     "deepseek-v2-lite": (2048, 1408, 64, 6, 4096),
     "toy": (1024, 2048, 16, 2, 256),
+    "qwen3-30b-a3b": (2048, 768, 128, 8, 8192),        # 128x128 block-scale weights, Zipf(1.1) expert popularity
+    "qwen3.6-35b-a3b": (2048, 512, 256, 8, 32768),     # 128x128 block-scale weights
 }
+BLOCK_SCALE = {"qwen3-30b-a3b", "qwen3.6-35b-a3b"}
+ZIPF = {"qwen3-30b-a3b"}
+
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one gate+up GEMM launch from the ncu capture
+# summarised in profiles/grouped_gemm_mixtral_T2048_ncu_full.md: workload -> (T of the capture, bytes).
+NCU_GATEUP_TRAFFIC = {"mixtral-8x7b": (2048, 956.4e6 + 108.8e6)}
+
+
+def gateup_traffic_bytes(workload, T, D, H, E, K):
+    """Measured traffic of the small capture scaled to T tokens: the weight bytes are read once whatever
+    T is; the rest (FP8 activations in, bf16 h out) grows in proportion to the rows processed."""
+    if workload not in NCU_GATEUP_TRAFFIC:
+        return None
+    t0, measured = NCU_GATEUP_TRAFFIC[workload]
+    weights = 2.0 * E * D * H
+    return weights + (measured - weights) * (T / t0)
 
 
 def kernels_per_forward(M: int) -> int:
@@ -56,7 +75,7 @@ def parse():
 
 
 # --------------------------------------------------------------------------- inputs
-def synth_weights(D, H, E, dev, seed, experts=None, keep_bf16=False):
+def synth_weights(D, H, E, dev, seed, experts=None, keep_bf16=False, block=False):
     """Random-init weights of the workload's architecture: bf16 ~N(0, 0.02^2), quantised per
     expert matrix to E4M3 (scale 448/amax) exactly as the reference's bench does
     (src/blackwell_moe/bench/cli.py:39-70).  Generated expert by expert on the device."""
@@ -69,7 +88,7 @@ def synth_weights(D, H, E, dev, seed, experts=None, keep_bf16=False):
         for name, shape in (("gate", (D, H)), ("up", (D, H)), ("down", (H, D))):
             g.manual_seed(seed * 100003 + e * 7 + {"gate": 0, "up": 1, "down": 2}[name])
             w = (torch.randn(shape, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-            q, s = bw.quant_fp8_e4m3(w)
+            q, s = bw.quant_fp8_block_128(w) if block else bw.quant_fp8_e4m3(w)
             out["q_" + name].append(q), out["s_" + name].append(s)
             if keep_bf16:
                 bf[name].append(w.cpu())
@@ -81,10 +100,18 @@ def synth_weights(D, H, E, dev, seed, experts=None, keep_bf16=False):
     return res
 
 
-def synth_activations(T, D, E, dev, seed):
+def synth_activations(T, D, E, dev, seed, zipf=False, gate_seed=None):
+    """x ~ N(0,1) bf16, w_gate ~ N(0, 0.02^2) bf16.  zipf: expert popularity ~ Zipf(1.1) through a
+    constant input feature and a log-rank row of w_gate, i.e. inside the plain API."""
     g = torch.Generator(device=dev).manual_seed(seed)
     x = torch.randn((T, D), generator=g, device=dev).to(torch.bfloat16)
+    g.manual_seed(seed if gate_seed is None else gate_seed)
     w_gate = (torch.randn((D, E), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    if zipf:
+        ranks = torch.randperm(E, generator=g, device=dev).float() + 1.0
+        bias = -1.1 * torch.log(ranks)
+        x[:, 0] = 1.0
+        w_gate[0] = (bias - bias.mean()).to(torch.bfloat16)
     return x, w_gate
 
 
@@ -211,18 +238,18 @@ def run_ours(args):
     D, H, E, K, T_default = WORKLOADS[args.workload]
     T = args.tokens or T_default
     stream = torch.cuda.current_stream(dev)
-    x, w_gate = synth_activations(T, D, E, dev, seed=1234 + rank)
+    block, zipf = args.workload in BLOCK_SCALE, args.workload in ZIPF
+    x, w_gate = synth_activations(T, D, E, dev, seed=1234 + rank, zipf=zipf, gate_seed=1234)   # router replicated
 
     if world == 1:
-        W = synth_weights(D, H, E, dev, seed=7)
+        W = synth_weights(D, H, E, dev, seed=7, block=block)
         wargs = (w_gate, W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"])
         step = lambda: bw.fp8_moe_forward(x, *wargs, top_k=K)            # noqa: E731
     else:
         from blackwell_moe_b200.ep import ExpertParallelMoE
         assert E % world == 0, f"E={E} experts do not shard over {world} ranks"
         mine = range(rank * (E // world), (rank + 1) * (E // world))
-        _, w_gate = synth_activations(1, D, E, dev, seed=1234)           # router replicated
-        W = synth_weights(D, H, E, dev, seed=7, experts=mine)
+        W = synth_weights(D, H, E, dev, seed=7, experts=mine, block=block)
         ep = ExpertParallelMoE(w_gate, W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"],
                                num_experts=E, top_k=K, group=dist.group.WORLD)
         step = lambda: ep.forward(x)                                     # noqa: E731
@@ -279,13 +306,28 @@ def run_ours(args):
             p, n = C.c_void_p(), C.c_size_t()
             _lib.check(lib.bwmoe_workspace_view(ws.data_ptr(), T, D, H, E, K, sel, C.byref(p), C.byref(n)))
             return p.value
-        amax_h = torch.zeros(E, device=dev, dtype=torch.float32)
-        scratch = torch.empty(max(256, lib.bwmoe_gemm_scratch_bytes(M, D, H, E)), device=dev, dtype=torch.uint8)
+        if block:
+            def view(sel):                                                            # noqa: F811
+                p, n = C.c_void_p(), C.c_size_t()
+                _lib.check(lib.bwmoe_workspace_view_block(ws.data_ptr(), T, D, H, E, K, sel, C.byref(p), C.byref(n)))
+                return p.value
 
-        def gateup():
-            _lib.check(lib.bwmoe_gateup_swiglu(view(8), view(1), view(6), W["q_gate"].data_ptr(), W["q_up"].data_ptr(),
-                                               W["s_gate"].data_ptr(), W["s_up"].data_ptr(), M, D, H, E, view(10),
-                                               amax_h.data_ptr(), view(0), scratch.data_ptr(), stream.cuda_stream))
+            def gateup():
+                _lib.check(lib.bwmoe_gateup_swiglu_block(view(8), view(13), view(1), W["q_gate"].data_ptr(),
+                                                         W["q_up"].data_ptr(), W["s_gate"].data_ptr(),
+                                                         W["s_up"].data_ptr(), M, D, H, E, view(9), view(14), view(0),
+                                                         stream.cuda_stream))
+            kernel_name = "block_gemm_kernel<GATE_UP>"
+        else:
+            amax_h = torch.zeros(E, device=dev, dtype=torch.float32)
+            scratch = torch.empty(max(256, lib.bwmoe_gemm_scratch_bytes(M, D, H, E)), device=dev, dtype=torch.uint8)
+
+            def gateup():
+                _lib.check(lib.bwmoe_gateup_swiglu(view(8), view(1), view(6), W["q_gate"].data_ptr(),
+                                                   W["q_up"].data_ptr(), W["s_gate"].data_ptr(), W["s_up"].data_ptr(),
+                                                   M, D, H, E, view(10), amax_h.data_ptr(), view(0), scratch.data_ptr(),
+                                                   stream.cuda_stream))
+            kernel_name = "grouped_gemm_kernel<GATE_UP>"
         for _ in range(3):
             gateup()
         torch.cuda.synchronize(dev)
@@ -299,7 +341,7 @@ def run_ours(args):
         peak = 2.0 * bf16_sus if bf16_sus else 2.0 * 1400.0
         achieved = flops / k_secs / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "grouped_gemm_kernel<GATE_UP>",
+                    "traffic": gateup_traffic_bytes(args.workload, T, D, H, E, K), "kernel": kernel_name,
                     "kernel_ms": k_secs * 1e3, "flops_per_launch": flops,
                     "peak_basis": ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it has no FP8 entry)"
                                    if bf16_sus else "2 x 1400 TFLOP/s fallback (sustained bf16 of the profiling recipe)")}
@@ -320,7 +362,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (weights %.0f MB per step)" % (3.0 * E * D * H / world / 1e6)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 2 * world,
                 "d2h_bytes_per_step": T * D * 2 * world, "ms_per_step": e2e_secs / args.steps * 1e3},
-        "gpu_launches": kernels_per_forward(T * K) * args.steps,
+        "gpu_launches": (9 if block and T * K > 1024 else 6 if block else kernels_per_forward(T * K)) * args.steps,
         "clocks": clocks.summary(),
     }
     if roofline is not None:

@@ -34,7 +34,8 @@ SIGNATURES = {
     "bwmoe_workspace_bytes_host": (_sz, [_i] * 5),
     "bwmoe_workspace_view": (_i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_sz)]),
     "bwmoe_read_status": (_i, [_vp, _vp, C.POINTER(C.c_int32)]),
-    "bwmoe_router": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _ip, _fp, _vp]),
+    "bwmoe_router_scratch_bytes": (_sz, [_i] * 4),
+    "bwmoe_router": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _ip, _fp, _vp, _sz, _vp]),
     "bwmoe_moe_forward": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed": (_i, [_vp, _fp, _ip] + [_vp] * 3 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_host": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),

@@ -43,7 +43,7 @@ inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 struct Layout {
   size_t status, amax_x, amax_h, zero_end;
   size_t offsets, scale_x, scale_h, topk_idx, topk_w, row_amax, pos, row_slot, row_expert;
-  size_t plan_scratch, gemm_scratch, xq, h, hq, y, total;
+  size_t plan_scratch, gemm_scratch, router_scratch, router_scratch_bytes, xq, h, hq, y, total;
 };
 
 bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
@@ -71,6 +71,8 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   L->row_expert = take(sizeof(int32_t) * M);
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
   L->gemm_scratch = take(gemm_scratch_bytes((int)M, D, H, E));
+  L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
+  L->router_scratch = take(L->router_scratch_bytes);
   L->xq = take(M * D);
   L->h = take(M * H * 2);
   L->hq = take(M * H);
@@ -82,7 +84,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
 // Workspace of the block-scale recipe: no bf16 h, no segment statistics; per-row group scales instead.
 struct BlockLayout {
   size_t status, zero_end, offsets, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, plan_scratch;
-  size_t xq, x_inv, hq, h_inv, y, total;
+  size_t router_scratch, router_scratch_bytes, xq, x_inv, hq, h_inv, y, total;
 };
 
 bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
@@ -105,6 +107,8 @@ bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
   L->row_slot = take(sizeof(int32_t) * M);
   L->row_expert = take(sizeof(int32_t) * M);
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
+  L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
+  L->router_scratch = take(L->router_scratch_bytes);
   L->xq = take(M * D);
   L->x_inv = take(sizeof(float) * M * ((D + 127) / 128));
   L->hq = take(M * H);
@@ -244,9 +248,15 @@ int bwmoe_read_status(void* ws, void* stream, int32_t* status) {
   return BWMOE_OK;
 }
 
+size_t bwmoe_router_scratch_bytes(int T, int D, int E, int K) {
+  if (T <= 0 || D <= 0 || E <= 0 || K <= 0) return 0;
+  return router_scratch_bytes(T, D, E, K);
+}
+
 int bwmoe_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights, int32_t* indices,
-                 float* row_amax, void* stream) {
-  return launch_router(x, wg, T, D, E, K, weights, indices, row_amax, static_cast<cudaStream_t>(stream));
+                 float* row_amax, void* scratch, size_t scratch_bytes, void* stream) {
+  return launch_router(x, wg, T, D, E, K, weights, indices, row_amax, static_cast<cudaStream_t>(stream), scratch,
+                       scratch_bytes, nullptr);
 }
 
 int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
@@ -261,7 +271,9 @@ int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const v
   float* weights = at<float>(ws, L.topk_w);
   int32_t* indices = at<int32_t>(ws, L.topk_idx);
   float* row_amax = at<float>(ws, L.row_amax);
-  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, row_amax, st)) return rc;
+  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, row_amax, st, at<void>(ws, L.router_scratch),
+                             L.router_scratch_bytes, at<int32_t>(ws, L.status)))
+    return rc;
   return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
 }
 
@@ -366,7 +378,9 @@ int bwmoe_moe_forward_block(const void* x, const void* w_gate, const void* wg, c
   int32_t* status = at<int32_t>(ws, L.status);
   int32_t* offsets = at<int32_t>(ws, L.offsets);
   int rc;
-  if ((rc = launch_router(x, w_gate, T, D, E, K, weights, indices, nullptr, st))) return rc;
+  if ((rc = launch_router(x, w_gate, T, D, E, K, weights, indices, nullptr, st, at<void>(ws, L.router_scratch),
+                          L.router_scratch_bytes, status)))
+    return rc;
   if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
                         at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
     return rc;

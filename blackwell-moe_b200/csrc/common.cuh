@@ -58,8 +58,17 @@ __device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
 }
 
 // ---- launchers implemented in the individual .cu files ---------------------
+// scratch (optional): enables the tensor-core router where it applies; needs router_scratch_bytes()
+size_t router_scratch_bytes(int T, int D, int E, int K);
 int launch_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
-                  int32_t* indices, float* row_amax, cudaStream_t st);
+                  int32_t* indices, float* row_amax, cudaStream_t st, void* scratch = nullptr,
+                  size_t scratch_bytes = 0, int32_t* status = nullptr);
+bool router_tc_applicable(int T, int D, int E, int K);
+size_t router_tc_scratch_bytes(int T, int D, int E);
+int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, float* weights, int32_t* indices,
+                     float* row_amax, int32_t* status, void* scratch, cudaStream_t st);
+int launch_router_fallback(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
+                           int32_t* indices, const int32_t* list, const int32_t* count, cudaStream_t st);
 size_t plan_scratch_bytes(int T, int E, int K);
 int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int K, int32_t* offsets,
                 int32_t* pos, int32_t* row_slot, int32_t* row_expert, float* seg_amax, int32_t* status,

@@ -195,10 +195,16 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       float accA[64], accB[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) accA[j] = 0.f, accB[j] = 0.f;
+      // scales of the next K block are fetched while the current one is folded in
+      float a_nx = ai[0], wA_nx = wA[0], wB_nx = wB[0];
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const uint32_t buf = it & 1u, use = it >> 1;
-        const float a = ai[kb];
-        const float sA = a * wA[(size_t)kb * p.nb], sB = a * wB[(size_t)kb * p.nb];
+        const float sA = a_nx * wA_nx, sB = a_nx * wB_nx;
+        if (kb + 1 < k_blocks) {
+          a_nx = ai[kb + 1];
+          wA_nx = wA[(size_t)(kb + 1) * p.nb];
+          wB_nx = wB[(size_t)(kb + 1) * p.nb];
+        }
         ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -336,36 +342,47 @@ int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUten
 
 // ---- per-token, per-128-element activation quantisation (gather from token order) ----
 // q = e4m3(clamp(x * s)), s = 448 / max(amax, 1e-4) (torch's reciprocal-then-multiply),
-// inv = max(amax, 1e-4) / 448.  One thread per 8 elements, 16 threads per group.
+// inv = max(amax, 1e-4) / 448.  A thread owns 8 elements of kGroupVecs different groups (all loaded
+// before the first is used); the 16 threads of a group reduce the maximum with shuffles.
+constexpr int kGroupVecs = 4;
 __global__ void __launch_bounds__(256)
 quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot, int M, int W,
                         int K, uint8_t* __restrict__ dst, float* __restrict__ inv_out) {
   const int groups = (W + 127) / 128;
-  const unsigned threads_per_row = groups * 16;
-  const unsigned chunks_per_row = (threads_per_row + blockDim.x - 1) / blockDim.x;
+  const unsigned per_block = blockDim.x * kGroupVecs;
+  const unsigned chunks_per_row = (groups * 16 + per_block - 1) / per_block;
   const int m = (int)(blockIdx.x / chunks_per_row);
-  const int v = (int)(blockIdx.x % chunks_per_row) * blockDim.x + threadIdx.x;      // 8-element vector index
-  const bool live = v * 8 < W;
+  const int v0 = (int)(blockIdx.x % chunks_per_row) * per_block + threadIdx.x;     // 8-element vector index
   const size_t srow = row_slot != nullptr ? (size_t)(row_slot[m] / K) : (size_t)m;
-  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-  if (live) raw = reinterpret_cast<const uint4*>(src + srow * W)[v];
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  float f[8];
-  float amax = 0.f;
+  const uint4* in = reinterpret_cast<const uint4*>(src + srow * W);
+  uint4 raw[kGroupVecs];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 t = __bfloat1622float2(p[j]);
-    f[2 * j] = t.x, f[2 * j + 1] = t.y;
-    amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+  for (int i = 0; i < kGroupVecs; ++i) {
+    const int v = v0 + i * blockDim.x;
+    raw[i] = v * 8 < W ? in[v] : make_uint4(0u, 0u, 0u, 0u);
   }
-  for (int off = 8; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, 16));
-  amax = fmaxf(amax, kGroupAmaxFloor);
-  const float s = __fmul_rn(__frcp_rn(amax), kFp8Max);
-  if (!live) return;
-  const uint32_t lo = (uint32_t)to_e4m3x2(f[0] * s, f[1] * s) | ((uint32_t)to_e4m3x2(f[2] * s, f[3] * s) << 16);
-  const uint32_t hi = (uint32_t)to_e4m3x2(f[4] * s, f[5] * s) | ((uint32_t)to_e4m3x2(f[6] * s, f[7] * s) << 16);
-  reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
-  if ((v & 15) == 0) inv_out[(size_t)m * groups + (v >> 4)] = __fdiv_rn(amax, kFp8Max);
+#pragma unroll
+  for (int i = 0; i < kGroupVecs; ++i) {
+    const int v = v0 + i * blockDim.x;
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    float f[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(p[j]);
+      f[2 * j] = t.x, f[2 * j + 1] = t.y;
+      amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+    }
+    for (int off = 8; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, 16));
+    amax = fmaxf(amax, kGroupAmaxFloor);
+    const float s = __fmul_rn(__frcp_rn(amax), kFp8Max);
+    if (v * 8 < W) {
+      const uint32_t lo = (uint32_t)to_e4m3x2(f[0] * s, f[1] * s) | ((uint32_t)to_e4m3x2(f[2] * s, f[3] * s) << 16);
+      const uint32_t hi = (uint32_t)to_e4m3x2(f[4] * s, f[5] * s) | ((uint32_t)to_e4m3x2(f[6] * s, f[7] * s) << 16);
+      reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
+      if ((v & 15) == 0) inv_out[(size_t)m * groups + (v >> 4)] = __fdiv_rn(amax, kFp8Max);
+    }
+  }
 }
 
 int check_block(const char* who, int M, int D, int H, int E) {
@@ -382,9 +399,10 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
   BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant_group: M=%d D=%d K=%d", M, D, K);
   BWMOE_REQUIRE(x && xq && x_inv, BWMOE_ERR_NULL, "gather_quant_group: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant_group: pointers must be 16-byte aligned");
-  const int threads_per_row = ceil_div(D, 128) * 16;
-  const int threads = threads_per_row >= 256 ? 256 : ((threads_per_row + 31) / 32) * 32;
-  const unsigned grid = (unsigned)((size_t)M * ceil_div(threads_per_row, threads));
+  const int vecs_per_row = ceil_div(D, 128) * 16;
+  int threads = 32;
+  while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
+  const unsigned grid = (unsigned)((size_t)M * ceil_div(vecs_per_row, threads * kGroupVecs));
   quant_group_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
                                                     static_cast<uint8_t*>(xq), x_inv);
   BWMOE_CUDA_OK(cudaGetLastError());

@@ -565,14 +565,50 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   }
 }
 
+// Exact (fp64) routing of the tokens in a device-side list; used behind the tensor-core router
+// for tokens whose candidate list overflowed.  Blocks stride over the list.
+__global__ void __launch_bounds__(256)
+router_fallback_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int D, int E,
+                       int K, float* __restrict__ weights, int32_t* __restrict__ indices,
+                       const int32_t* __restrict__ list, const int32_t* __restrict__ count) {
+  __shared__ float lg[256];
+  __shared__ double dsum[256];
+  const int n = *count;
+  for (int f = blockIdx.x; f < n; f += gridDim.x) {
+    const int tok = list[f];
+    exact_logits_block(x + (size_t)tok * D, wg, D, E, lg, dsum);
+    if (threadIdx.x < 32)
+      select_token(lg, E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, threadIdx.x);
+    __syncthreads();
+  }
+}
+
 }  // namespace
 
+int launch_router_fallback(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
+                           int32_t* indices, const int32_t* list, const int32_t* count, cudaStream_t st) {
+  (void)T;
+  router_fallback_kernel<<<64, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                             static_cast<const __nv_bfloat16*>(wg), D, E, K, weights, indices, list,
+                                             count);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+size_t router_scratch_bytes(int T, int D, int E, int K) {
+  return router_tc_applicable(T, D, E, K) ? router_tc_scratch_bytes(T, D, E) : 0;
+}
+
 int launch_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
-                  int32_t* indices, float* row_amax, cudaStream_t st) {
+                  int32_t* indices, float* row_amax, cudaStream_t st, void* scratch, size_t scratch_bytes,
+                  int32_t* status) {
   BWMOE_REQUIRE(T > 0 && D > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "router: T=%d D=%d E=%d K=%d", T, D, E, K);
   BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "router: E=%d > 256", E);
   BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "router: K=%d must be <= min(E,32)", K);
   BWMOE_REQUIRE(x && wg && weights && indices, BWMOE_ERR_NULL, "router: null pointer");
+  if (router_tc_applicable(T, D, E, K) && scratch != nullptr && scratch_bytes >= router_tc_scratch_bytes(T, D, E) &&
+      aligned16(x) && aligned16(wg))
+    return launch_router_tc(x, wg, T, D, E, K, weights, indices, row_amax, status, scratch, st);
   int Epad = 8;
   while (Epad < E) Epad <<= 1;
   auto xp = static_cast<const __nv_bfloat16*>(x);

@@ -99,6 +99,7 @@ class ExpertParallelMoE:
         self.w_gate = w_gate.contiguous()
         self.wg, self.wu, self.wd = (t.contiguous() for t in (experts_w_gate, experts_w_up, experts_w_down))
         self.sg, self.su, self.sd = (t.to(torch.float32).contiguous() for t in (scales_gate, scales_up, scales_down))
+        self.block = self.sg.dim() == 3          # [E_local, in/128, out/128] inverse scales: block recipe
         self.D, self.H = self.wg.shape[1], self.wg.shape[2]
         self.dev = self.wg.device
         assert self.w_gate.shape == (self.D, num_experts)
@@ -114,9 +115,13 @@ class ExpertParallelMoE:
         i32, f32 = torch.int32, torch.float32
         new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         weights, indices, row_amax = new(T, K, dtype=f32), new(T, K, dtype=i32), new(T, dtype=f32)
+        need = lib.bwmoe_router_scratch_bytes(T, D, E, K)
+        rs = new(need, dtype=torch.uint8) if need else None
         _lib.check(lib.bwmoe_router(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, weights.data_ptr(),
-                                    indices.data_ptr(), row_amax.data_ptr(), st))
+                                    indices.data_ptr(), row_amax.data_ptr(), rs.data_ptr() if need else None, need, st))
         offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
+        if self.block:
+            return self._forward_block(x, weights, indices, offsets, pos, row_slot, row_expert, host_in)
         stats = torch.zeros(2 * E, dtype=f32, device=dev)          # [amax | counts-as-int32 bits]
         status = torch.zeros(4, dtype=i32, device=dev)
         scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=torch.uint8)
@@ -159,9 +164,50 @@ class ExpertParallelMoE:
         out = new(T, D, dtype=torch.bfloat16)
         _lib.check(lib.bwmoe_combine(y_home.data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K, out.data_ptr(), st))
         self.last_status = status
+        return self._finish(out, host_in)
+
+    def _finish(self, out, host_in):
         if host_in:
             host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
             host.copy_(out, non_blocking=True)
-            torch.cuda.current_stream(dev).synchronize()
+            torch.cuda.current_stream(self.dev).synchronize()
             return host
         return out
+
+    def _forward_block(self, x, weights, indices, offsets, pos, row_slot, row_expert, host_in):
+        """Block-scale recipe: activation scales are per token, so only row counts are exchanged."""
+        lib, dev, E, K, D, H, el = _lib.lib(), self.dev, self.E, self.K, self.D, self.H, self.el
+        T = x.shape[0]
+        M = T * K
+        st = torch.cuda.current_stream(dev).cuda_stream
+        i32, f32 = torch.int32, torch.float32
+        new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
+        status = torch.zeros(4, dtype=i32, device=dev)
+        scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=torch.uint8)
+        _lib.check(lib.bwmoe_permute_plan(indices.data_ptr(), None, T, E, K, offsets.data_ptr(), pos.data_ptr(),
+                                          row_slot.data_ptr(), row_expert.data_ptr(), None, status.data_ptr(),
+                                          scratch.data_ptr(), st))
+        counts = new(self.world * E, dtype=i32)
+        dist.all_gather_into_tensor(counts, (offsets[1:] - offsets[:-1]).contiguous(), group=self.group)
+        nd, nh = (D + 127) // 128, (H + 127) // 128
+        xq, x_inv = new(M, D, dtype=torch.uint8), new(M, nd, dtype=f32)
+        _lib.check(lib.bwmoe_gather_quant_group(x.data_ptr(), row_slot.data_ptr(), M, D, K, xq.data_ptr(),
+                                                x_inv.data_ptr(), st))
+        plan = ExchangePlan(counts.view(self.world, E), self.rank)
+        xq_local = dispatch(xq, plan, self.group)
+        xinv_local = dispatch(x_inv, plan, self.group)
+        R = plan.rows_local
+        y_local = new(R, D, dtype=torch.bfloat16)
+        if R > 0:
+            hq, h_inv = new(R, H, dtype=torch.uint8), new(R, nh, dtype=f32)
+            _lib.check(lib.bwmoe_gateup_swiglu_block(xq_local.data_ptr(), xinv_local.data_ptr(), plan.offsets.data_ptr(),
+                                                     self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                                     self.su.data_ptr(), R, D, H, el, hq.data_ptr(), h_inv.data_ptr(),
+                                                     status.data_ptr(), st))
+            _lib.check(lib.bwmoe_down_block(hq.data_ptr(), h_inv.data_ptr(), plan.offsets.data_ptr(), self.wd.data_ptr(),
+                                            self.sd.data_ptr(), R, D, H, el, y_local.data_ptr(), status.data_ptr(), st))
+        y_home = combine_back(y_local, plan, M, self.group)
+        out = new(T, D, dtype=torch.bfloat16)
+        _lib.check(lib.bwmoe_combine(y_home.data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K, out.data_ptr(), st))
+        self.last_status = status
+        return self._finish(out, host_in)

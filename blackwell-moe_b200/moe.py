@@ -66,11 +66,14 @@ def top_k_router(hidden: torch.Tensor, gate_w: torch.Tensor, k: int):
     T, D = hidden.shape
     E = gate_w.shape[1]
     hidden, gate_w = _contig(hidden, "hidden"), _contig(gate_w, "gate_w")
+    lib = _lib.lib()
     with torch.cuda.device(dev):
         w_out = torch.empty((T, k), device=dev, dtype=torch.float32)
         i_out = torch.empty((T, k), device=dev, dtype=torch.int32)
-        _lib.check(_lib.lib().bwmoe_router(hidden.data_ptr(), gate_w.data_ptr(), T, D, E, k,
-                                           w_out.data_ptr(), i_out.data_ptr(), None, _stream(dev)))
+        need = lib.bwmoe_router_scratch_bytes(T, D, E, k)
+        scratch = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
+        _lib.check(lib.bwmoe_router(hidden.data_ptr(), gate_w.data_ptr(), T, D, E, k, w_out.data_ptr(),
+                                    i_out.data_ptr(), None, scratch.data_ptr() if need else None, need, _stream(dev)))
     return w_out, i_out
 
 
@@ -117,8 +120,9 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
     with torch.cuda.device(dev):
         ptrs = [t.data_ptr() for t in weights]
         if scales_gate.dim() == 3:
-            if not x.is_cuda:
-                raise ValueError("the block-scale recipe takes CUDA activations")
+            host_x = not x.is_cuda
+            if host_x:      # host activations: copy in, run, copy out and wait (pinned memory makes the copies async)
+                x = x.to(dev, non_blocking=True)
             _require_cuda(x, w_gate)
             need = lib.bwmoe_workspace_bytes_block(T, D, H, E, top_k)
             if need == 0:
@@ -127,6 +131,11 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
             out = torch.empty_like(x)
             _lib.check(lib.bwmoe_moe_forward_block(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
                                                    ws.data_ptr(), ws.numel(), _stream(dev)))
+            if host_x:
+                host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+                host.copy_(out, non_blocking=True)
+                torch.cuda.current_stream(dev).synchronize()
+                return host
             return out
         if x.is_cuda:
             _require_cuda(x, w_gate)

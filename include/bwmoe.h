@@ -99,10 +99,15 @@ int bwmoe_read_status(void* d_workspace, void* stream, int32_t* status);
  * Selection is on the exactly-rounded fp32 logits; equal logits go to the lower
  * expert id.  d_weights[T,K] fp32 sum to 1, d_indices[T,K] int32 are ordered by
  * decreasing probability.  d_row_amax[T] (optional, may be null) receives
- * max|x[t,:]|.  Any E in [1,256], any K in [1,min(E,32)].
+ * max|x[t,:]|.  Any E in [1,256], any K in [1,min(E,32)].  d_scratch is optional: with
+ * bwmoe_router_scratch_bytes() bytes of it (non-zero for wide gates and large batches) the
+ * logits are computed on the tensor cores and only the few experts near the cut are
+ * re-evaluated exactly; the selection is the same either way.
  */
+size_t bwmoe_router_scratch_bytes(int T, int D, int E, int K);
 int bwmoe_router(const void* d_x, const void* d_w_gate, int T, int D, int E, int K,
-                 float* d_weights, int32_t* d_indices, float* d_row_amax, void* stream);
+                 float* d_weights, int32_t* d_indices, float* d_row_amax,
+                 void* d_scratch, size_t scratch_bytes, void* stream);
 
 /*
  * Whole block: router -> permute + segment-amax + E4M3 quant -> grouped gate+up

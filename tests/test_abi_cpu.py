@@ -43,11 +43,11 @@ def test_workspace_sizes():
 
 def test_errors_are_reported_before_any_device_work():
     lib = bw.lib()
-    rc = lib.bwmoe_router(None, None, 0, 16, 8, 2, None, None, None, None)
+    rc = lib.bwmoe_router(None, None, 0, 16, 8, 2, None, None, None, None, 0, None)
     assert rc == -1 and "router" in _lib.last_error()
-    rc = lib.bwmoe_router(None, None, 4, 16, 8, 2, None, None, None, None)
+    rc = lib.bwmoe_router(None, None, 4, 16, 8, 2, None, None, None, None, 0, None)
     assert rc == -6
-    rc = lib.bwmoe_router(None, None, 4, 16, 300, 2, None, None, None, None)
+    rc = lib.bwmoe_router(None, None, 4, 16, 300, 2, None, None, None, None, 0, None)
     assert rc == -4
     rc = lib.bwmoe_moe_forward(*([None] * 8), 4, 20, 32, 8, 2, None, None, 0, None)
     assert rc == -1

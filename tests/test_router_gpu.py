@@ -30,7 +30,9 @@ def test_router_matches_reference_fixtures(golden):
 
 
 @pytest.mark.parametrize("T,D,E,K", [(1, 4096, 8, 2), (7, 2048, 64, 6), (300, 2048, 128, 8), (2500, 2048, 256, 8),
-                                     (33, 1024, 12, 12), (64, 512, 1, 1), (5000, 4096, 8, 2), (129, 272, 200, 32)])
+                                     (33, 1024, 12, 12), (64, 512, 1, 1), (5000, 4096, 8, 2), (129, 272, 200, 32),
+                                     (4096, 2048, 64, 6), (3000, 1024, 128, 8), (1500, 512, 24, 4),
+                                     (1100, 2048, 256, 8), (2048, 1024, 16, 2), (1024, 320, 40, 8)])
 def test_router_bit_exact_vs_canonical(T, D, E, K):
     g = torch.Generator().manual_seed(T + E)
     x = torch.randn(T, D, generator=g).to(BF16)
@@ -60,3 +62,24 @@ def test_router_ties_go_to_lower_id_and_near_ties_are_resolved_exactly():
     wt, idx = _route(z, w2, 4)
     assert torch.equal(idx, torch.arange(4, dtype=torch.int32).repeat(3, 1))
     torch.testing.assert_close(wt, torch.full((3, 4), 0.25))
+
+
+def test_tensor_core_router_ties_and_candidate_overflow():
+    """Large batch, wide gate: the tensor-core path.  Identical gate columns make every expert
+    tie, which overflows the per-token candidate list and must fall back to the exact path;
+    a few distinct columns exercise near ties inside the candidate list."""
+    T, D, E, K = 1200, 512, 64, 6
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(T, D, generator=g).to(BF16)
+    col = (torch.randn(D, 1, generator=g) * 0.02).to(BF16)
+    w = col.repeat(1, E).contiguous()
+    _, idx = _route(x, w, K)
+    assert torch.equal(idx, torch.arange(K, dtype=torch.int32).repeat(T, 1))
+    w2 = w.clone()
+    for e in (3, 17, 40, 41, 63):
+        w2[e % D, e] = (w2[e % D, e].float() * 1.02).to(BF16)
+        w2[(7 * e) % D, e] = (w2[(7 * e) % D, e].float() * 0.97).to(BF16)
+    wt, idx = _route(x, w2, K)
+    wr, ir = oracle.router_canonical(x, w2, K)
+    assert torch.equal(idx, ir)
+    torch.testing.assert_close(wt, wr, rtol=1e-3, atol=1e-4)
