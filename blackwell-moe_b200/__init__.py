@@ -17,6 +17,8 @@ from .moe import (
     top_k_router,
 )
 from ._lib import lib, library_path, BwmoeError
+from .modules import (FP8MixtralSparseMoeBlock, FP8MoELayer, FP8SharedExpert, fp8_dense_mlp,
+                      patch_deepseek_moe_with_store, patch_shared_experts)
 
 # The reference exports the same forward under several version names
 # (src/blackwell_moe/__init__.py:14-15); all of them map to the one CUDA path.
@@ -27,7 +29,8 @@ fp8_moe_forward_small_e = fp8_moe_forward
 __version__ = "0.1.0"
 
 __all__ = [
-    "FP8_MAX_E4M3", "BwmoeError", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_routed",
+    "FP8_MAX_E4M3", "BwmoeError", "FP8MixtralSparseMoeBlock", "FP8MoELayer", "FP8SharedExpert", "fp8_dense_mlp",
+    "patch_deepseek_moe_with_store", "patch_shared_experts", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_routed",
     "fp8_moe_forward_small_e", "fp8_moe_forward_v3", "fp8_moe_forward_v4", "lib", "library_path",
     "moe_stage_views", "quant_fp8_block_128", "quant_fp8_e4m3", "quantize_expert_weights",
     "quantize_expert_weights_block", "top_k_router",

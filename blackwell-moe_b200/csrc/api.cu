@@ -84,7 +84,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
 // Workspace of the block-scale recipe: no bf16 h, no segment statistics; per-row group scales instead.
 struct BlockLayout {
   size_t status, zero_end, offsets, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, plan_scratch;
-  size_t router_scratch, router_scratch_bytes, xq, x_inv, hq, h_inv, y, total;
+  size_t router_scratch, router_scratch_bytes, xq_tok, inv_tok, xq, x_inv, hq, h_inv, y, total;
 };
 
 bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
@@ -109,6 +109,8 @@ bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
   L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
   L->router_scratch = take(L->router_scratch_bytes);
+  L->xq_tok = take((size_t)T * D);
+  L->inv_tok = take(sizeof(float) * (size_t)T * ((D + 127) / 128));
   L->xq = take(M * D);
   L->x_inv = take(sizeof(float) * M * ((D + 127) / 128));
   L->hq = take(M * H);
@@ -145,7 +147,7 @@ int check_forward_args(const char* who, const void* x, const void* wg, const voi
 int run_pipeline(const void* x, const float* weights, const int32_t* indices, const float* row_amax,
                  const void* wg, const void* wu, const void* wd, const float* sg, const float* su,
                  const float* sd, int T, int D, int H, int E, int K, void* out, void* ws, const Layout& L,
-                 cudaStream_t st) {
+                 cudaStream_t st, float out_scale = 1.0f, const void* residual = nullptr) {
   const int M = T * K;
   int32_t* status = at<int32_t>(ws, L.status);
   int32_t* offsets = at<int32_t>(ws, L.offsets);
@@ -169,7 +171,7 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   if ((rc = launch_down(at<void>(ws, L.hq), offsets, scale_h, wd, sd, M, D, H, E, at<void>(ws, L.y), status,
                         at<void>(ws, L.gemm_scratch), st)))
     return rc;
-  return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st);
+  return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st, out_scale, residual);
 }
 
 // max|x| per row, for callers that bring their own routing
@@ -275,6 +277,56 @@ int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const v
                              L.router_scratch_bytes, at<int32_t>(ws, L.status)))
     return rc;
   return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
+}
+
+int bwmoe_moe_forward_ex(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                         const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                         float routed_scale, const void* residual, void* out, void* ws, size_t ws_bytes,
+                         void* stream) {
+  Layout L;
+  if (int rc = check_forward_args("moe_forward_ex", x, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, ws_bytes, &L, 0))
+    return rc;
+  BWMOE_REQUIRE(w_gate != nullptr, BWMOE_ERR_NULL, "moe_forward_ex: w_gate is null");
+  BWMOE_REQUIRE(residual == nullptr || aligned16(residual), BWMOE_ERR_BAD_ALIGN, "moe_forward_ex: residual alignment");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* weights = at<float>(ws, L.topk_w);
+  int32_t* indices = at<int32_t>(ws, L.topk_idx);
+  float* row_amax = at<float>(ws, L.row_amax);
+  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, row_amax, st, at<void>(ws, L.router_scratch),
+                             L.router_scratch_bytes, at<int32_t>(ws, L.status)))
+    return rc;
+  return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st,
+                      routed_scale, residual);
+}
+
+int bwmoe_dense_mlp(const void* x, const void* wg, const void* wu, const void* wd, const float* sg, const float* su,
+                    const float* sd, int T, int D, int H, void* out, void* ws, size_t ws_bytes, void* stream) {
+  Layout L;
+  if (int rc = check_forward_args("dense_mlp", x, wg, wu, wd, sg, su, sd, T, D, H, 1, 1, out, ws, ws_bytes, &L, 0))
+    return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // one segment with every row: row_expert = 0 everywhere, whole-tensor scales for x and h
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  BWMOE_CUDA_OK(cudaMemsetAsync(at<void>(ws, L.row_expert), 0, sizeof(int32_t) * (size_t)T, st));
+  float* row_amax = at<float>(ws, L.row_amax);
+  int32_t* offsets = at<int32_t>(ws, L.offsets);
+  int32_t* status = at<int32_t>(ws, L.status);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  int rc;
+  if ((rc = launch_dense_prepare(row_amax, T, offsets, at<float>(ws, L.amax_x), st))) return rc;
+  if ((rc = launch_quant_rows_from_amax(x, at<int32_t>(ws, L.row_expert), at<float>(ws, L.amax_x), T, D,
+                                        at<void>(ws, L.xq), at<float>(ws, L.scale_x), st)))
+    return rc;
+  if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, at<float>(ws, L.scale_x), wg, wu, sg, su, T, D, H, 1,
+                          at<void>(ws, L.h), at<float>(ws, L.amax_h), status, at<void>(ws, L.gemm_scratch), st)))
+    return rc;
+  if ((rc = launch_requant(at<void>(ws, L.h), at<int32_t>(ws, L.row_expert), at<float>(ws, L.amax_h), T, H,
+                           at<void>(ws, L.hq), st, at<float>(ws, L.scale_h))))
+    return rc;
+  return launch_down(at<void>(ws, L.hq), offsets, at<float>(ws, L.scale_h), wd, sd, T, D, H, 1, out, status,
+                     at<void>(ws, L.gemm_scratch), st);
 }
 
 int bwmoe_moe_forward_routed(const void* x, const float* weights, const int32_t* indices, const void* wg,
@@ -384,8 +436,8 @@ int bwmoe_moe_forward_block(const void* x, const void* w_gate, const void* wg, c
   if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
                         at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
     return rc;
-  if ((rc = launch_gather_quant_group(x, at<int32_t>(ws, L.row_slot), M, D, K, at<void>(ws, L.xq),
-                                      at<float>(ws, L.x_inv), st)))
+  if ((rc = launch_quant_then_gather_group(x, at<int32_t>(ws, L.row_slot), T, D, K, at<void>(ws, L.xq_tok),
+                                           at<float>(ws, L.inv_tok), at<void>(ws, L.xq), at<float>(ws, L.x_inv), st)))
     return rc;
   if ((rc = launch_gateup_block(at<void>(ws, L.xq), at<float>(ws, L.x_inv), offsets, wg, wu, inv_g, inv_u, M, D, H, E,
                                 at<void>(ws, L.hq), at<float>(ws, L.h_inv), status, st)))

@@ -83,7 +83,10 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
                    void* hq, cudaStream_t st, float* scales_from_amax_out = nullptr);
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
-                   void* out, cudaStream_t st);
+                   void* out, cudaStream_t st, float scale = 1.0f, const void* residual = nullptr);
+int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* seg_amax, cudaStream_t st);
+int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
+                                void* xq, float* scales_out, cudaStream_t st);
 size_t gemm_scratch_bytes(int M, int D, int H, int E);
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
@@ -94,6 +97,8 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
 // 128x128 block-scale recipe
 int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,
                               cudaStream_t st);
+int launch_quant_then_gather_group(const void* x, const int32_t* row_slot, int T, int D, int K, void* xq_tok,
+                                   float* inv_tok, void* xq, float* x_inv, cudaStream_t st);
 int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
                         const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
                         int32_t* status, cudaStream_t st);

@@ -385,6 +385,22 @@ quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __
   }
 }
 
+// ---- copy quantised token rows (codes + group scales) into expert-contiguous order ----
+// One thread per 16 bytes of codes; the first threads of a row also move its scales.
+__global__ void __launch_bounds__(256)
+gather_quantised_rows_kernel(const uint8_t* __restrict__ xq_tok, const float* __restrict__ inv_tok,
+                             const int32_t* __restrict__ row_slot, int M, int D, int K, int groups,
+                             uint8_t* __restrict__ xq, float* __restrict__ x_inv) {
+  const int vec_per_row = D / 16;
+  const unsigned chunks_per_row = (vec_per_row + blockDim.x - 1) / blockDim.x;
+  const int m = (int)(blockIdx.x / chunks_per_row);
+  const int v = (int)(blockIdx.x % chunks_per_row) * blockDim.x + threadIdx.x;
+  const size_t t = (size_t)(row_slot[m] / K);
+  if (v < vec_per_row)
+    reinterpret_cast<uint4*>(xq + (size_t)m * D)[v] = reinterpret_cast<const uint4*>(xq_tok + t * D)[v];
+  if (v < groups) x_inv[(size_t)m * groups + v] = inv_tok[t * groups + v];
+}
+
 int check_block(const char* who, int M, int D, int H, int E) {
   BWMOE_REQUIRE(M > 0 && D > 0 && H > 0 && E > 0, BWMOE_ERR_BAD_SHAPE, "%s: M=%d D=%d H=%d E=%d", who, M, D, H, E);
   BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
@@ -405,6 +421,22 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
   const unsigned grid = (unsigned)((size_t)M * ceil_div(vecs_per_row, threads * kGroupVecs));
   quant_group_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
                                                     static_cast<uint8_t*>(xq), x_inv);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+// Block recipe: scales are per token, so tokens are quantised once in token order and the FP8 rows
+// are then copied into expert order (the codes are half the bytes and fit in L2 when re-read K times).
+int launch_quant_then_gather_group(const void* x, const int32_t* row_slot, int T, int D, int K, void* xq_tok,
+                                   float* inv_tok, void* xq, float* x_inv, cudaStream_t st) {
+  if (int rc = launch_gather_quant_group(x, nullptr, T, D, 1, xq_tok, inv_tok, st)) return rc;
+  BWMOE_REQUIRE(row_slot && xq && x_inv, BWMOE_ERR_NULL, "quant_then_gather_group: null pointer");
+  const int M = T * K, groups = ceil_div(D, 128), vec_per_row = D / 16;
+  int threads = 32;
+  while (threads < 256 && threads < vec_per_row) threads <<= 1;
+  const unsigned grid = (unsigned)((size_t)M * ceil_div(vec_per_row, threads));
+  gather_quantised_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const uint8_t*>(xq_tok), inv_tok, row_slot, M, D,
+                                                        K, groups, static_cast<uint8_t*>(xq), x_inv);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

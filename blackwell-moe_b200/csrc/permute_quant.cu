@@ -243,9 +243,12 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
 }
 
 // ---- out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ) ----
+// Optional tail (the block glue of FP8MoELayer.forward, src/blackwell_moe/runtime/deepseek_patch.py:51-53):
+//   out = bf16( bf16(routed * scale) + residual ) with routed = the bf16 sum above.
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ pos,
-               const float* __restrict__ weights, int T, int D, int K, __nv_bfloat16* __restrict__ out) {
+               const float* __restrict__ weights, int T, int D, int K, __nv_bfloat16* __restrict__ out,
+               float scale, const __nv_bfloat16* __restrict__ residual) {
   const int vec_per_row = D / 8;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)T * vec_per_row) return;
@@ -264,6 +267,21 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
       const float2 f = __bfloat1622float2(q[i]);
       acc[2 * i] += bf16_round(f.x * w);
       acc[2 * i + 1] += bf16_round(f.y * w);
+    }
+  }
+  if (scale != 1.0f) {
+    const float sb = bf16_round(scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * sb);
+  }
+  if (residual != nullptr) {
+    const uint4 raw = reinterpret_cast<const uint4*>(residual + (size_t)t * D)[v];
+    const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(q[i]);
+      acc[2 * i] = bf16_round(acc[2 * i]) + f.x;
+      acc[2 * i + 1] = bf16_round(acc[2 * i + 1]) + f.y;
     }
   }
   uint4 o;
@@ -398,15 +416,51 @@ int launch_requant(const void* h, const int32_t* row_expert, const float* scales
   return BWMOE_OK;
 }
 
+// ---- dense (always-on) expert: one segment holding every row ----
+__global__ void __launch_bounds__(1024)
+dense_prepare_kernel(const float* __restrict__ row_amax, int T, int32_t* __restrict__ offsets,
+                     float* __restrict__ seg_amax) {
+  __shared__ float red[32];
+  float m = 0.f;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) m = fmaxf(m, row_amax[t]);
+  for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+    seg_amax[0] = m;
+    offsets[0] = 0;
+    offsets[1] = T;
+  }
+}
+
+int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* seg_amax, cudaStream_t st) {
+  dense_prepare_kernel<<<1, 1024, 0, st>>>(row_amax, T, offsets, seg_amax);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+// rows in place (no gather), scale derived from the segment amax and published
+int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
+                                void* xq, float* scales_out, cudaStream_t st) {
+  const int threads = quant_block_threads(W / 8);
+  quant_rows_kernel<false, true><<<quant_grid(M, W / 8, threads), threads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), nullptr, row_expert, seg_amax, scales_out, M, W, 1,
+      static_cast<uint8_t*>(xq));
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
-                   void* out, cudaStream_t st) {
+                   void* out, cudaStream_t st, float scale, const void* residual) {
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 8 == 0, BWMOE_ERR_BAD_SHAPE, "combine: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(y && pos && weights && out, BWMOE_ERR_NULL, "combine: null pointer");
   BWMOE_REQUIRE(aligned16(y) && aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine: pointers must be 16-byte aligned");
   const size_t n = (size_t)T * (D / 8);
   combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(y), pos,
                                                               weights, T, D, K,
-                                                              static_cast<__nv_bfloat16*>(out));
+                                                              static_cast<__nv_bfloat16*>(out), scale,
+                                                              static_cast<const __nv_bfloat16*>(residual));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

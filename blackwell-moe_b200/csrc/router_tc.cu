@@ -5,16 +5,18 @@
 //   1. transpose_gate_kernel : w_gate[D,E] -> w_gate^T[E,D] (so that one expert's column is
 //                              contiguous) and the squared column norms
 //   2. tc_logits_kernel      : logits = x . w_gate with tcgen05.mma kind::f16 (bf16 inputs, fp32
-//                              accumulators in tensor memory); each epilogue thread owns one
-//                              token and keeps its 12 best (logit, expert) pairs, sorted
-//   3. refine_kernel         : one warp per token.  The tensor-core logits are only trusted to
-//                              +-2^-14 * |x|_2 * |w_e|_2 (four times the worst case of a
-//                              truncating fp32 accumulation of 4096 products); every expert whose
-//                              tensor-core logit is within twice that of the K-th best is a
-//                              candidate.  The candidates' logits are recomputed with the blocked
-//                              compensated fp32 sum of the SIMT routers (error bound known), near
-//                              ties among them in fp64, and the final top-K is taken from those.
-//                              A token with more than 12 candidates is recomputed over all experts.
+//                              accumulators in tensor memory), written to a [T, E] fp32 scratch
+//   3. refine_kernel         : one warp per token.  Warp-wide selection of the 12 best tensor-core
+//                              logits, sorted.  Those logits are only trusted to
+//                              t = 2^-14 * |x|_2 * |w_e|_2 (four times the worst case of a
+//                              truncating fp32 accumulation of 4096 products).  Every expert within
+//                              2t of the K-th best is a candidate; candidates more than 2t apart are
+//                              certainly in the right order already.  Runs of candidates that are
+//                              closer than 2t to a neighbour are recomputed with the blocked
+//                              compensated fp32 sum of the SIMT routers (error bound known), and in
+//                              fp64 if still within that bound of each other; the final top-K is
+//                              read off the mixed list.  A token whose 12 best all fall within the
+//                              cut is recomputed over all experts by the exact fallback kernel.
 // An expert outside the candidate set has an exact logit below that of K candidates, so the
 // result equals the exact selection.
 #include "sm100_gemm.cuh"
@@ -56,8 +58,7 @@ transpose_gate_kernel(const __nv_bfloat16* __restrict__ wg, int D, int E, __nv_b
 
 // ---- 2. tensor-core logits + per-token candidate list ------------------------------------
 struct TcParams {
-  float* cand_val;      // [T, L_CAND] sorted descending
-  int32_t* cand_idx;    // [T, L_CAND]
+  float* logits;        // [T, n_mma] fp32
   int32_t* status;
   int T, D, E, n_chunks, n_mma;   // n_chunks = ceil(E/64) weight boxes; n_mma = MMA N (multiple of 16)
 };
@@ -170,44 +171,22 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
-      float lv[L_CAND];
-      int li[L_CAND];
-#pragma unroll
-      for (int j = 0; j < L_CAND; ++j) lv[j] = -INFINITY, li[j] = 0x7fffffff;
+      const int row = tile * BM + r_in_tile;
+      float* dst = p.logits + (size_t)row * p.n_mma;
       for (int c = 0; c < p.n_mma; c += 32) {
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         tmem_ld_wait();
+        if (row < p.T) {
 #pragma unroll
-        for (int q = 0; q < 32; ++q) {
-          float v = __uint_as_float(r[q]);
-          int id = c + q;
-          if (id < p.E && (v > lv[L_CAND - 1] || (v == lv[L_CAND - 1] && id < li[L_CAND - 1]))) {
-            // sorted insert: bubble the new pair up from the bottom
-            lv[L_CAND - 1] = v, li[L_CAND - 1] = id;
-#pragma unroll
-            for (int j = L_CAND - 1; j > 0; --j) {
-              const bool up = lv[j] > lv[j - 1] || (lv[j] == lv[j - 1] && li[j] < li[j - 1]);
-              const float tv = up ? lv[j - 1] : lv[j];
-              const int ti = up ? li[j - 1] : li[j];
-              lv[j - 1] = up ? lv[j] : lv[j - 1];
-              li[j - 1] = up ? li[j] : li[j - 1];
-              lv[j] = tv, li[j] = ti;
-            }
-          }
+          for (int v = 0; v < 8; ++v)
+            if (c + 4 * v < p.n_mma)
+              reinterpret_cast<uint4*>(dst + c)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-      const int row = tile * BM + r_in_tile;
-      if (row < p.T) {
-#pragma unroll
-        for (int j = 0; j < L_CAND; ++j) {
-          p.cand_val[(size_t)row * L_CAND + j] = lv[j];
-          p.cand_idx[(size_t)row * L_CAND + j] = li[j];
-        }
-      }
     }
   }
   if (*abort_flag) {
@@ -230,18 +209,44 @@ __device__ __forceinline__ void kahan_add_r(float& sum, float& comp, float y) {
 
 __global__ void __launch_bounds__(256)
 refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wgt,
-              const float* __restrict__ wnorm2, const float* __restrict__ cand_val,
-              const int32_t* __restrict__ cand_idx, int T, int D, int E, int K, float* __restrict__ weights,
-              int32_t* __restrict__ indices, float* __restrict__ row_amax, int32_t* __restrict__ fallback_count,
+              const float* __restrict__ wnorm2, const float* __restrict__ logits, int ld_logits, int T, int D,
+              int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
+              float* __restrict__ row_amax, int32_t* __restrict__ fallback_count,
               int32_t* __restrict__ fallback_list) {
   const int lane = threadIdx.x & 31;
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (tok >= T) return;
   const __nv_bfloat16* xrow = x + (size_t)tok * D;
-  // candidate list: lane j < L_CAND holds entry j
-  const float cv = lane < L_CAND ? cand_val[(size_t)tok * L_CAND + lane] : -INFINITY;
-  const int ci = lane < L_CAND ? cand_idx[(size_t)tok * L_CAND + lane] : 0x7fffffff;
-  // |x|_2, max|x|
+
+  // ---- the 12 best tensor-core logits, sorted by (value desc, id asc): lane j keeps entry j ----
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? logits[(size_t)tok * ld_logits + e] : -INFINITY;
+  }
+  float cv = -INFINITY;
+  int ci = 0x7fffffff;
+  unsigned taken = 0;
+  const int n_list = E < L_CAND ? E : L_CAND;
+  for (int it = 0; it < n_list; ++it) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      if (!((taken >> j) & 1u) && e < E && (v[j] > bv || (v[j] == bv && e < bi))) bv = v[j], bi = e;
+    }
+    for (int off = 16; off; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (lane == it) cv = bv, ci = bi;
+  }
+
+  // ---- |x|_2, max|x|, largest column norm ----
   float xsq = 0.f, xmax = 0.f;
   for (int d0 = lane * 8; d0 < D; d0 += 256) {
     const uint4 raw = *reinterpret_cast<const uint4*>(xrow + d0);
@@ -262,76 +267,84 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   for (int e = lane; e < E; e += 32) wn2 = fmaxf(wn2, wnorm2[e]);
   for (int off = 16; off; off >>= 1) wn2 = fmaxf(wn2, __shfl_xor_sync(0xffffffffu, wn2, off));
   const float xw = sqrtf(xsq) * sqrtf(wn2) * 1.002f;      // >= sum_d |x_d w_de| for every expert
-  // candidates: list prefix whose tensor-core logit is within 2 * trust of the K-th
+  const float t2 = 2.f * kTcTrust * xw;                   // two logits further apart are ordered for sure
+
+  // ---- candidates: the list prefix within 2t of the K-th entry ----
   const float kth = __shfl_sync(0xffffffffu, cv, K - 1);
-  const float cut = kth - 2.f * kTcTrust * xw;
-  const unsigned in_mask = __ballot_sync(0xffffffffu, lane < L_CAND && ci < E && cv >= cut);
-  const int n_cand = __popc(in_mask);                      // a prefix: the list is sorted
+  const unsigned in_mask = __ballot_sync(0xffffffffu, lane < n_list && cv >= kth - t2);
+  const int n_cand = __popc(in_mask);
   if (n_cand >= L_CAND && E > L_CAND) {
-    // too many near-equal experts for the list: leave this token to the all-expert kernel
+    // the list may be missing experts that are just as close: all-expert exact kernel
     if (lane == 0) fallback_list[atomicAdd(fallback_count, 1)] = tok;
     return;
   }
-  // blocked + compensated fp32 logits of the candidates (same scheme and bound as the SIMT routers)
-  float acc[L_CAND], comp[L_CAND], inner[L_CAND];
-  int cid[L_CAND];
+  // ---- runs of candidates closer than 2t to a neighbour need exact logits ----
+  const float prev = __shfl_up_sync(0xffffffffu, cv, 1);
+  const bool close_up = lane > 0 && lane < n_cand && prev - cv <= t2;
+  const unsigned up_mask = __ballot_sync(0xffffffffu, close_up);
+  const unsigned redo = (up_mask | (up_mask >> 1)) & ((1u << n_cand) - 1u);   // both members of every close pair
+  float mine = cv;
+  if (redo != 0u) {
+    float acc[L_CAND], comp[L_CAND], inner[L_CAND];
+    int cid[L_CAND];
 #pragma unroll
-  for (int c = 0; c < L_CAND; ++c) {
-    acc[c] = 0.f, comp[c] = 0.f, inner[c] = 0.f;
-    cid[c] = __shfl_sync(0xffffffffu, ci, c);
-  }
-  int inner_n = 0;
-  for (int d0 = lane * 8; d0 < D; d0 += 256) {
-    const uint4 xraw = *reinterpret_cast<const uint4*>(xrow + d0);
-    const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xraw);
-    float xv[8];
+    for (int c = 0; c < L_CAND; ++c) {
+      acc[c] = 0.f, comp[c] = 0.f, inner[c] = 0.f;
+      cid[c] = __shfl_sync(0xffffffffu, ci, c);
+    }
+    int inner_n = 0;
+    for (int d0 = lane * 8; d0 < D; d0 += 256) {
+      const uint4 xraw = *reinterpret_cast<const uint4*>(xrow + d0);
+      const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+      float xv[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(px[j]);
-      xv[2 * j] = f.x, xv[2 * j + 1] = f.y;
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(px[j]);
+        xv[2 * j] = f.x, xv[2 * j + 1] = f.y;
+      }
+#pragma unroll
+      for (int c = 0; c < L_CAND; ++c) {
+        if ((redo >> c) & 1u) {
+          const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(wgt + (size_t)cid[c] * D + d0));
+          const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(pw[j]);
+            inner[c] = fmaf(xv[2 * j], f.x, inner[c]);
+            inner[c] = fmaf(xv[2 * j + 1], f.y, inner[c]);
+          }
+        }
+      }
+      inner_n += 8;
+      if (inner_n == kInnerR) {
+#pragma unroll
+        for (int c = 0; c < L_CAND; ++c) {
+          kahan_add_r(acc[c], comp[c], inner[c]);
+          inner[c] = 0.f;
+        }
+        inner_n = 0;
+      }
     }
 #pragma unroll
     for (int c = 0; c < L_CAND; ++c) {
-      if (c < n_cand) {
-        const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(wgt + (size_t)cid[c] * D + d0));
-        const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(pw[j]);
-          inner[c] = fmaf(xv[2 * j], f.x, inner[c]);
-          inner[c] = fmaf(xv[2 * j + 1], f.y, inner[c]);
-        }
-      }
+      kahan_add_r(acc[c], comp[c], inner[c]);
+      float s = __fsub_rn(acc[c], comp[c]);
+      for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      if (lane == c && ((redo >> c) & 1u)) mine = s;
     }
-    inner_n += 8;
-    if (inner_n == kInnerR) {
-#pragma unroll
-      for (int c = 0; c < L_CAND; ++c) {
-        kahan_add_r(acc[c], comp[c], inner[c]);
-        inner[c] = 0.f;
-      }
-      inner_n = 0;
+    // recomputed logits carry a known bound; pairs of them still inside it go to fp64
+    const float gamma = (float)(kInnerR + 8) * 5.9604645e-8f * 1.05f;
+    const float thr = 2.f * gamma * xw + fabsf(kth) * 1.0e-6f + 1e-30f;
+    unsigned exact = 0u;
+    for (int c = 0; c < L_CAND; ++c) {
+      const float vc = __shfl_sync(0xffffffffu, mine, c);
+      const bool hit = ((redo >> c) & 1u) && ((redo >> lane) & 1u) && lane < L_CAND && c != lane &&
+                       fabsf(vc - mine) <= thr;
+      exact |= __ballot_sync(0xffffffffu, hit);
     }
-  }
-  float mine = -INFINITY;    // lane c ends up with the logit of candidate c
-#pragma unroll
-  for (int c = 0; c < L_CAND; ++c) {
-    kahan_add_r(acc[c], comp[c], inner[c]);
-    float v = __fsub_rn(acc[c], comp[c]);
-    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    if (lane == c && c < n_cand) mine = v;
-  }
-  // near ties among the candidates -> exact fp64 for all of them
-  const float gamma = (float)(kInnerR + 8) * 5.9604645e-8f * 1.05f;
-  const float thr = 2.f * gamma * xw + fabsf(kth) * 1.0e-6f + 1e-30f;
-  bool ambiguous = false;
-  for (int c = 0; c < L_CAND; ++c) {
-    const float vc = __shfl_sync(0xffffffffu, mine, c);
-    if (lane < n_cand && c < n_cand && c != lane && fabsf(vc - mine) <= thr) ambiguous = true;
-  }
-  if (__any_sync(0xffffffffu, ambiguous)) {
 #pragma unroll 1
     for (int c = 0; c < n_cand; ++c) {
+      if (!((exact >> c) & 1u)) continue;
       const int e = __shfl_sync(0xffffffffu, ci, c);
       double a = 0.0;
       for (int d = lane; d < D; d += 32)
@@ -340,7 +353,7 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
       if (lane == c) mine = (float)a;
     }
   }
-  // final top-K among the candidates: rank = number of candidates ahead of mine
+  // ---- final top-K among the candidates: rank = number of candidates ahead of mine ----
   int rank = 0;
   for (int c = 0; c < L_CAND; ++c) {
     const float vc = __shfl_sync(0xffffffffu, mine, c);
@@ -374,7 +387,7 @@ int make_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int bo
 }
 
 struct TcScratch {
-  size_t wgt, wnorm2, cand_val, cand_idx, fb_count, fb_list, total;
+  size_t wgt, wnorm2, logits, fb_count, fb_list, total;
 };
 TcScratch tc_layout(int T, int D, int E) {
   TcScratch s;
@@ -387,8 +400,7 @@ TcScratch tc_layout(int T, int D, int E) {
   s.wnorm2 = take(sizeof(float) * E);
   s.fb_count = take(sizeof(int32_t) * 4);
   s.wgt = take((size_t)E * D * 2);
-  s.cand_val = take(sizeof(float) * (size_t)T * L_CAND);
-  s.cand_idx = take(sizeof(int32_t) * (size_t)T * L_CAND);
+  s.logits = take(sizeof(float) * (size_t)T * (size_t)((E + 15) / 16 * 16));
   s.fb_list = take(sizeof(int32_t) * (size_t)T);
   s.total = o;
   return s;
@@ -414,8 +426,7 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   uint8_t* base = static_cast<uint8_t*>(scratch);
   auto* wgt = reinterpret_cast<__nv_bfloat16*>(base + L.wgt);
   auto* wnorm2 = reinterpret_cast<float*>(base + L.wnorm2);
-  auto* cand_val = reinterpret_cast<float*>(base + L.cand_val);
-  auto* cand_idx = reinterpret_cast<int32_t*>(base + L.cand_idx);
+  auto* logits = reinterpret_cast<float*>(base + L.logits);
   auto* fb_count = reinterpret_cast<int32_t*>(base + L.fb_count);
   auto* fb_list = reinterpret_cast<int32_t*>(base + L.fb_list);
   BWMOE_CUDA_OK(cudaMemsetAsync(base, 0, L.wgt, st));        // column norms, fallback counter, private status word
@@ -433,12 +444,12 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
     attr_err = cudaFuncSetAttribute(tc_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM_BYTES);
   });
   BWMOE_CUDA_OK(attr_err);
-  TcParams p{cand_val, cand_idx, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16};
+  TcParams p{logits, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16};
   const int grid = std::min(sm_count(), ceil_div(T, BM));
   tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, st>>>(mx, mw, p);
   BWMOE_CUDA_OK(cudaGetLastError());
-  refine_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), wgt, wnorm2, cand_val, cand_idx,
-                                                T, D, E, K, weights, indices, row_amax, fb_count, fb_list);
+  refine_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), wgt, wnorm2, logits, p.n_mma, T, D,
+                                                E, K, weights, indices, row_amax, fb_count, fb_list);
   BWMOE_CUDA_OK(cudaGetLastError());
   return launch_router_fallback(x, wg, T, D, E, K, weights, indices, fb_list, fb_count, st);
 }

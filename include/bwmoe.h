@@ -124,6 +124,29 @@ int bwmoe_moe_forward(const void* d_x, const void* d_w_gate,
                       void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * bwmoe_moe_forward with the glue of the DeepSeek drop-in fused into the combine:
+ *   out = bf16( bf16(routed * routed_scale) + residual )   (d_residual[T,D] bf16 may be null)
+ * replaces: the tail of FP8MoELayer.forward, src/blackwell_moe/runtime/deepseek_patch.py:51-53.
+ */
+int bwmoe_moe_forward_ex(const void* d_x, const void* d_w_gate,
+                         const void* d_experts_w_gate, const void* d_experts_w_up,
+                         const void* d_experts_w_down,
+                         const float* d_scales_gate, const float* d_scales_up, const float* d_scales_down,
+                         int T, int D, int H, int E, int K, float routed_scale, const void* d_residual,
+                         void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Dense (always-on) FP8 SwiGLU MLP over all T rows with whole-tensor scales for x and h:
+ * the shared experts of a DeepSeek block.  Weights [D,H] / [H,D] e4m3, scales [1] fp32.
+ * Workspace: bwmoe_workspace_bytes(T, D, H, 1, 1).
+ * replaces: FP8SharedExpert.forward, src/blackwell_moe/runtime/shared_expert_fp8.py:57-68.
+ */
+int bwmoe_dense_mlp(const void* d_x, const void* d_w_gate, const void* d_w_up, const void* d_w_down,
+                    const float* d_scale_gate, const float* d_scale_up, const float* d_scale_down,
+                    int T, int D, int H, void* d_out, void* d_workspace, size_t workspace_bytes,
+                    void* stream);
+
+/*
  * Same block with the routing decided by the caller: d_weights[T,K] fp32 and
  * d_indices[T,K] int32 index the E expert slots of the weight tensors.
  * replaces: fp8_moe_forward_fastcache, src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-55,
