@@ -11,6 +11,7 @@ missing or no B200 is present the calls raise.
 from .quant import (FP8_MAX_E4M3, dequant_fp8_e4m3, quant_fp8_block_128, quant_fp8_e4m3, quantize_expert_weights,
                     quantize_expert_weights_block)
 from .moe import (
+    HostPipeline,
     fp8_moe_forward,
     fp8_moe_forward_routed,
     moe_stage_views,
@@ -29,7 +30,7 @@ fp8_moe_forward_small_e = fp8_moe_forward
 __version__ = "0.1.0"
 
 __all__ = [
-    "FP8_MAX_E4M3", "BwmoeError", "FP8MixtralSparseMoeBlock", "FP8MoELayer", "FP8SharedExpert", "fp8_dense_mlp",
+    "FP8_MAX_E4M3", "BwmoeError", "HostPipeline", "FP8MixtralSparseMoeBlock", "FP8MoELayer", "FP8SharedExpert", "fp8_dense_mlp",
     "patch_deepseek_moe_with_store", "patch_shared_experts", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_routed",
     "fp8_moe_forward_small_e", "fp8_moe_forward_v3", "fp8_moe_forward_v4", "lib", "library_path",
     "moe_stage_views", "quant_fp8_block_128", "quant_fp8_e4m3", "quantize_expert_weights",

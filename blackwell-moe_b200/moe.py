@@ -230,3 +230,80 @@ def moe_stage_views(dev, T: int, D: int, H: int, E: int, K: int, block: bool = F
     else:
         out["h"] = out["h"].view(M, H)
     return out
+
+
+class HostPipeline:
+    """MoE-block forward for callers whose activations live in (pinned) host memory, with the
+    host->device copy of batch i+1 and the device->host copy of batch i-1 overlapping the
+    compute of batch i (three CUDA streams, ``depth`` slots of device buffers).  Numerically it
+    is :func:`fp8_moe_forward` on every batch; only the scheduling differs.
+
+        pipe = HostPipeline(w_gate, wg, wu, wd, sg, su, sd, top_k=2, max_tokens=16384)
+        t0 = pipe.submit(x0)          # returns at once
+        t1 = pipe.submit(x1)
+        y0 = pipe.result(t0)          # pinned host tensor, valid until its slot is reused
+    """
+
+    def __init__(self, w_gate, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down,
+                 top_k: int, max_tokens: int, depth: int = 2):
+        self.weights = [_contig(t, "weight tensor") for t in (w_gate, experts_w_gate, experts_w_up, experts_w_down,
+                                                             scales_gate, scales_up, scales_down)]
+        self.dev = _require_cuda(*self.weights)
+        self.block = scales_gate.dim() == 3
+        self.K, self.Tmax, self.depth = top_k, max_tokens, depth
+        self.E, self.D, self.H = experts_w_gate.shape
+        lib = _lib.lib()
+        size_fn = lib.bwmoe_workspace_bytes_block if self.block else lib.bwmoe_workspace_bytes
+        need = size_fn(max_tokens, self.D, self.H, self.E, top_k)
+        if need == 0:
+            raise ValueError("unsupported shape")
+        with torch.cuda.device(self.dev):
+            self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+            self.slots = []
+            for _ in range(depth):
+                self.slots.append(dict(
+                    x=torch.empty(max_tokens, self.D, dtype=torch.bfloat16, device=self.dev),
+                    y=torch.empty(max_tokens, self.D, dtype=torch.bfloat16, device=self.dev),
+                    ws=torch.empty(need, dtype=torch.uint8, device=self.dev),
+                    host=torch.empty(max_tokens, self.D, dtype=torch.bfloat16, pin_memory=True),
+                    in_done=torch.cuda.Event(), cmp_done=torch.cuda.Event(), out_done=torch.cuda.Event(), T=0))
+        self.ticket = 0
+
+    def submit(self, x_host: torch.Tensor) -> int:
+        assert not x_host.is_cuda and x_host.dtype == torch.bfloat16 and x_host.shape[1] == self.D
+        T = x_host.shape[0]
+        assert 0 < T <= self.Tmax
+        lib = _lib.lib()
+        slot = self.slots[self.ticket % self.depth]
+        first_use = self.ticket < self.depth
+        with torch.cuda.device(self.dev):
+            if not first_use:
+                self.s_in.wait_event(slot["cmp_done"])        # the previous batch in this slot has been consumed
+            with torch.cuda.stream(self.s_in):
+                slot["x"][:T].copy_(x_host, non_blocking=True)
+                slot["in_done"].record(self.s_in)
+            self.s_cmp.wait_event(slot["in_done"])
+            if not first_use:
+                self.s_cmp.wait_event(slot["out_done"])       # its previous result has left the device
+            fn = lib.bwmoe_moe_forward_block if self.block else lib.bwmoe_moe_forward
+            _lib.check(fn(slot["x"].data_ptr(), *[t.data_ptr() for t in self.weights], T, self.D, self.H, self.E,
+                          self.K, slot["y"].data_ptr(), slot["ws"].data_ptr(), slot["ws"].numel(),
+                          self.s_cmp.cuda_stream))
+            slot["cmp_done"].record(self.s_cmp)
+            self.s_out.wait_event(slot["cmp_done"])
+            with torch.cuda.stream(self.s_out):
+                slot["host"][:T].copy_(slot["y"][:T], non_blocking=True)
+                slot["out_done"].record(self.s_out)
+        slot["T"] = T
+        self.ticket += 1
+        return self.ticket - 1
+
+    def result(self, ticket: int) -> torch.Tensor:
+        assert self.ticket - self.depth <= ticket < self.ticket, "result no longer (or not yet) available"
+        slot = self.slots[ticket % self.depth]
+        slot["out_done"].synchronize()
+        return slot["host"][:slot["T"]]
+
+    def drain(self) -> None:
+        for slot in self.slots:
+            slot["out_done"].synchronize()

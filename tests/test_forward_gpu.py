@@ -76,6 +76,25 @@ def test_host_buffer_entry_point_matches_device_entry_point():
     assert not host_out.is_cuda and torch.equal(dev_out, host_out)
 
 
+def test_host_pipeline_matches_synchronous_calls():
+    import blackwell_moe_b200 as bw
+    inp = make_inputs(120, 256, 8, 2, 128, seed=12)
+    c = to_cuda(inp)
+    args = (c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"], c["s_down"])
+    pipe = bw.HostPipeline(*args, top_k=2, max_tokens=120, depth=2)
+    g = torch.Generator().manual_seed(13)
+    batches = [torch.randn(n, 256, generator=g).to(BF16).pin_memory() for n in (120, 64, 1, 120, 77)]
+    tickets, outs = [], []
+    for i, xb in enumerate(batches):
+        tickets.append(pipe.submit(xb))
+        if i >= 1:                                  # collect with one batch in flight behind
+            outs.append(pipe.result(tickets[i - 1]).clone())
+    outs.append(pipe.result(tickets[-1]).clone())
+    for xb, y in zip(batches, outs):
+        ref = bw.fp8_moe_forward(xb.cuda(), *args, top_k=2).cpu()
+        assert torch.equal(y, ref)
+
+
 def test_routed_entry_point_matches_full_forward():
     import blackwell_moe_b200 as bw
     inp = make_inputs(50, 256, 8, 2, 128, seed=6)
