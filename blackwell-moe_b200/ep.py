@@ -46,7 +46,6 @@ class ExchangePlan:
         self.rank, self.world, self.experts_local = rank, G, E // G
         el = self.experts_local
         cpu = counts.cpu().to(torch.int64)                       # the only host copy: split sizes must be ints
-        self.counts_host = cpu                                   # [G, E] on the host
         self.send_splits = cpu[rank].view(G, el).sum(1).tolist()  # rows I send to each rank
         mine = cpu[:, rank * el:(rank + 1) * el]                 # [G, el] rows each rank sends me, per local expert
         self.recv_splits = mine.sum(1).tolist()
@@ -61,68 +60,18 @@ class ExchangePlan:
         n = self.rows_local
         rows = torch.arange(n, device=dev)
         self.src_of_dst = (torch.repeat_interleave(block_src - start_dst, sizes_dst, output_size=n) + rows)
+        self.dst_of_src = torch.empty_like(self.src_of_dst)      # inverse map: the way back is a gather too
+        self.dst_of_src[self.src_of_dst] = rows
         seg = mine.sum(0)
         self.offsets = torch.zeros(el + 1, dtype=torch.int32, device=dev)
         self.offsets[1:] = torch.cumsum(seg, 0).to(torch.int32)
         self.row_expert = torch.repeat_interleave(torch.arange(el, device=dev, dtype=torch.int32), seg, output_size=n)
 
 
-# Up to this many (peer, expert) blocks per exchange are sent as individual point-to-point
-# transfers that land directly where they belong (no regrouping copy); beyond it one
-# all-to-all plus a row gather is cheaper than the per-message overhead.
-DIRECT_BLOCK_LIMIT = 64
-
-
-def _blocks(plan: ExchangePlan):
-    """Host-side geometry: for every (peer p, local-expert j) the home-side block of the rows this
-    rank routed to expert (p, j), and the owner-side block where rows from p for my expert j live."""
-    G, el, r = plan.world, plan.experts_local, plan.rank
-    cnt = plan.counts_host
-    home_off = torch.zeros(G * el + 1, dtype=torch.int64)
-    home_off[1:] = torch.cumsum(cnt[r], 0)                     # my rows are sorted by global expert
-    mine = cnt[:, r * el:(r + 1) * el]                         # [G, el]
-    seg_off = torch.zeros(el + 1, dtype=torch.int64)
-    seg_off[1:] = torch.cumsum(mine.sum(0), 0)
-    within = torch.cumsum(mine, 0) - mine                      # rows of earlier sources inside a segment
-    home, owner = {}, {}
-    for p in range(G):
-        for j in range(el):
-            e = p * el + j
-            home[(p, j)] = (int(home_off[e]), int(cnt[r, e]))
-            owner[(p, j)] = (int(seg_off[j] + within[p, j]), int(mine[p, j]))
-    return home, owner
-
-
-def _exchange_direct(src, dst, send_blocks, recv_blocks, plan, group):
-    """Point-to-point exchange of blocks: send_blocks / recv_blocks map (peer, expert) -> (offset, rows)."""
-    ops = []
-    G, el, r = plan.world, plan.experts_local, plan.rank
-    peer_rank = (lambda p: p) if group is None else (lambda p: dist.get_global_rank(group, p))
-    for p in range(G):
-        for j in range(el):
-            so, sn = send_blocks[(p, j)]
-            ro, rn = recv_blocks[(p, j)]
-            if p == r:
-                if sn:
-                    dst[ro:ro + rn].copy_(src[so:so + sn])
-                continue
-            if sn:
-                ops.append(dist.P2POp(dist.isend, src[so:so + sn], peer_rank(p), group))
-            if rn:
-                ops.append(dist.P2POp(dist.irecv, dst[ro:ro + rn], peer_rank(p), group))
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-
-
 def dispatch(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor:
     """Send rows (sorted by global expert id) to the expert owners; returns the
     received rows regrouped into per-local-expert segments."""
     recv = rows.new_empty((plan.rows_local,) + tuple(rows.shape[1:]))
-    if plan.world * plan.experts_local <= DIRECT_BLOCK_LIMIT:
-        home, owner = _blocks(plan)
-        _exchange_direct(rows, recv, home, owner, plan, group)
-        return recv
     dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
     return recv.index_select(0, plan.src_of_dst)
 
@@ -130,13 +79,7 @@ def dispatch(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor
 def combine_back(rows_local: torch.Tensor, plan: ExchangePlan, n_home: int, group=None) -> torch.Tensor:
     """Inverse of :func:`dispatch`: per-expert rows go back to the ranks (and row
     positions) they came from."""
-    if plan.world * plan.experts_local <= DIRECT_BLOCK_LIMIT:
-        home_rows = rows_local.new_empty((n_home,) + tuple(rows_local.shape[1:]))
-        home, owner = _blocks(plan)
-        _exchange_direct(rows_local, home_rows, owner, home, plan, group)
-        return home_rows
-    send = torch.empty_like(rows_local)
-    send.index_copy_(0, plan.src_of_dst, rows_local)
+    send = rows_local.index_select(0, plan.dst_of_src)
     home = rows_local.new_empty((n_home,) + tuple(rows_local.shape[1:]))
     dist.all_to_all_single(home, send, plan.send_splits, plan.recv_splits, group=group)
     return home

@@ -27,12 +27,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, port, fn_name, ret, direct_limit=None):
+def _worker(rank, port, fn_name, ret):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
-    if direct_limit is not None:            # 0 forces the all-to-all + regroup path
-        import blackwell_moe_b200.ep as epmod
-        epmod.DIRECT_BLOCK_LIMIT = direct_limit
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
     try:
@@ -45,11 +42,11 @@ def _worker(rank, port, fn_name, ret, direct_limit=None):
         dist.destroy_process_group()
 
 
-def _run(fn_name, direct_limit=None):
+def _run(fn_name):
     port = _free_port()
     with mp.Manager() as m:
         ret = m.dict()
-        mp.spawn(_worker, args=(port, fn_name, ret, direct_limit), nprocs=WORLD, join=True)
+        mp.spawn(_worker, args=(port, fn_name, ret), nprocs=WORLD, join=True)
         for r in range(WORLD):
             assert ret.get(r) == "ok", f"rank {r}: {ret.get(r)}"
 
@@ -133,11 +130,9 @@ def _ep_forward_equals_single_process_oracle(rank):
     assert torch.equal(out, ref[rank * T:(rank + 1) * T])
 
 
-@pytest.mark.parametrize("direct_limit", [None, 0], ids=["point-to-point", "all-to-all"])
-def test_rows_travel_to_their_experts_and_back(direct_limit):
-    _run("_rows_travel_to_their_experts_and_back", direct_limit)
+def test_rows_travel_to_their_experts_and_back():
+    _run("_rows_travel_to_their_experts_and_back")
 
 
-@pytest.mark.parametrize("direct_limit", [None, 0], ids=["point-to-point", "all-to-all"])
-def test_ep_forward_equals_single_process_oracle(direct_limit):
-    _run("_ep_forward_equals_single_process_oracle", direct_limit)
+def test_ep_forward_equals_single_process_oracle():
+    _run("_ep_forward_equals_single_process_oracle")
