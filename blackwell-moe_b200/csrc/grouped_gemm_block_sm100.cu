@@ -154,8 +154,8 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t buf = it & 1u, use = it >> 1;
-          if (!(ok = mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
-          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
+          if (!(ok = mbar_wait_spin(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
+          if (!(ok = mbar_wait_spin(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -205,7 +205,7 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           wA_nx = wA[(size_t)(kb + 1) * p.nb];
           wB_nx = wB[(size_t)(kb + 1) * p.nb];
         }
-        ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
+        ok = mbar_wait_spin(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();

@@ -78,6 +78,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// Same contract as mbar_wait, but polls with the non-suspending test_wait: for waits that sit on
+// the critical path of every K block, where the wake-up latency of a suspended try_wait shows.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int32_t* status) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((it & 1023u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicOr(status, BWMOE_STATUS_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
