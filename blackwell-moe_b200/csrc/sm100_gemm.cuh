@@ -97,6 +97,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, vo
   const unsigned long long t0 = global_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_test_wait(bar, parity)) return true;
+    __nanosleep(20);                      // keep the poll loop from crowding the warps that still have work
     if ((it & 1023u) == 0u) {
       if (*abort_flag) return false;
       if (global_ns() - t0 > WAIT_LIMIT_NS) {

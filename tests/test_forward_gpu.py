@@ -106,6 +106,27 @@ def test_routed_entry_point_matches_full_forward():
     assert torch.equal(full, routed)
 
 
+def test_out_of_range_expert_ids_are_reported_not_trapped():
+    """Caller-supplied routing with an expert id outside [0, E): the kernels skip the slot, finish
+    normally and raise the BAD_EXPERT bit of the status word; the context stays usable."""
+    import blackwell_moe_b200 as bw
+    inp = make_inputs(40, 256, 8, 2, 128, seed=15)
+    c = to_cuda(inp)
+    args = (c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"], c["s_down"])
+    w, idx = bw.top_k_router(c["x"], c["w_gate"], 2)
+    good = bw.fp8_moe_forward_routed(c["x"], w, idx, *args)
+    assert int(bw.moe_stage_views("cuda:0", 40, 256, 128, 8, 2)["status"][0]) == 0
+    bad = idx.clone()
+    bad[3, 1] = 99
+    bad[17, 0] = -5
+    out = bw.fp8_moe_forward_routed(c["x"], w, bad, *args)
+    v = bw.moe_stage_views("cuda:0", 40, 256, 128, 8, 2)
+    assert int(v["status"][0]) & 2, "BAD_EXPERT bit not set"
+    assert torch.isfinite(out.float()).all()
+    assert int(v["offsets"][-1]) == 40 * 2 - 2          # the two bad slots own no row
+    assert torch.equal(bw.fp8_moe_forward_routed(c["x"], w, idx, *args), good)   # and the next call is clean
+
+
 def test_full_size_mixtral_block_via_duplicated_tokens():
     """BASELINE-size check (T=16384, D=4096, H=14336, E=8, top-2) that needs the oracle
     on 64 rows only: the 16384 tokens are 256 copies of 64 distinct rows.  Copies do
