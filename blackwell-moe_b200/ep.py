@@ -73,13 +73,15 @@ def dispatch(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor
     received rows regrouped into per-local-expert segments."""
     recv = rows.new_empty((plan.rows_local,) + tuple(rows.shape[1:]))
     dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group)
+    if plan.experts_local == 1:           # one expert per rank: (source, expert) order is already (expert, source)
+        return recv
     return recv.index_select(0, plan.src_of_dst)
 
 
 def combine_back(rows_local: torch.Tensor, plan: ExchangePlan, n_home: int, group=None) -> torch.Tensor:
     """Inverse of :func:`dispatch`: per-expert rows go back to the ranks (and row
     positions) they came from."""
-    send = rows_local.index_select(0, plan.dst_of_src)
+    send = rows_local if plan.experts_local == 1 else rows_local.index_select(0, plan.dst_of_src)
     home = rows_local.new_empty((n_home,) + tuple(rows_local.shape[1:]))
     dist.all_to_all_single(home, send, plan.send_splits, plan.recv_splits, group=group)
     return home

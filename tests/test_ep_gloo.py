@@ -58,11 +58,15 @@ def _routing(T_per_rank, E, K, seed):
     return scores.topk(K, dim=-1).indices.to(torch.int32)
 
 
-def _rows_travel_to_their_experts_and_back(rank):
+def _rows_travel_one_expert_per_rank(rank):
+    _rows_travel_to_their_experts_and_back(rank, E=WORLD, K=1)
+
+
+def _rows_travel_to_their_experts_and_back(rank, E=8, K=3):
     import oracle
     from blackwell_moe_b200.ep import ExchangePlan, combine_back, dispatch
-    T, E, K = 37, 8, 3
-    idx_all = _routing(T, E, K, seed=5)
+    T = 37
+    idx_all = _routing(T, E, K, seed=5) if E > 3 else torch.randint(0, E, (WORLD * T, K), generator=torch.Generator().manual_seed(6)).to(torch.int32)
     idx = idx_all[rank * T:(rank + 1) * T]
     sort_perm, _, offsets = oracle.permutation(idx, E)
     # payload: (global slot id, expert) per permuted row
@@ -132,6 +136,10 @@ def _ep_forward_equals_single_process_oracle(rank):
 
 def test_rows_travel_to_their_experts_and_back():
     _run("_rows_travel_to_their_experts_and_back")
+
+
+def test_rows_travel_with_one_expert_per_rank():
+    _run("_rows_travel_one_expert_per_rank")
 
 
 def test_ep_forward_equals_single_process_oracle():
