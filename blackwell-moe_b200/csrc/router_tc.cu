@@ -409,7 +409,7 @@ TcScratch tc_layout(int T, int D, int E) {
 }  // namespace
 
 bool router_tc_applicable(int T, int D, int E, int K) {
-  return T >= 1024 && E > 16 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0;
+  return T >= 1024 && E >= 8 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0;
 }
 
 size_t router_tc_scratch_bytes(int T, int D, int E) { return tc_layout(T, D, E).total; }
