@@ -21,6 +21,11 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+namespace {
+int g_sm_reserve = 0;   // SMs the persistent GEMM grids leave free (for collectives running beside them)
+}
+int gemm_sm_budget() { return std::max(1, sm_count() - g_sm_reserve); }
+
 int sm_count() {
   // per-device cache; the library may be used from one process per GPU or several devices
   static int cached[64] = {0};
@@ -193,6 +198,12 @@ using namespace bwmoe;
 extern "C" {
 
 int bwmoe_version(void) { return BWMOE_VERSION; }
+
+int bwmoe_set_sm_reserve(int n) {
+  BWMOE_REQUIRE(n >= 0 && n < 128, BWMOE_ERR_BAD_SHAPE, "set_sm_reserve: %d out of range", n);
+  g_sm_reserve = n;
+  return BWMOE_OK;
+}
 
 int bwmoe_last_error(char* buf, size_t len) {
   const size_t n = strlen(g_error);

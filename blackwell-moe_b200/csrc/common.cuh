@@ -26,6 +26,7 @@ int set_error(int code, const char* fmt, ...);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int sm_count();
+int gemm_sm_budget();   // sm_count() minus the SMs reserved through bwmoe_set_sm_reserve
 
 // ---- arithmetic shared by several kernels ---------------------------------
 constexpr float kFp8Max = 448.0f;

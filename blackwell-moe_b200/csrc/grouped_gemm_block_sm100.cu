@@ -361,7 +361,7 @@ int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUten
   });
   BWMOE_CUDA_OK(attr_err);
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
-  const int grid = (int)std::min<long long>(sm_count(), max_tiles);
+  const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
   block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;

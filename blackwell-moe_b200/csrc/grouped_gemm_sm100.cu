@@ -423,7 +423,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap
   });
   BWMOE_CUDA_OK(attr_err);
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
-  const int grid = (int)std::min<long long>(sm_count(), max_tiles);
+  const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
   grouped_gemm_kernel<GATE_UP, RAW><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;

@@ -40,12 +40,13 @@ class ExchangePlan:
     """Split sizes and row maps of one dispatch/combine pair, derived from the
     ``[G, E]`` matrix of per-rank, per-expert row counts."""
 
-    def __init__(self, counts: torch.Tensor, rank: int):
+    def __init__(self, counts: torch.Tensor, rank: int, counts_host: torch.Tensor = None):
         G, E = counts.shape
         assert E % G == 0, (E, G)
         self.rank, self.world, self.experts_local = rank, G, E // G
         el = self.experts_local
-        cpu = counts.cpu().to(torch.int64)                       # the only host copy: split sizes must be ints
+        # the only host copy: split sizes must be ints (callers planning several exchanges pass one copy)
+        cpu = (counts.cpu() if counts_host is None else counts_host).to(torch.int64)
         self.send_splits = cpu[rank].view(G, el).sum(1).tolist()  # rows I send to each rank
         mine = cpu[:, rank * el:(rank + 1) * el]                 # [G, el] rows each rank sends me, per local expert
         self.recv_splits = mine.sum(1).tolist()
@@ -78,6 +79,26 @@ def dispatch(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor
     return recv.index_select(0, plan.src_of_dst)
 
 
+def dispatch_start(rows: torch.Tensor, plan: ExchangePlan, group=None):
+    """Asynchronous half of :func:`dispatch`: returns ``(recv, work)``; after ``work.wait()`` pass
+    ``recv`` to :func:`dispatch_finish`."""
+    recv = rows.new_empty((plan.rows_local,) + tuple(rows.shape[1:]))
+    work = dist.all_to_all_single(recv, rows, plan.recv_splits, plan.send_splits, group=group, async_op=True)
+    return recv, work
+
+
+def dispatch_finish(recv: torch.Tensor, plan: ExchangePlan) -> torch.Tensor:
+    return recv if plan.experts_local == 1 else recv.index_select(0, plan.src_of_dst)
+
+
+def combine_back_start(rows_local: torch.Tensor, plan: ExchangePlan, n_home: int, group=None):
+    """Asynchronous :func:`combine_back`: returns ``(home, work)``."""
+    send = rows_local if plan.experts_local == 1 else rows_local.index_select(0, plan.dst_of_src)
+    home = rows_local.new_empty((n_home,) + tuple(rows_local.shape[1:]))
+    work = dist.all_to_all_single(home, send, plan.send_splits, plan.recv_splits, group=group, async_op=True)
+    return home, work
+
+
 def combine_back(rows_local: torch.Tensor, plan: ExchangePlan, n_home: int, group=None) -> torch.Tensor:
     """Inverse of :func:`dispatch`: per-expert rows go back to the ranks (and row
     positions) they came from."""
@@ -107,65 +128,110 @@ class ExpertParallelMoE:
         self.dev = self.wg.device
         assert self.w_gate.shape == (self.D, num_experts)
 
+    #: token micro-batches per forward: the dispatch of batch i+1 overlaps the gate/up GEMM of batch i and
+    #: the way back of batch i overlaps the down GEMM of batch i+1.  Results do not depend on it.
+    micro_batches = 1
+    micro_batch_min_tokens = 2048      # smaller batches per rank are not split
+    #: SMs the persistent GEMMs leave to NCCL while micro-batches overlap (they otherwise hold every SM
+    #: until they finish, and the collective queued beside them cannot start)
+    sm_reserve = 0
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         host_in = not x.is_cuda
         if host_in:
             x = x.to(self.dev, non_blocking=True)
         lib, dev, E, K, D, H, el = _lib.lib(), self.dev, self.E, self.K, self.D, self.H, self.el
         T = x.shape[0]
-        M = T * K
         st = torch.cuda.current_stream(dev).cuda_stream
-        i32, f32 = torch.int32, torch.float32
+        i32, f32, u8 = torch.int32, torch.float32, torch.uint8
         new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         weights, indices, row_amax = new(T, K, dtype=f32), new(T, K, dtype=i32), new(T, dtype=f32)
         need = lib.bwmoe_router_scratch_bytes(T, D, E, K)
-        rs = new(need, dtype=torch.uint8) if need else None
+        rs = new(need, dtype=u8) if need else None
         _lib.check(lib.bwmoe_router(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, weights.data_ptr(),
                                     indices.data_ptr(), row_amax.data_ptr(), rs.data_ptr() if need else None, need, st))
-        offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
         if self.block:
+            M = T * K
+            offsets, pos, row_slot, row_expert = (new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32),
+                                                  new(M, dtype=i32))
             return self._forward_block(x, weights, indices, offsets, pos, row_slot, row_expert, host_in)
-        stats = torch.zeros(2 * E, dtype=f32, device=dev)          # [amax | counts-as-int32 bits]
+
+        # ---- plan every micro-batch, exchange counts and activation maxima once ----
+        nmb = self.micro_batches if T >= self.micro_batch_min_tokens * self.micro_batches else 1
+        bounds = [T * i // nmb for i in range(nmb + 1)]
         status = torch.zeros(4, dtype=i32, device=dev)
-        scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=torch.uint8)
-        _lib.check(lib.bwmoe_permute_plan(indices.data_ptr(), row_amax.data_ptr(), T, E, K, offsets.data_ptr(),
-                                          pos.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(),
-                                          stats.data_ptr(), status.data_ptr(), scratch.data_ptr(), st))
-        stats[E:].view(i32).copy_(offsets[1:] - offsets[:-1])
-        gathered = new(self.world * 2 * E, dtype=f32)
+        stats = torch.zeros((1 + nmb) * E, dtype=f32, device=dev)      # [amax | counts of batch 0 | batch 1 ...]
+        mbs = []
+        for h in range(nmb):
+            t0, t1 = bounds[h], bounds[h + 1]
+            Th = t1 - t0
+            Mh = Th * K
+            mb = dict(t0=t0, t1=t1, T=Th, M=Mh, offsets=new(E + 1, dtype=i32), pos=new(Mh, dtype=i32),
+                      row_slot=new(Mh, dtype=i32), row_expert=new(Mh, dtype=i32), amax=new(E, dtype=f32))
+            scratch = new(lib.bwmoe_plan_scratch_bytes(Th, E, K), dtype=u8)
+            _lib.check(lib.bwmoe_permute_plan(indices[t0:t1].data_ptr(), row_amax[t0:t1].data_ptr(), Th, E, K,
+                                              mb["offsets"].data_ptr(), mb["pos"].data_ptr(),
+                                              mb["row_slot"].data_ptr(), mb["row_expert"].data_ptr(),
+                                              mb["amax"].data_ptr(), status.data_ptr(), scratch.data_ptr(), st))
+            torch.maximum(stats[:E], mb["amax"], out=stats[:E])
+            stats[(1 + h) * E:(2 + h) * E].view(i32).copy_(mb["offsets"][1:] - mb["offsets"][:-1])
+            mbs.append(mb)
+        gathered = new(self.world * (1 + nmb) * E, dtype=f32)
         dist.all_gather_into_tensor(gathered, stats, group=self.group)
-        gathered = gathered.view(self.world, 2 * E)
+        gathered = gathered.view(self.world, (1 + nmb) * E)
         amax = gathered[:, :E].amax(0).contiguous()                # exact: a max of the same floats
-        counts = gathered[:, E:].contiguous().view(i32)
+        counts_all = gathered[:, E:].contiguous().view(i32)        # [G, nmb * E]
+        counts_host = counts_all.cpu()                             # one synchronisation for every micro-batch
         scale_x = new(E, dtype=f32)
         _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
-        xq = new(M, D, dtype=torch.uint8)
-        _lib.check(lib.bwmoe_gather_quant(x.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(), scale_x.data_ptr(),
-                                          M, D, K, xq.data_ptr(), st))
-        plan = ExchangePlan(counts, self.rank)
-        xq_local = dispatch(xq, plan, self.group)
-        R = plan.rows_local
-        y_local = new(R, D, dtype=torch.bfloat16)
-        if R > 0:
-            sx_local = scale_x[self.rank * el:(self.rank + 1) * el].contiguous()
-            h = new(R, H, dtype=torch.bfloat16)
-            amax_h = torch.zeros(el, dtype=f32, device=dev)
-            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, D, H, el)), dtype=torch.uint8)
-            _lib.check(lib.bwmoe_gateup_swiglu(xq_local.data_ptr(), plan.offsets.data_ptr(), sx_local.data_ptr(),
-                                               self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
-                                               self.su.data_ptr(), R, D, H, el, h.data_ptr(), amax_h.data_ptr(),
-                                               status.data_ptr(), gs.data_ptr(), st))
-            scale_h = new(el, dtype=f32)
-            _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), plan.offsets.data_ptr(), el, scale_h.data_ptr(), st))
-            hq = new(R, H, dtype=torch.uint8)
-            _lib.check(lib.bwmoe_requant(h.data_ptr(), plan.row_expert.data_ptr(), scale_h.data_ptr(), R, H,
-                                         hq.data_ptr(), st))
-            _lib.check(lib.bwmoe_down(hq.data_ptr(), plan.offsets.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
-                                      self.sd.data_ptr(), R, D, H, el, y_local.data_ptr(), status.data_ptr(),
-                                      gs.data_ptr(), st))
-        y_home = combine_back(y_local, plan, M, self.group)
+        sx_local = scale_x[self.rank * el:(self.rank + 1) * el].contiguous()
+
+        if nmb > 1:
+            _lib.check(lib.bwmoe_set_sm_reserve(self.sm_reserve))
+        # ---- quantise and dispatch (asynchronously) ----
+        for h, mb in enumerate(mbs):
+            mb["plan"] = ExchangePlan(counts_all[:, h * E:(h + 1) * E], self.rank, counts_host[:, h * E:(h + 1) * E])
+            xq = new(mb["M"], D, dtype=u8)
+            _lib.check(lib.bwmoe_gather_quant(x[mb["t0"]:mb["t1"]].data_ptr(), mb["row_slot"].data_ptr(),
+                                              mb["row_expert"].data_ptr(), scale_x.data_ptr(), mb["M"], D, K,
+                                              xq.data_ptr(), st))
+            mb["recv"], mb["work"] = dispatch_start(xq, mb["plan"], self.group)
+        # ---- gate/up as the batches arrive; the segment amax of h spans all batches ----
+        amax_h = torch.zeros(el, dtype=f32, device=dev)
+        for mb in mbs:
+            mb["work"].wait()
+            R = mb["plan"].rows_local
+            mb["xq_local"] = dispatch_finish(mb["recv"], mb["plan"])
+            mb["h"] = new(R, H, dtype=torch.bfloat16)
+            if R > 0:
+                mb["gs"] = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, D, H, el)), dtype=u8)
+                _lib.check(lib.bwmoe_gateup_swiglu(mb["xq_local"].data_ptr(), mb["plan"].offsets.data_ptr(),
+                                                   sx_local.data_ptr(), self.wg.data_ptr(), self.wu.data_ptr(),
+                                                   self.sg.data_ptr(), self.su.data_ptr(), R, D, H, el,
+                                                   mb["h"].data_ptr(), amax_h.data_ptr(), status.data_ptr(),
+                                                   mb["gs"].data_ptr(), st))
+        scale_h = new(el, dtype=f32)
+        _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
+        # ---- requant + down per batch; rows travel home while the next batch computes ----
+        for mb in mbs:
+            R = mb["plan"].rows_local
+            y_local = new(R, D, dtype=torch.bfloat16)
+            if R > 0:
+                hq = new(R, H, dtype=u8)
+                _lib.check(lib.bwmoe_requant(mb["h"].data_ptr(), mb["plan"].row_expert.data_ptr(), scale_h.data_ptr(),
+                                             R, H, hq.data_ptr(), st))
+                _lib.check(lib.bwmoe_down(hq.data_ptr(), mb["plan"].offsets.data_ptr(), scale_h.data_ptr(),
+                                          self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el, y_local.data_ptr(),
+                                          status.data_ptr(), mb["gs"].data_ptr(), st))
+            mb["home"], mb["work"] = combine_back_start(y_local, mb["plan"], mb["M"], self.group)
+        if nmb > 1:
+            _lib.check(lib.bwmoe_set_sm_reserve(0))
         out = new(T, D, dtype=torch.bfloat16)
-        _lib.check(lib.bwmoe_combine(y_home.data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K, out.data_ptr(), st))
+        for mb in mbs:
+            mb["work"].wait()
+            _lib.check(lib.bwmoe_combine(mb["home"].data_ptr(), mb["pos"].data_ptr(),
+                                         weights[mb["t0"]:mb["t1"]].data_ptr(), mb["T"], D, K,
+                                         out[mb["t0"]:mb["t1"]].data_ptr(), st))
         self.last_status = status
         return self._finish(out, host_in)
 

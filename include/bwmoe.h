@@ -74,6 +74,11 @@ enum {
 
 int bwmoe_version(void);
 
+/* Process-wide: the persistent GEMM kernels launch on (SM count - n) SMs, leaving n free for
+ * kernels that must run beside them (NCCL collectives of the expert-parallel path).  Default 0.
+ * No counterpart in the reference (it is single-GPU). */
+int bwmoe_set_sm_reserve(int n);
+
 /* Copies the calling thread's last error message (NUL-terminated, truncated to
  * `len`) and returns its length. */
 int bwmoe_last_error(char* buf, size_t len);

@@ -37,13 +37,17 @@ def _worker(rank, world, port, ret):
         from blackwell_moe_b200.ep import ExpertParallelMoE
         from helpers import make_inputs
         msgs = []
-        for (T, D, E, K, H) in ((96, 256, 8, 2, 256), (33, 512, 16, 4, 384), (700, 256, 4, 2, 128)):
+        # the last two shapes are split into micro-batches (asynchronous, overlapped exchanges)
+        for (T, D, E, K, H, min_tok) in ((96, 256, 8, 2, 256, 2048), (33, 512, 16, 4, 384, 2048),
+                                         (700, 256, 4, 2, 128, 2048), (700, 256, 4, 2, 128, 100),
+                                         (301, 256, 2, 2, 128, 50)):
             inp = make_inputs(world * T, D, E, K, H, seed=T + E, keep_bf16=False)
             c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
             el = E // world
             sl = slice(rank * el, (rank + 1) * el)
             ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c["s_gate"][sl],
                                    c["s_up"][sl], c["s_down"][sl], num_experts=E, top_k=K)
+            ep.micro_batch_min_tokens = min_tok
             out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
             assert int(ep.last_status[0]) == 0
             full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
@@ -51,7 +55,7 @@ def _worker(rank, world, port, ret):
             ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"],
                                      c["s_down"], top_k=K)
             if not torch.equal(full, ref):
-                msgs.append(f"shape {(T, D, E, K, H)}: max diff {(full.float() - ref.float()).abs().max().item()}")
+                msgs.append(f"shape {(T, D, E, K, H, min_tok)}: max diff {(full.float() - ref.float()).abs().max().item()}")
             host = ep.forward(inp["x"][rank * T:(rank + 1) * T].contiguous().pin_memory())
             if not torch.equal(host, out.cpu()):
                 msgs.append(f"shape {(T, D, E, K, H)}: host-buffer path differs")
