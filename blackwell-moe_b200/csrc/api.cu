@@ -173,9 +173,12 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
     return rc;
   // scale_h is derived from amax_h inside the requantisation kernel
   if ((rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h))) return rc;
+  const CombineArgs ca{pos, weights, T, K, out, out_scale, residual};
+  bool combined = false;
   if ((rc = launch_down(at<void>(ws, L.hq), offsets, scale_h, wd, sd, M, D, H, E, at<void>(ws, L.y), status,
-                        at<void>(ws, L.gemm_scratch), st)))
+                        at<void>(ws, L.gemm_scratch), st, &ca, &combined)))
     return rc;
+  if (combined) return BWMOE_OK;
   return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st, out_scale, residual);
 }
 

@@ -92,8 +92,19 @@ size_t gemm_scratch_bytes(int M, int D, int H, int E);
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
                   int32_t* status, void* scratch, cudaStream_t st);
+// What the weighted combine needs; handed to launch_down so that a split-K down projection can sum its
+// slabs and combine in one kernel (*fused reports whether it did; otherwise the caller combines).
+struct CombineArgs {
+  const int32_t* pos;
+  const float* weights;
+  int T, K;
+  void* out;
+  float scale;
+  const void* residual;
+};
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
-                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st);
+                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
+                const CombineArgs* combine = nullptr, bool* fused = nullptr);
 
 // 128x128 block-scale recipe
 int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,

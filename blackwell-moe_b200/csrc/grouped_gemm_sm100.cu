@@ -394,6 +394,62 @@ down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D
       make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
 }
 
+// The same sum, followed at once by the weighted combine of the token's K rows: one thread per
+// (token, 4 columns).  Arithmetic and order equal down_from_partials_kernel + the combine kernel
+// (bf16 y, bf16 weight, bf16 product, fp32 sum over k in order, optional scale and residual);
+// y is still written so that the staged view of the workspace stays complete.
+__global__ void __launch_bounds__(256)
+down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D,
+                                  const int32_t* __restrict__ offsets, int E, const float* __restrict__ sh,
+                                  const float* __restrict__ sd, __nv_bfloat16* __restrict__ y,
+                                  const int32_t* __restrict__ pos, const float* __restrict__ weights, int T, int K,
+                                  __nv_bfloat16* __restrict__ out, float scale,
+                                  const __nv_bfloat16* __restrict__ residual) {
+  const int vec_per_row = D / 4;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (size_t)T * vec_per_row) return;
+  const int t = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < K; ++k) {
+    const int m = pos[(size_t)t * K + k];
+    if (m < 0) continue;
+    const int e = expert_of_row(offsets, E, m);
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < S; ++s) {
+      const float4 q = reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v];
+      a[0] += q.x, a[1] += q.y, a[2] += q.z, a[3] += q.w;
+    }
+    const float inv = 1.0f / (sh[e] * sd[e]);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a[0] * inv, a[1] * inv), hi = __floats2bfloat162_rn(a[2] * inv, a[3] * inv);
+    reinterpret_cast<uint2*>(y + (size_t)m * D)[v] =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    const float w = bf16_round(weights[(size_t)t * K + k]);
+    const float2 f0 = __bfloat1622float2(lo), f1 = __bfloat1622float2(hi);
+    acc[0] += bf16_round(f0.x * w);
+    acc[1] += bf16_round(f0.y * w);
+    acc[2] += bf16_round(f1.x * w);
+    acc[3] += bf16_round(f1.y * w);
+  }
+  if (scale != 1.0f) {
+    const float sb = bf16_round(scale);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * sb);
+  }
+  if (residual != nullptr) {
+    const uint2 raw = reinterpret_cast<const uint2*>(residual + (size_t)t * D)[v];
+    const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 f = __bfloat1622float2(q[i]);
+      acc[2 * i] = bf16_round(acc[2 * i]) + f.x;
+      acc[2 * i + 1] = bf16_round(acc[2 * i + 1]) + f.y;
+    }
+  }
+  const __nv_bfloat162 o0 = __floats2bfloat162_rn(acc[0], acc[1]), o1 = __floats2bfloat162_rn(acc[2], acc[3]);
+  reinterpret_cast<uint2*>(out + (size_t)t * D)[v] =
+      make_uint2(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1));
+}
+
 // Split-K is for small batches, where a few experts x column blocks cannot occupy every SM:
 // the K loop of each tile is cut so that about four waves of tiles exist.
 constexpr int kSplitMaxRows = 64;
@@ -470,7 +526,9 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
 }
 
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
-                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st) {
+                int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
+                const CombineArgs* combine, bool* fused) {
+  if (fused) *fused = false;
   BWMOE_REQUIRE(hq && offsets && sh && wd && sd && y && status, BWMOE_ERR_NULL, "down: null pointer");
   if (int rc = check_common("down", hq, y, M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(wd), BWMOE_ERR_BAD_ALIGN, "down: weights must be 16-byte aligned");
@@ -484,6 +542,16 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
   BWMOE_REQUIRE(scratch != nullptr && aligned16(scratch), BWMOE_ERR_WORKSPACE, "down: scratch buffer required");
   p.partial = static_cast<float*>(scratch);
   if (int rc = launch_gemm<false, true>(ma, mb, mb, p, M, st)) return rc;
+  if (combine != nullptr && fused != nullptr && combine->T * combine->K == M) {
+    const size_t nt = (size_t)combine->T * (D / 4);
+    down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, st>>>(
+        p.partial, sp.split_k, M, D, offsets, E, sh, sd, static_cast<__nv_bfloat16*>(y), combine->pos,
+        combine->weights, combine->T, combine->K, static_cast<__nv_bfloat16*>(combine->out), combine->scale,
+        static_cast<const __nv_bfloat16*>(combine->residual));
+    BWMOE_CUDA_OK(cudaGetLastError());
+    *fused = true;
+    return BWMOE_OK;
+  }
   const size_t n = (size_t)M * (D / 4);
   down_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.partial, sp.split_k, M, D, offsets, E, sh,
                                                                         sd, static_cast<__nv_bfloat16*>(y));

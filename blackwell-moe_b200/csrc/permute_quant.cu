@@ -209,12 +209,9 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   const unsigned chunks_per_row = (vec_per_row + per_block - 1) / per_block;
   const int m = (int)(blockIdx.x / chunks_per_row);
   const int v0 = (int)(blockIdx.x % chunks_per_row) * per_block + threadIdx.x;
+  // Two dependent round trips, not three: the row's data is requested as soon as its source row is
+  // known, and the scale (expert id -> scale) is fetched while the data is in flight.
   const int expert = row_expert[m];
-  float scale = scales[expert];
-  if (FROM_AMAX) {
-    scale = scale_from_amax(scale);
-    if (v0 == 0) scales_out[expert] = scale;     // every row of the segment writes the same value
-  }
   const size_t srow = SRC_BY_SLOT ? (size_t)(row_slot[m] / K) : (size_t)m;
   const uint4* in = reinterpret_cast<const uint4*>(src + srow * W);
   uint2* out = reinterpret_cast<uint2*>(dst + (size_t)m * W);
@@ -223,6 +220,12 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   for (int i = 0; i < kQuantVecs; ++i) {
     const int v = v0 + i * blockDim.x;
     raw[i] = v < vec_per_row ? in[v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  asm volatile("" ::: "memory");                 // keep the scale load behind the data loads
+  float scale = scales[expert];
+  if (FROM_AMAX) {
+    scale = scale_from_amax(scale);
+    if (v0 == 0) scales_out[expert] = scale;     // every row of the segment writes the same value
   }
 #pragma unroll
   for (int i = 0; i < kQuantVecs; ++i) {

@@ -180,26 +180,38 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   int inner_n = 0;
   for (int e = tid; e < 256; e += blockDim.x) s_wsq[e] = 0.f;
   __syncthreads();
-#pragma unroll 4
-  for (int d = dg; d < D; d += NG) {
-    const float xv = __bfloat162float(xrow[d]);
-    if (ev == 0) {
-      xsq = fmaf(xv, xv, xsq);
-      xmax = fmaxf(xmax, fabsf(xv));
+  // kLoads loads are issued before any of them is used: with one token per block the loop is a chain of
+  // memory round trips otherwise.  Padding steps multiply by zero and change nothing.
+  constexpr int kLoads = 8;
+  static_assert(kInner % kLoads == 0, "a Kahan step closes a whole number of load batches");
+  for (int d0 = dg; d0 < D; d0 += NG * kLoads) {
+    float xv[kLoads];
+    uint4 raw[kLoads];
+#pragma unroll
+    for (int u = 0; u < kLoads; ++u) {
+      const int d = d0 + u * NG;
+      const bool ok = d < D;
+      xv[u] = ok ? __bfloat162float(xrow[d]) : 0.f;
+      raw[u] = (ok && ev_ok) ? *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev) : make_uint4(0u, 0u, 0u, 0u);
     }
-    if (ev_ok) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev);
-      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < kLoads; ++u) {
+      if (ev == 0) {
+        xsq = fmaf(xv[u], xv[u], xsq);
+        xmax = fmaxf(xmax, fabsf(xv[u]));
+      }
+      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(pw[j]);
         wsq[2 * j] = fmaf(f.x, f.x, wsq[2 * j]);
         wsq[2 * j + 1] = fmaf(f.y, f.y, wsq[2 * j + 1]);
-        inner[2 * j] = fmaf(xv, f.x, inner[2 * j]);
-        inner[2 * j + 1] = fmaf(xv, f.y, inner[2 * j + 1]);
+        inner[2 * j] = fmaf(xv[u], f.x, inner[2 * j]);
+        inner[2 * j + 1] = fmaf(xv[u], f.y, inner[2 * j + 1]);
       }
     }
-    if (++inner_n == kInner) {
+    inner_n += kLoads;
+    if (inner_n == kInner) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         kahan_add(acc[j], comp[j], inner[j]);
@@ -619,7 +631,7 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
     router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, st>>>(xp, wp, T, D, E, K, weights,
                                                                                  indices, row_amax);
   } else if (vec_gate && T < 1024) {
-    const int threads = E >= 128 ? 1024 : 256;
+    const int threads = (E >= 128 || T <= 64) ? 1024 : 256;   // few tokens: spread each row over more threads
     router_token_kernel<<<T, threads, 0, st>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
   } else if (T >= 2048) {
     constexpr int TOK = 16;

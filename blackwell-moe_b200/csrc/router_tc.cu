@@ -207,6 +207,7 @@ __device__ __forceinline__ void kahan_add_r(float& sum, float& comp, float y) {
   sum = t;
 }
 
+template <int EJ>   // 32 * EJ >= E: logits each lane holds
 __global__ void __launch_bounds__(256)
 refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wgt,
               const float* __restrict__ wnorm2, const float* __restrict__ logits, int ld_logits, int T, int D,
@@ -217,34 +218,6 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (tok >= T) return;
   const __nv_bfloat16* xrow = x + (size_t)tok * D;
-
-  // ---- the 12 best tensor-core logits, sorted by (value desc, id asc): lane j keeps entry j ----
-  float v[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int e = lane + 32 * j;
-    v[j] = e < E ? logits[(size_t)tok * ld_logits + e] : -INFINITY;
-  }
-  float cv = -INFINITY;
-  int ci = 0x7fffffff;
-  unsigned taken = 0;
-  const int n_list = E < L_CAND ? E : L_CAND;
-  for (int it = 0; it < n_list; ++it) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = lane + 32 * j;
-      if (!((taken >> j) & 1u) && e < E && (v[j] > bv || (v[j] == bv && e < bi))) bv = v[j], bi = e;
-    }
-    for (int off = 16; off; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-    }
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    if (lane == it) cv = bv, ci = bi;
-  }
 
   // ---- |x|_2, max|x|, largest column norm ----
   float xsq = 0.f, xmax = 0.f;
@@ -268,6 +241,41 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   for (int off = 16; off; off >>= 1) wn2 = fmaxf(wn2, __shfl_xor_sync(0xffffffffu, wn2, off));
   const float xw = sqrtf(xsq) * sqrtf(wn2) * 1.002f;      // >= sum_d |x_d w_de| for every expert
   const float t2 = 2.f * kTcTrust * xw;                   // two logits further apart are ordered for sure
+
+  // ---- the best tensor-core logits, sorted by (value desc, id asc): lane j keeps entry j.  The list
+  //      stops at 12 entries, or earlier once an entry past the K-th falls below kth - 2t: nothing
+  //      after it can be a candidate. ----
+  float v[EJ];
+#pragma unroll
+  for (int j = 0; j < EJ; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? logits[(size_t)tok * ld_logits + e] : -INFINITY;
+  }
+  float cv = -INFINITY;
+  int ci = 0x7fffffff;
+  unsigned taken = 0;
+  const int n_max = E < L_CAND ? E : L_CAND;
+  int n_list = 0;
+  float kth_tc = 0.f;
+  for (int it = 0; it < n_max; ++it) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < EJ; ++j) {
+      const int e = lane + 32 * j;
+      if (!((taken >> j) & 1u) && e < E && (v[j] > bv || (v[j] == bv && e < bi))) bv = v[j], bi = e;
+    }
+    for (int off = 16; off; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (lane == it) cv = bv, ci = bi;
+    n_list = it + 1;
+    if (it == K - 1) kth_tc = bv;
+    if (it >= K && bv < kth_tc - t2) break;      // warp-uniform: bv is the same in every lane
+  }
 
   // ---- candidates: the list prefix within 2t of the K-th entry ----
   const float kth = __shfl_sync(0xffffffffu, cv, K - 1);
@@ -448,8 +456,20 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   const int grid = std::min(sm_count(), ceil_div(T, BM));
   tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, st>>>(mx, mw, p);
   BWMOE_CUDA_OK(cudaGetLastError());
-  refine_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), wgt, wnorm2, logits, p.n_mma, T, D,
-                                                E, K, weights, indices, row_amax, fb_count, fb_list);
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  const unsigned rgrid = (unsigned)ceil_div(T, 8);
+  if (E <= 32)
+    refine_kernel<1><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list);
+  else if (E <= 64)
+    refine_kernel<2><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list);
+  else if (E <= 128)
+    refine_kernel<4><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list);
+  else
+    refine_kernel<8><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list);
   BWMOE_CUDA_OK(cudaGetLastError());
   return launch_router_fallback(x, wg, T, D, E, K, weights, indices, fb_list, fb_count, st);
 }
