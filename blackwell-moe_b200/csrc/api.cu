@@ -167,7 +167,7 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   if ((rc = launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, amax_x, status,
                         at<void>(ws, L.plan_scratch), st, scale_x)))
     return rc;
-  if ((rc = launch_gather_quant(x, row_slot, row_expert, scale_x, M, D, K, at<void>(ws, L.xq), st))) return rc;
+  if ((rc = launch_scatter_quant(x, pos, indices, scale_x, T, D, K, at<void>(ws, L.xq), st))) return rc;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
                           amax_h, status, at<void>(ws, L.gemm_scratch), st)))
     return rc;

@@ -79,6 +79,8 @@ int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int
                        cudaStream_t st);
 int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,
                           cudaStream_t st);
+int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indices, const float* scales, int T,
+                         int D, int K, void* xq, cudaStream_t st);
 int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert,
                         const float* scales, int M, int D, int K, void* xq, cudaStream_t st);
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,

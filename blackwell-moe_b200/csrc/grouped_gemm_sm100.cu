@@ -68,8 +68,14 @@ struct TileCursor {
   }
 };
 
+// Eight epilogue warps: two per tensor-memory lane quarter, each taking half of the tile's columns.
+// With four, the short K loops (K = 1408: 11 blocks) finished before the previous tile's 64 KiB of
+// output had left the SM, and the MMA warp waited for its accumulator buffer.
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+
 template <bool GATE_UP, bool RAW>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -87,7 +93,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   // ---- set-up ----
   // tiles before each expert: every thread fetches the segments it owns, warp 0 scans
-  for (int e = threadIdx.x; e < 256; e += NUM_THREADS) {
+  for (int e = threadIdx.x; e < 256; e += GEMM_THREADS) {
     int t = 0;
     if (e < p.E) {
       const int rows = p.offsets[e + 1] - p.offsets[e];
@@ -103,7 +109,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, 4);
+      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -190,8 +196,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ===================== epilogue (warps 2..5) =====================
+    // ===================== epilogue (warps 2..9) =====================
     const int quarter = warp & 3;                      // TMEM lane group this warp may read
+    const int half = (warp - 2) >> 2;                  // which half of the tile's columns
     const int r_in_tile = quarter * 32 + lane;
     TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
     uint32_t local = 0;
@@ -213,7 +220,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
         float* dst_row = p.partial + ((size_t)split * p.M + row) * p.ldp;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
           uint32_t a[32];
           tmem_ld32(t_row + c * 32, a);
           tmem_ld_wait();
@@ -235,7 +242,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int n0 = n_idx * BN_HALF;
         float amax = 0.f;
 #pragma unroll 1
-        for (int c = 0; c < BN_HALF / 32; ++c) {
+        for (int c = half * (BN_HALF / 64); c < (half + 1) * (BN_HALF / 64); ++c) {
           uint32_t g[32], u[32];
           tmem_ld32(t_row + c * 32, g);
           tmem_ld32(t_row + BN_HALF + c * 32, u);
@@ -276,24 +283,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float inv = 1.0f / (sa * p.scale_b0[e]);
         const int n0 = n_idx * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t a[32];
-          tmem_ld32(t_row + c * 32, a);
+        for (int c2 = half * (BN / 128); c2 < (half + 1) * (BN / 128); ++c2) {
+          uint32_t a[2][32];                           // two 32-column loads per wait
+          tmem_ld32(t_row + c2 * 64, a[0]);
+          tmem_ld32(t_row + c2 * 64 + 32, a[1]);
           tmem_ld_wait();
-          uint32_t packed[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[2 * j]) * inv,
-                                                      __uint_as_float(a[2 * j + 1]) * inv);
-            packed[j] = *reinterpret_cast<uint32_t*>(&b2);
-          }
-          if (row_ok) {
-            __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
+          for (int q = 0; q < 2; ++q) {
+            const int c = 2 * c2 + q;
+            uint32_t packed[16];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (n0 + c * 32 + v * 8 < p.N_out)
-                reinterpret_cast<uint4*>(dst)[v] =
-                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int j = 0; j < 16; ++j) {
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[q][2 * j]) * inv,
+                                                        __uint_as_float(a[q][2 * j + 1]) * inv);
+              packed[j] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            if (row_ok) {
+              __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (n0 + c * 32 + v * 8 < p.N_out)
+                  reinterpret_cast<uint4*>(dst)[v] =
+                      make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+              }
             }
           }
         }
@@ -318,6 +330,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 
 // ---- split-K post-passes (small batches only) ---------------------------------------
+constexpr int kSplitMaxRows = 64;   // rows (T*K) up to which the K loop is split
+constexpr int kSplitMax = 8;        // slabs at most
 __device__ __forceinline__ int expert_of_row(const int32_t* __restrict__ offsets, int E, int row) {
   int lo = 0, hi = E;                       // largest e with offsets[e] <= row
   while (hi - lo > 1) {
@@ -341,12 +355,17 @@ swiglu_from_partials_kernel(const float* __restrict__ partial, int S, int M, int
   float amax = 0.f;
   if (live) {
     float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < S; ++s) {            // fixed order: deterministic
+    float4 a[kSplitMax], b[kSplitMax];       // every slab is requested before the first is used
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s) {
       const float* row = partial + ((size_t)s * M + m) * (2 * H);
-      const float4 a = reinterpret_cast<const float4*>(row)[v];
-      const float4 b = reinterpret_cast<const float4*>(row + H)[v];
-      g[0] += a.x, g[1] += a.y, g[2] += a.z, g[3] += a.w;
-      u[0] += b.x, u[1] += b.y, u[2] += b.z, u[3] += b.w;
+      a[s] = s < S ? reinterpret_cast<const float4*>(row)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+      b[s] = s < S ? reinterpret_cast<const float4*>(row + H)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s) {    // fixed order: deterministic (absent slabs add +0)
+      g[0] += a[s].x, g[1] += a[s].y, g[2] += a[s].z, g[3] += a[s].w;
+      u[0] += b[s].x, u[1] += b[s].y, u[2] += b[s].z, u[3] += b[s].w;
     }
     const float inv_g = 1.0f / (sx[e] * sg[e]), inv_u = 1.0f / (sx[e] * su[e]);
     float hv[4];
@@ -384,10 +403,12 @@ down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D
   const int m = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
   const int e = expert_of_row(offsets, E, m);
   float a[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < S; ++s) {
-    const float4 t = reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v];
-    a[0] += t.x, a[1] += t.y, a[2] += t.z, a[3] += t.w;
-  }
+  float4 t[kSplitMax];
+#pragma unroll
+  for (int s = 0; s < kSplitMax; ++s)
+    t[s] = s < S ? reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int s = 0; s < kSplitMax; ++s) a[0] += t[s].x, a[1] += t[s].y, a[2] += t[s].z, a[3] += t[s].w;
   const float inv = 1.0f / (sh[e] * sd[e]);
   __nv_bfloat162 lo = __floats2bfloat162_rn(a[0] * inv, a[1] * inv), hi = __floats2bfloat162_rn(a[2] * inv, a[3] * inv);
   reinterpret_cast<uint2*>(y + (size_t)m * D)[v] =
@@ -415,10 +436,12 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
     if (m < 0) continue;
     const int e = expert_of_row(offsets, E, m);
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < S; ++s) {
-      const float4 q = reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v];
-      a[0] += q.x, a[1] += q.y, a[2] += q.z, a[3] += q.w;
-    }
+    float4 q[kSplitMax];
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s)
+      q[s] = s < S ? reinterpret_cast<const float4*>(partial + ((size_t)s * M + m) * D)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s) a[0] += q[s].x, a[1] += q[s].y, a[2] += q[s].z, a[3] += q[s].w;
     const float inv = 1.0f / (sh[e] * sd[e]);
     const __nv_bfloat162 lo = __floats2bfloat162_rn(a[0] * inv, a[1] * inv), hi = __floats2bfloat162_rn(a[2] * inv, a[3] * inv);
     reinterpret_cast<uint2*>(y + (size_t)m * D)[v] =
@@ -452,8 +475,6 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
 
 // Split-K is for small batches, where a few experts x column blocks cannot occupy every SM:
 // the K loop of each tile is cut so that about four waves of tiles exist.
-constexpr int kSplitMaxRows = 64;
-constexpr int kSplitMax = 8;
 struct SplitPlan {
   int split_k, k_per_split;
 };
@@ -480,7 +501,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap
   BWMOE_CUDA_OK(attr_err);
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  grouped_gemm_kernel<GATE_UP, RAW><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  grouped_gemm_kernel<GATE_UP, RAW><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

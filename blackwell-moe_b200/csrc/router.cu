@@ -42,14 +42,14 @@ __device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
 // Top-K (+1) selection of one token by one warp.  Writes weights/indices; returns true when
 // two neighbouring selected logits (or the K-th and the best rejected one) are within thr.
 __device__ __forceinline__ bool select_token(const float* lg_row, int E, int K, float thr_rel, float thr_abs,
-                                             float* w_out, int32_t* i_out, int lane) {
+                                             float* w_out, int32_t* i_out, int lane, float* cut_out = nullptr) {
   float v[kMaxEJ];
   float lmax = 0.f;
 #pragma unroll
   for (int j = 0; j < kMaxEJ; ++j) {
     const int ee = lane + 32 * j;
     v[j] = ee < E ? lg_row[ee] : -INFINITY;
-    if (ee < E) lmax = fmaxf(lmax, fabsf(v[j]));
+    if (ee < E && fabsf(v[j]) < INFINITY) lmax = fmaxf(lmax, fabsf(v[j]));
   }
   for (int off = 16; off; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
   const float thr = thr_abs + lmax * thr_rel;
@@ -74,6 +74,9 @@ __device__ __forceinline__ bool select_token(const float* lg_row, int E, int K, 
     prev = best.v;
     if (it < K && lane == it) chosen = best;
   }
+  // Experts whose approximate logit lies below this cannot reach the top K whatever the rounding did
+  // (prev is the best rejected logit, or the K-th one when K == E).
+  if (cut_out != nullptr && lane == 0) *cut_out = prev - thr;
   // weights: softmax over the selected logits == softmax over all experts, renormalised
   const float top = __shfl_sync(0xffffffffu, chosen.v, 0);
   const float p = lane < K ? expf(chosen.v - top) : 0.f;
@@ -150,6 +153,35 @@ __device__ void exact_logits_block(const __nv_bfloat16* __restrict__ xrow, const
   __syncthreads();
 }
 
+// Exact logits of at most 32 listed experts of one token (fp64, whole block), rounded once to fp32;
+// every other expert's logit becomes -inf.  Threads are laid out as (candidate, d-group); partial sums
+// meet in a fixed order (shuffle tree inside the warp, then warp by warp).
+__device__ void exact_candidates_block(const __nv_bfloat16* __restrict__ xrow, const __nv_bfloat16* __restrict__ wg,
+                                       int D, int E, const int* cand /* smem */, int n_cand, float* lg_row,
+                                       double* dpart /* smem [nwarps][32] */) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
+  int P = 1;
+  while (P < n_cand) P <<= 1;                  // lanes per d, a power of two <= 32
+  const int c = tid % P, dg = tid / P, NG = nthreads / P;
+  double a = 0.0;
+  if (c < n_cand) {
+    const int e = cand[c];
+#pragma unroll 4
+    for (int d = dg; d < D; d += NG)
+      a = fma((double)__bfloat162float(xrow[d]), (double)__bfloat162float(wg[(size_t)d * E + e]), a);
+  }
+  for (int off = P; off < 32; off <<= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+  if (lane < P) dpart[warp * 32 + lane] = a;
+  for (int e = tid; e < E; e += nthreads) lg_row[e] = -INFINITY;
+  __syncthreads();
+  if (tid < n_cand) {
+    double sum = 0.0;
+    for (int w = 0; w < nwarps; ++w) sum += dpart[w * 32 + tid];
+    lg_row[cand[tid]] = (float)sum;
+  }
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------
 // One block per token: threads = (expert octet, d-group).  Used when the gate is narrow
 // (E <= 16: the whole w_gate stays in L1) or the batch is small (decode), where tiling
@@ -159,12 +191,13 @@ __global__ void __launch_bounds__(1024)
 router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
                     int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
                     float* __restrict__ row_amax) {
-  __shared__ float part[32][256];     // per-warp partial logits
+  __shared__ __align__(16) float part[32][256];     // per-warp partial logits (reused for fp64 partials)
   __shared__ float lg[256];
   __shared__ double dsum[256];
   __shared__ float s_stat[3][32];
   __shared__ float s_wsq[256];        // squared column norms of w_gate
-  __shared__ int s_amb;
+  __shared__ int s_amb, s_ncand, s_cand[32];
+  __shared__ float s_cut;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int tok = blockIdx.x;
   const __nv_bfloat16* xrow = x + (size_t)tok * D;
@@ -265,15 +298,27 @@ router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const float gamma = (float)(kInner + 10) * 5.9604645e-8f * 1.05f;
   if (warp == 0) {
     const bool amb = select_token(lg, E, K, 1.0e-6f, 2.f * gamma * xw_bound, weights + (size_t)tok * K,
-                                  indices + (size_t)tok * K, lane);
+                                  indices + (size_t)tok * K, lane, &s_cut);
     if (lane == 0) {
       s_amb = amb ? 1 : 0;
+      s_ncand = 0;
       if (row_amax != nullptr) row_amax[tok] = m_tok;
     }
   }
   __syncthreads();
   if (!s_amb) return;
-  exact_logits_block(xrow, wg, D, E, lg, dsum);
+  // near tie: only the experts that can still reach the top K are evaluated exactly
+  for (int e = tid; e < E; e += blockDim.x) {
+    if (lg[e] >= s_cut) {
+      const int slot = atomicAdd(&s_ncand, 1);
+      if (slot < 32) s_cand[slot] = e;
+    }
+  }
+  __syncthreads();
+  if (s_ncand <= 32)
+    exact_candidates_block(xrow, wg, D, E, s_cand, s_ncand, lg, reinterpret_cast<double*>(&part[0][0]));
+  else
+    exact_logits_block(xrow, wg, D, E, lg, dsum);
   if (warp == 0)
     select_token(lg, E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, lane);
 }

@@ -199,7 +199,7 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 }
 
 // ---- 3. exact refinement of the candidates: one warp per token ------------------------------
-constexpr int kInnerR = 16;
+constexpr int kInnerR = 16;   // products per plain-FMA block of the recomputation
 __device__ __forceinline__ void kahan_add_r(float& sum, float& comp, float y) {
   const float yc = __fsub_rn(y, comp);
   const float t = __fadd_rn(sum, yc);
@@ -293,52 +293,39 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   const unsigned redo = (up_mask | (up_mask >> 1)) & ((1u << n_cand) - 1u);   // both members of every close pair
   float mine = cv;
   if (redo != 0u) {
-    float acc[L_CAND], comp[L_CAND], inner[L_CAND];
-    int cid[L_CAND];
+    // one candidate at a time (usually two or three): x is re-read from L1, few registers are live
+    for (unsigned rm = redo; rm != 0u; rm &= rm - 1u) {        // warp-uniform
+      const int c = __ffs(rm) - 1;
+      const __nv_bfloat16* wrow = wgt + (size_t)__shfl_sync(0xffffffffu, ci, c) * D;
+      float acc = 0.f, comp = 0.f;
+      for (int d0 = lane * 8; d0 < D; d0 += 512) {             // two 8-product steps = one plain-FMA block
+        const bool two = d0 + 256 < D;
+        const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + d0);
+        const uint4 w0 = __ldg(reinterpret_cast<const uint4*>(wrow + d0));
+        const uint4 x1 = two ? *reinterpret_cast<const uint4*>(xrow + d0 + 256) : make_uint4(0u, 0u, 0u, 0u);
+        const uint4 w1 = two ? __ldg(reinterpret_cast<const uint4*>(wrow + d0 + 256)) : make_uint4(0u, 0u, 0u, 0u);
+        const __nv_bfloat162* px0 = reinterpret_cast<const __nv_bfloat162*>(&x0);
+        const __nv_bfloat162* pw0 = reinterpret_cast<const __nv_bfloat162*>(&w0);
+        const __nv_bfloat162* px1 = reinterpret_cast<const __nv_bfloat162*>(&x1);
+        const __nv_bfloat162* pw1 = reinterpret_cast<const __nv_bfloat162*>(&w1);
+        float inner = 0.f;
 #pragma unroll
-    for (int c = 0; c < L_CAND; ++c) {
-      acc[c] = 0.f, comp[c] = 0.f, inner[c] = 0.f;
-      cid[c] = __shfl_sync(0xffffffffu, ci, c);
-    }
-    int inner_n = 0;
-    for (int d0 = lane * 8; d0 < D; d0 += 256) {
-      const uint4 xraw = *reinterpret_cast<const uint4*>(xrow + d0);
-      const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xraw);
-      float xv[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(px[j]);
-        xv[2 * j] = f.x, xv[2 * j + 1] = f.y;
-      }
-#pragma unroll
-      for (int c = 0; c < L_CAND; ++c) {
-        if ((redo >> c) & 1u) {
-          const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(wgt + (size_t)cid[c] * D + d0));
-          const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(pw[j]);
-            inner[c] = fmaf(xv[2 * j], f.x, inner[c]);
-            inner[c] = fmaf(xv[2 * j + 1], f.y, inner[c]);
-          }
+        for (int j = 0; j < 4; ++j) {
+          const float2 fx = __bfloat1622float2(px0[j]), fw = __bfloat1622float2(pw0[j]);
+          inner = fmaf(fx.x, fw.x, inner);
+          inner = fmaf(fx.y, fw.y, inner);
         }
-      }
-      inner_n += 8;
-      if (inner_n == kInnerR) {
 #pragma unroll
-        for (int c = 0; c < L_CAND; ++c) {
-          kahan_add_r(acc[c], comp[c], inner[c]);
-          inner[c] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+          const float2 fx = __bfloat1622float2(px1[j]), fw = __bfloat1622float2(pw1[j]);
+          inner = fmaf(fx.x, fw.x, inner);
+          inner = fmaf(fx.y, fw.y, inner);
         }
-        inner_n = 0;
+        kahan_add_r(acc, comp, inner);
       }
-    }
-#pragma unroll
-    for (int c = 0; c < L_CAND; ++c) {
-      kahan_add_r(acc[c], comp[c], inner[c]);
-      float s = __fsub_rn(acc[c], comp[c]);
-      for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      if (lane == c && ((redo >> c) & 1u)) mine = s;
+      float sum = __fsub_rn(acc, comp);
+      for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      if (lane == c) mine = sum;
     }
     // recomputed logits carry a known bound; pairs of them still inside it go to fp64
     const float gamma = (float)(kInnerR + 8) * 5.9604645e-8f * 1.05f;
