@@ -54,12 +54,16 @@ def gateup_traffic_bytes(workload, T, D, H, E, K):
     return weights + (measured - weights) * (T / t0)
 
 
-def kernels_per_forward(M: int) -> int:
-    """Kernels of ours launched by one single-GPU forward of M = T*K permuted rows."""
-    if M > 1024:   # router, 3 plan passes, segment scales, gather+quant, gate/up GEMM, requant, down GEMM, combine
-        return 10
-    n = 7          # router, one-block plan, gather+quant, gate/up GEMM, requant, down GEMM, combine
-    return n + 2 if M <= 64 else n   # split-K adds one fixed-order summation pass behind each GEMM
+def kernels_per_forward(M: int, T: int = 0, D: int = 0, E: int = 0, K: int = 0) -> int:
+    """Kernels of ours launched by one single-GPU forward (per-tensor recipe) of M = T*K permuted rows."""
+    tc_router = T >= 1024 and 8 <= E <= 256 and E % 8 == 0 and K <= 8 and K < E and D % 64 == 0
+    router = 4 if tc_router else 1   # transpose, tensor-core logits, refine, all-expert fallback | one SIMT kernel
+    if M > 1024:   # + 3 plan passes, segment scales, scatter+quant, gate/up GEMM, requant, down GEMM, combine
+        return router + 9
+    if M > 64:     # + one-block plan, scatter+quant, gate/up GEMM, requant, down GEMM, combine
+        return router + 6
+    # split-K: + plan, scatter+quant, gate/up GEMM, slab sum + SwiGLU, requant, down GEMM, slab sum + combine
+    return router + 7
 
 
 def parse():
@@ -71,6 +75,8 @@ def parse():
     ap.add_argument("--workload", default="mixtral-8x7b", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's prefill size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-transport", default=None, choices=["auto", "nccl", "peer"],
+                    help="expert-parallel exchange (N > 1): NCCL all-to-all or stores/loads over peer memory")
     return ap.parse_args()
 
 
@@ -265,6 +271,8 @@ def run_ours(args):
         W = synth_weights(D, H, E, dev, seed=7, experts=mine, block=block)
         ep = ExpertParallelMoE(w_gate, W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"],
                                num_experts=E, top_k=K, group=dist.group.WORLD)
+        if args.ep_transport:
+            ep.transport = args.ep_transport
         step = lambda: ep.forward(x)                                     # noqa: E731
 
     def barrier():
@@ -393,13 +401,17 @@ def run_ours(args):
         "warmup": max(3, args.warmup), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": f"{args.workload} D={D} H={H} E={E} top_k={K} T={T} per GPU",
-                   "parallelism": "single GPU" if world == 1 else f"ep{world} (experts sharded, tokens per rank fixed)",
+                   "parallelism": "single GPU" if world == 1 else
+                   f"ep{world} (experts sharded, tokens per rank fixed, exchange: "
+                   f"{'peer memory' if getattr(ep, '_peer', None) else 'NCCL all-to-all'})",
                    "l2": ("inputs larger than L2 (weights %.0f MB per step)" % (3.0 * E * D * H / world / 1e6)
                           if flush is None else "flushed: a 512 MiB buffer is rewritten before every timed step")},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 2 * world,
                 "d2h_bytes_per_step": T * D * 2 * world, "ms_per_step": e2e_secs / args.steps * 1e3, "api": e2e_api,
                 "sync_call_value": tokens_total / e2e_sync_secs, "sync_call_ms_per_step": e2e_sync_secs / args.steps * 1e3},
-        "gpu_launches": (9 if block and T * K > 1024 else 6 if block else kernels_per_forward(T * K)) * args.steps,
+        # expert parallel: the same kernels plus one more segment-scale launch (the library's; NCCL's are not counted)
+        "gpu_launches": ((9 if block and T * K > 1024 else 6 if block else kernels_per_forward(T * K, T, D, E, K))
+                         + (1 if world > 1 and not block else 0)) * args.steps,
         "clocks": clocks.summary(),
     }
     if roofline is not None:

@@ -531,6 +531,20 @@ int bwmoe_down(const void* hq, const int32_t* offsets, const float* sh, const vo
   return launch_down(hq, offsets, sh, wd, sd, M, D, H, E, y, status, scratch, static_cast<cudaStream_t>(stream));
 }
 
+int bwmoe_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
+                              const int32_t* delta, int T, int D, int K, int experts_per_rank,
+                              void* const* dst_of_rank, int n_ranks, void* stream) {
+  return launch_scatter_quant_peers(x, pos, indices, scales, delta, T, D, K, experts_per_rank, dst_of_rank, n_ranks,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_combine_peers(void* const* y_of_rank, int n_ranks, const int32_t* pos, const int32_t* indices,
+                        const float* weights, const int32_t* delta, int experts_per_rank, int T, int D, int K,
+                        void* out, void* stream) {
+  return launch_combine_peers(y_of_rank, n_ranks, pos, indices, weights, delta, experts_per_rank, T, D, K, out,
+                              static_cast<cudaStream_t>(stream));
+}
+
 int bwmoe_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K, void* out,
                   void* stream) {
   return launch_combine(y, pos, weights, T, D, K, out, static_cast<cudaStream_t>(stream));

@@ -81,6 +81,12 @@ int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, 
                           cudaStream_t st);
 int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indices, const float* scales, int T,
                          int D, int K, void* xq, cudaStream_t st);
+int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
+                               const int32_t* delta, int T, int D, int K, int experts_per_rank, void* const* dst,
+                               int n_ranks, cudaStream_t st);
+int launch_combine_peers(void* const* src, int n_ranks, const int32_t* pos, const int32_t* indices,
+                         const float* weights, const int32_t* delta, int experts_per_rank, int T, int D, int K,
+                         void* out, cudaStream_t st);
 int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* row_expert,
                         const float* scales, int M, int D, int K, void* xq, cudaStream_t st);
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,

@@ -272,6 +272,75 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restr
   }
 }
 
+// Expert-parallel dispatch fused into the quantisation: the row of slot (t, k), bound for expert e, is
+// written straight into the memory of the rank that owns e (peer stores over NVLink; the owner's own rows
+// are ordinary local stores).  dst[r] is rank r's receive buffer; the row lands at
+// pos[t, k] + delta[e], which is its place in the owner's per-expert segments ordered by (source rank,
+// source row).  No multicast, no bulk copies: plain 16-byte stores.
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+__global__ void __launch_bounds__(256)
+scatter_quant_peers_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos,
+                           const int32_t* __restrict__ indices, const float* __restrict__ scales,
+                           const int32_t* __restrict__ delta, unsigned T, unsigned W, int K, int experts_per_rank,
+                           const PeerPtrs dst) {
+  const unsigned per_row = W / 16;
+  const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= T * per_row) return;
+  const unsigned t = p / per_row, c = p - t * per_row;
+  const uint4* in = reinterpret_cast<const uint4*>(x + (size_t)t * W) + 2 * c;
+  const uint4 r0 = in[0], r1 = in[1];
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const int row = pos[(size_t)t * K + k];
+    if (row < 0) continue;
+    const int e = indices[(size_t)t * K + k];
+    const unsigned long long s2 = splat2(scales[e]);
+    uint8_t* base = static_cast<uint8_t*>(dst.p[e / experts_per_rank]);
+    reinterpret_cast<uint4*>(base + (size_t)(row + delta[e]) * W)[c] =
+        make_uint4(e4m3x4_scaled(r0.x, r0.y, s2), e4m3x4_scaled(r0.z, r0.w, s2), e4m3x4_scaled(r1.x, r1.y, s2),
+                   e4m3x4_scaled(r1.z, r1.w, s2));
+  }
+}
+
+// Expert-parallel way back fused into the combine: the result row of slot (t, k) is read from the
+// memory of the rank that computed it (peer loads), same arithmetic and order as combine_kernel.
+__global__ void __launch_bounds__(256)
+combine_peers_kernel(const PeerPtrs src, const int32_t* __restrict__ pos, const int32_t* __restrict__ indices,
+                     const float* __restrict__ weights, const int32_t* __restrict__ delta, int experts_per_rank,
+                     int T, int D, int K, __nv_bfloat16* __restrict__ out) {
+  const int vec_per_row = D / 8;
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (size_t)T * vec_per_row) return;
+  const int t = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const int p = pos[(size_t)t * K + k];
+    if (p < 0) continue;
+    const int e = indices[(size_t)t * K + k];
+    const float w = bf16_round(weights[(size_t)t * K + k]);
+    const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(src.p[e / experts_per_rank]);
+    const uint4 raw = reinterpret_cast<const uint4*>(y + (size_t)(p + delta[e]) * D)[v];
+    const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(q[i]);
+      acc[2 * i] += bf16_round(f.x * w);
+      acc[2 * i + 1] += bf16_round(f.y * w);
+    }
+  }
+  uint4 o;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) op[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  reinterpret_cast<uint4*>(out + (size_t)t * D)[v] = o;
+}
+
 // ---- out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ) ----
 // Optional tail (the block glue of FP8MoELayer.forward, src/blackwell_moe/runtime/deepseek_patch.py:51-53):
 //   out = bf16( bf16(routed * scale) + residual ) with routed = the bf16 sum above.
@@ -491,6 +560,45 @@ int launch_combine(const void* y, const int32_t* pos, const float* weights, int 
                                                               weights, T, D, K,
                                                               static_cast<__nv_bfloat16*>(out), scale,
                                                               static_cast<const __nv_bfloat16*>(residual));
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
+                               const int32_t* delta, int T, int D, int K, int experts_per_rank, void* const* dst,
+                               int n_ranks, cudaStream_t st) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_quant_peers: T=%d D=%d K=%d", T, D, K);
+  BWMOE_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers && experts_per_rank >= 1, BWMOE_ERR_UNSUPPORTED,
+                "scatter_quant_peers: %d ranks (at most %d)", n_ranks, kMaxPeers);
+  BWMOE_REQUIRE(x && pos && indices && scales && delta && dst, BWMOE_ERR_NULL, "scatter_quant_peers: null pointer");
+  PeerPtrs pp{};
+  for (int r = 0; r < n_ranks; ++r) {
+    BWMOE_REQUIRE(dst[r] != nullptr && aligned16(dst[r]), BWMOE_ERR_BAD_ALIGN, "scatter_quant_peers: buffer of rank %d", r);
+    pp.p[r] = dst[r];
+  }
+  BWMOE_REQUIRE(aligned16(x), BWMOE_ERR_BAD_ALIGN, "scatter_quant_peers: x must be 16-byte aligned");
+  scatter_quant_peers_kernel<<<quant_grid(T, D), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), pos, indices,
+                                                               scales, delta, T, D, K, experts_per_rank, pp);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_combine_peers(void* const* src, int n_ranks, const int32_t* pos, const int32_t* indices,
+                         const float* weights, const int32_t* delta, int experts_per_rank, int T, int D, int K,
+                         void* out, cudaStream_t st) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 8 == 0, BWMOE_ERR_BAD_SHAPE, "combine_peers: T=%d D=%d K=%d", T, D, K);
+  BWMOE_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers && experts_per_rank >= 1, BWMOE_ERR_UNSUPPORTED,
+                "combine_peers: %d ranks (at most %d)", n_ranks, kMaxPeers);
+  BWMOE_REQUIRE(src && pos && indices && weights && delta && out, BWMOE_ERR_NULL, "combine_peers: null pointer");
+  PeerPtrs pp{};
+  for (int r = 0; r < n_ranks; ++r) {
+    BWMOE_REQUIRE(src[r] != nullptr && aligned16(src[r]), BWMOE_ERR_BAD_ALIGN, "combine_peers: buffer of rank %d", r);
+    pp.p[r] = src[r];
+  }
+  BWMOE_REQUIRE(aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine_peers: out must be 16-byte aligned");
+  const size_t n = (size_t)T * (D / 8);
+  combine_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(pp, pos, indices, weights, delta, experts_per_rank,
+                                                                    T, D, K, static_cast<__nv_bfloat16*>(out));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

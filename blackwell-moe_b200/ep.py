@@ -27,6 +27,8 @@ tokens.  The index arithmetic (:class:`ExchangePlan`, :func:`dispatch`,
 from __future__ import annotations
 
 import ctypes as C
+import os
+import warnings
 
 import torch
 import torch.distributed as dist
@@ -135,6 +137,118 @@ class ExpertParallelMoE:
     #: SMs the persistent GEMMs leave to NCCL while micro-batches overlap (they otherwise hold every SM
     #: until they finish, and the collective queued beside them cannot start)
     sm_reserve = 0
+    #: "nccl": all-to-all over NCCL plus a row regroup on either side.  "peer": the quantisation kernel stores
+    #: each row straight into its owner's memory and the combine kernel loads result rows from their owners'
+    #: memory (symmetric memory over NVLink, three stream-ordered barriers per step, no collective on the
+    #: data path).  "auto": "peer" where symmetric memory can be set up (per-tensor recipe, CUDA, <= 8 ranks).
+    transport = "nccl"
+    _peer = None
+
+    def _peer_setup(self, rows_cap: int):
+        """Symmetric receive (FP8 rows) and result (bf16 rows) buffers of ``rows_cap`` rows, mapped on every rank.
+        Collective.  Returns False (on every rank alike) when symmetric memory is not available."""
+        if self._peer is not None and self._peer["cap"] >= rows_cap:
+            return True
+        if self._peer is False:
+            return False
+        ok = 1
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer loads/stores only
+            import torch.distributed._symmetric_memory as symm
+            group = self.group if self.group is not None else dist.group.WORLD
+            xq = symm.empty(rows_cap * self.D, dtype=torch.uint8, device=self.dev)
+            y = symm.empty(rows_cap * self.D, dtype=torch.bfloat16, device=self.dev)
+            hx, hy = symm.rendezvous(xq, group), symm.rendezvous(y, group)
+            G = self.world
+            peer = dict(cap=rows_cap, xq=xq, y=y, hx=hx, hy=hy,
+                        xq_ptrs=(C.c_void_p * G)(*[int(p) for p in hx.buffer_ptrs]),
+                        y_ptrs=(C.c_void_p * G)(*[int(p) for p in hy.buffer_ptrs]))
+        except Exception as ex:      # noqa: BLE001 - any failure means "use NCCL", agreed on below
+            ok, peer = 0, repr(ex)
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            if self.rank == 0:
+                warnings.warn(f"expert parallelism: symmetric memory unavailable ({peer if not ok else 'on a peer'}); "
+                              "using the NCCL all-to-all transport")
+            self._peer = False
+            return False
+        self._peer = peer
+        return True
+
+    def _use_peers(self, T: int) -> bool:
+        if self.transport == "nccl" or self.block or self.dev.type != "cuda" or self.world > 8:
+            return False
+        ok = self._peer_setup(self.world * T * self.K)       # worst case: every row of every rank lands here
+        if not ok and self.transport == "peer":
+            raise RuntimeError("transport='peer' requested but symmetric memory could not be set up")
+        return ok
+
+    def _forward_peers(self, x, weights, indices, row_amax, host_in):
+        """Per-tensor recipe over peer memory: route/plan locally, exchange counts and maxima, then
+        barrier - quantise-and-store to the owners - barrier - local GEMMs - barrier - combine from the owners."""
+        lib, dev, E, K, D, H, el = _lib.lib(), self.dev, self.E, self.K, self.D, self.H, self.el
+        G, rank, T = self.world, self.rank, x.shape[0]
+        M = T * K
+        st = torch.cuda.current_stream(dev).cuda_stream
+        i32, f32, u8 = torch.int32, torch.float32, torch.uint8
+        new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
+        peer = self._peer
+        status = torch.zeros(4, dtype=i32, device=dev)
+        offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
+        stats = new(2 * E, dtype=f32)                                   # [amax | counts]
+        scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=u8)
+        _lib.check(lib.bwmoe_permute_plan(indices.data_ptr(), row_amax.data_ptr(), T, E, K, offsets.data_ptr(),
+                                          pos.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(),
+                                          stats[:E].data_ptr(), status.data_ptr(), scratch.data_ptr(), st))
+        stats[E:].view(i32).copy_(offsets[1:] - offsets[:-1])
+        gathered = new(G * 2 * E, dtype=f32)
+        dist.all_gather_into_tensor(gathered, stats, group=self.group)
+        gathered = gathered.view(G, 2 * E)
+        amax = gathered[:, :E].amax(0).contiguous()
+        counts = gathered[:, E:].contiguous().view(i32)                 # [G, E] rows rank s has for expert e
+        counts_host = counts.cpu()                                      # the step's one host synchronisation
+        scale_x = new(E, dtype=f32)
+        _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
+        sx_local = scale_x[rank * el:(rank + 1) * el].contiguous()
+        # where my rows of expert e start inside e's segment on its owner, relative to my own permuted order
+        total = counts.sum(0, dtype=i32).view(G, el)
+        seg_start = (torch.cumsum(total, 1, dtype=i32) - total).view(E)
+        below = counts[:rank].sum(0, dtype=i32) if rank > 0 else torch.zeros(E, dtype=i32, device=dev)
+        delta = (seg_start + below - offsets[:E]).contiguous()
+        seg = total[rank]
+        offsets_l = torch.zeros(el + 1, dtype=i32, device=dev)
+        offsets_l[1:] = torch.cumsum(seg, 0, dtype=i32)
+        R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
+        assert R <= peer["cap"], (R, peer["cap"])
+
+        peer["hx"].barrier()             # every rank is done with the previous step's buffers
+        _lib.check(lib.bwmoe_scatter_quant_peers(x.data_ptr(), pos.data_ptr(), indices.data_ptr(), scale_x.data_ptr(),
+                                                 delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, st))
+        peer["hx"].barrier()             # every row of this step has landed
+        if R > 0:
+            row_expert_l = torch.repeat_interleave(torch.arange(el, device=dev, dtype=i32), seg.to(torch.int64),
+                                                   output_size=R)
+            amax_h = torch.zeros(el, dtype=f32, device=dev)
+            h, hq = new(R, H, dtype=torch.bfloat16), new(R, H, dtype=u8)
+            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, D, H, el)), dtype=u8)
+            _lib.check(lib.bwmoe_gateup_swiglu(peer["xq"].data_ptr(), offsets_l.data_ptr(), sx_local.data_ptr(),
+                                               self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                               self.su.data_ptr(), R, D, H, el, h.data_ptr(), amax_h.data_ptr(),
+                                               status.data_ptr(), gs.data_ptr(), st))
+            scale_h = new(el, dtype=f32)
+            _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
+            _lib.check(lib.bwmoe_requant(h.data_ptr(), row_expert_l.data_ptr(), scale_h.data_ptr(), R, H,
+                                         hq.data_ptr(), st))
+            _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
+                                      self.sd.data_ptr(), R, D, H, el, peer["y"].data_ptr(), status.data_ptr(),
+                                      gs.data_ptr(), st))
+        peer["hy"].barrier()             # every rank's result rows are complete
+        out = new(T, D, dtype=torch.bfloat16)
+        _lib.check(lib.bwmoe_combine_peers(peer["y_ptrs"], G, pos.data_ptr(), indices.data_ptr(), weights.data_ptr(),
+                                           delta.data_ptr(), el, T, D, K, out.data_ptr(), st))
+        self.last_status = status
+        return self._finish(out, host_in)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         host_in = not x.is_cuda
@@ -155,6 +269,8 @@ class ExpertParallelMoE:
             offsets, pos, row_slot, row_expert = (new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32),
                                                   new(M, dtype=i32))
             return self._forward_block(x, weights, indices, offsets, pos, row_slot, row_expert, host_in)
+        if self._use_peers(T):
+            return self._forward_peers(x, weights, indices, row_amax, host_in)
 
         # ---- plan every micro-batch, exchange counts and activation maxima once ----
         nmb = self.micro_batches if T >= self.micro_batch_min_tokens * self.micro_batches else 1

@@ -315,6 +315,27 @@ int bwmoe_down(const void* d_hq, const int32_t* d_offsets, const float* d_scales
 int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights, int T, int D, int K,
                   void* d_out, void* stream);
 
+/*
+ * Expert-parallel transport over peer memory (one process per GPU, the buffers of every rank mapped
+ * into each process; the host pointer arrays hold one device pointer per rank).  No counterpart in
+ * the reference, which is single-GPU (docs/DESIGN.md:24 names expert parallelism as future work).
+ *
+ * bwmoe_scatter_quant_peers: quantise the token rows (as bwmoe_gather_quant does) and store the row of
+ *   slot (t,k), routed to expert e, into row d_pos[t*K+k] + d_delta[e] of the receive buffer of rank
+ *   e / experts_per_rank.  d_delta[e] = (first row of e's segment on its owner, plus the rows the lower
+ *   ranks send to e) - (first row of e among the caller's permuted rows).
+ * bwmoe_combine_peers: bwmoe_combine, reading the result row of slot (t,k) from the same place in the
+ *   result buffer of the rank that owns its expert.
+ * The caller orders the steps across ranks (a barrier before the stores, one after them, one before
+ * the loads).  At most 8 ranks.
+ */
+int bwmoe_scatter_quant_peers(const void* d_x, const int32_t* d_pos, const int32_t* d_indices,
+                              const float* d_scales, const int32_t* d_delta, int T, int D, int K,
+                              int experts_per_rank, void* const* h_dst_of_rank, int n_ranks, void* stream);
+int bwmoe_combine_peers(void* const* h_y_of_rank, int n_ranks, const int32_t* d_pos, const int32_t* d_indices,
+                        const float* d_weights, const int32_t* d_delta, int experts_per_rank, int T, int D,
+                        int K, void* d_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,4 +1,5 @@
-"""Expert-parallel forward on 2 GPUs (NCCL) against the single-GPU forward.
+"""Expert-parallel forward on 2 GPUs (both transports: NCCL all-to-all and peer memory) against the
+single-GPU forward.
 
 Needs two CUDA devices; skipped otherwise.  Every rank builds the same seeded
 inputs, keeps its shard of the experts and its slice of the tokens; the
@@ -38,9 +39,13 @@ def _worker(rank, world, port, ret):
         from helpers import make_inputs
         msgs = []
         # the last two shapes are split into micro-batches (asynchronous, overlapped exchanges)
-        for (T, D, E, K, H, min_tok) in ((96, 256, 8, 2, 256, 2048), (33, 512, 16, 4, 384, 2048),
-                                         (700, 256, 4, 2, 128, 2048), (700, 256, 4, 2, 128, 100),
-                                         (301, 256, 2, 2, 128, 50)):
+        cases = [(s, "nccl") for s in ((96, 256, 8, 2, 256, 2048), (33, 512, 16, 4, 384, 2048),
+                                       (700, 256, 4, 2, 128, 2048), (700, 256, 4, 2, 128, 100),
+                                       (301, 256, 2, 2, 128, 50))]
+        # rows stored straight into the owner's memory, results loaded from it (symmetric memory)
+        cases += [(s, "peer") for s in ((96, 256, 8, 2, 256, 2048), (33, 512, 16, 4, 384, 2048),
+                                        (700, 256, 4, 2, 128, 2048), (301, 256, 2, 2, 128, 2048))]
+        for (T, D, E, K, H, min_tok), transport in cases:
             inp = make_inputs(world * T, D, E, K, H, seed=T + E, keep_bf16=False)
             c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
             el = E // world
@@ -48,14 +53,20 @@ def _worker(rank, world, port, ret):
             ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c["s_gate"][sl],
                                    c["s_up"][sl], c["s_down"][sl], num_experts=E, top_k=K)
             ep.micro_batch_min_tokens = min_tok
+            ep.transport = transport
             out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
             assert int(ep.last_status[0]) == 0
             full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
             dist.all_gather_into_tensor(full, out)
             ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"],
                                      c["s_down"], top_k=K)
+            if transport == "peer":
+                assert ep._peer, "the peer transport was not set up"
+                out2 = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())     # buffers are reused
+                if not torch.equal(out2, out):
+                    msgs.append(f"shape {(T, D, E, K, H)} peer: second step differs")
             if not torch.equal(full, ref):
-                msgs.append(f"shape {(T, D, E, K, H, min_tok)}: max diff {(full.float() - ref.float()).abs().max().item()}")
+                msgs.append(f"shape {(T, D, E, K, H, min_tok)} {transport}: max diff {(full.float() - ref.float()).abs().max().item()}")
             host = ep.forward(inp["x"][rank * T:(rank + 1) * T].contiguous().pin_memory())
             if not torch.equal(host, out.cpu()):
                 msgs.append(f"shape {(T, D, E, K, H)}: host-buffer path differs")
