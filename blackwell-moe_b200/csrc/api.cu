@@ -531,6 +531,15 @@ int bwmoe_down(const void* hq, const int32_t* offsets, const float* sh, const vo
   return launch_down(hq, offsets, sh, wd, sd, M, D, H, E, y, status, scratch, static_cast<cudaStream_t>(stream));
 }
 
+int bwmoe_down_peers(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd, int M,
+                     int D, int H, int E, const int32_t* home_counts, const int32_t* home_first,
+                     void* const* y_of_rank, int n_ranks, int32_t* status, void* stream) {
+  BWMOE_REQUIRE(y_of_rank != nullptr && n_ranks >= 1 && n_ranks <= 8, BWMOE_ERR_UNSUPPORTED, "down_peers: %d ranks", n_ranks);
+  const HomeRoute route{n_ranks, home_counts, home_first, y_of_rank};
+  return launch_down(hq, offsets, sh, wd, sd, M, D, H, E, y_of_rank[0], status, nullptr, static_cast<cudaStream_t>(stream),
+                     nullptr, nullptr, &route);
+}
+
 int bwmoe_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                               const int32_t* delta, int T, int D, int K, int experts_per_rank,
                               void* const* dst_of_rank, int n_ranks, void* stream) {

@@ -110,9 +110,17 @@ struct CombineArgs {
   float scale;
   const void* residual;
 };
+// Expert-parallel return route for the down projection's epilogue: counts[s*E+e] rows of segment e came
+// from rank s and go back to rows first[s*E+e]... of home[s] (device pointers valid on this GPU).
+struct HomeRoute {
+  int n_ranks;
+  const int32_t* counts;
+  const int32_t* first;
+  void* const* home;
+};
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
                 int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
-                const CombineArgs* combine = nullptr, bool* fused = nullptr);
+                const CombineArgs* combine = nullptr, bool* fused = nullptr, const HomeRoute* route = nullptr);
 
 // 128x128 block-scale recipe
 int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,

@@ -43,6 +43,13 @@ struct GemmParams {
   // accumulators into slab `split` of `partial` ([split_k][M][ldp] floats) for a later fixed-order sum
   int split_k, k_per_split, M, ldp;
   float* partial;
+  // Expert-parallel way back fused into the DOWN epilogue (n_home > 0): the rows of segment e are the
+  // rows ranks 0..n_home-1 sent, in that order; home_counts[s*E+e] of them came from rank s and return
+  // to rows home_first[s*E+e] ... of rank s's result buffer home[s] (peer stores; the own rank's are local).
+  int n_home = 0;
+  const int32_t* home_counts = nullptr;
+  const int32_t* home_first = nullptr;
+  void* home[8] = {};
 };
 
 
@@ -282,6 +289,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float sa = p.scale_a[e];
         const float inv = 1.0f / (sa * p.scale_b0[e]);
         const int n0 = n_idx * BN;
+        // where this lane's row goes: the local result buffer, or the row's place on its home rank
+        __nv_bfloat16* out_row = out + (size_t)row * p.N_out;
+        if (p.n_home > 0 && row_ok) {
+          int j = row - p.offsets[e], s = 0;
+          for (; s < p.n_home - 1; ++s) {
+            const int c = p.home_counts[s * p.E + e];
+            if (j < c) break;
+            j -= c;
+          }
+          out_row = static_cast<__nv_bfloat16*>(p.home[s]) + (size_t)(p.home_first[s * p.E + e] + j) * p.N_out;
+        }
 #pragma unroll 1
         for (int c2 = half * (BN / 128); c2 < (half + 1) * (BN / 128); ++c2) {
           uint32_t a[2][32];                           // two 32-column loads per wait
@@ -299,7 +317,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               packed[j] = *reinterpret_cast<uint32_t*>(&b2);
             }
             if (row_ok) {
-              __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
+              __nv_bfloat16* dst = out_row + n0 + c * 32;
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 if (n0 + c * 32 + v * 8 < p.N_out)
@@ -548,7 +566,7 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
 
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
                 int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
-                const CombineArgs* combine, bool* fused) {
+                const CombineArgs* combine, bool* fused, const HomeRoute* route) {
   if (fused) *fused = false;
   BWMOE_REQUIRE(hq && offsets && sh && wd && sd && y && status, BWMOE_ERR_NULL, "down: null pointer");
   if (int rc = check_common("down", hq, y, M, D, H, E)) return rc;
@@ -557,8 +575,21 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
   if (int rc = make_map_a(&ma, hq, M, H)) return rc;
   if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;
   const int k_blocks = ceil_div(H, BK), n_tiles = ceil_div(D, BN);
-  const SplitPlan sp = choose_split(M, E, k_blocks, n_tiles);
+  SplitPlan sp = choose_split(M, E, k_blocks, n_tiles);
+  if (route != nullptr) sp = SplitPlan{1, k_blocks};      // rows leave from the epilogue: no slab pass
   GemmParams p{offsets, sh, sd, nullptr, y, nullptr, status, E, H, D, n_tiles, sp.split_k, sp.k_per_split, M, D, nullptr};
+  if (route != nullptr) {
+    BWMOE_REQUIRE(route->n_ranks >= 1 && route->n_ranks <= 8 && route->counts && route->first && route->home,
+                  BWMOE_ERR_UNSUPPORTED, "down: home route with %d ranks", route->n_ranks);
+    p.n_home = route->n_ranks;
+    p.home_counts = route->counts;
+    p.home_first = route->first;
+    for (int r = 0; r < route->n_ranks; ++r) {
+      BWMOE_REQUIRE(route->home[r] != nullptr && aligned16(route->home[r]), BWMOE_ERR_BAD_ALIGN,
+                    "down: result buffer of rank %d", r);
+      p.home[r] = route->home[r];
+    }
+  }
   if (sp.split_k == 1) return launch_gemm<false, false>(ma, mb, mb, p, M, st);
   BWMOE_REQUIRE(scratch != nullptr && aligned16(scratch), BWMOE_ERR_WORKSPACE, "down: scratch buffer required");
   p.partial = static_cast<float*>(scratch);

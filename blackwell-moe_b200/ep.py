@@ -141,8 +141,28 @@ class ExpertParallelMoE:
     #: each row straight into its owner's memory and the combine kernel loads result rows from their owners'
     #: memory (symmetric memory over NVLink, three stream-ordered barriers per step, no collective on the
     #: data path).  "auto": "peer" where symmetric memory can be set up (per-tensor recipe, CUDA, <= 8 ranks).
-    transport = "nccl"
+    transport = "auto"
+    #: way back of the peer transport.  "push": the down projection's epilogue stores each finished row
+    #: into its home rank's buffer (the transfer overlaps the GEMM) and the combine is local.  "pull": the
+    #: down projection writes locally and the combine kernel loads the rows from their owners.
+    way_back = "push"
     _peer = None
+    #: when True, the peer-memory forward records a CUDA event at every phase boundary;
+    #: :meth:`phase_times` turns the last step's events into milliseconds
+    profile = False
+    _marks = ()
+
+    def _mark(self, name: str):
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.dev))
+            self._marks.append((name, ev))
+
+    def phase_times(self) -> dict:
+        """Milliseconds between the phase marks of the last profiled step (synchronises)."""
+        torch.cuda.synchronize(self.dev)
+        m = self._marks
+        return {m[i + 1][0]: m[i][1].elapsed_time(m[i + 1][1]) for i in range(len(m) - 1)}
 
     def _peer_setup(self, rows_cap: int):
         """Symmetric receive (FP8 rows) and result (bf16 rows) buffers of ``rows_cap`` rows, mapped on every rank.
@@ -194,6 +214,9 @@ class ExpertParallelMoE:
         i32, f32, u8 = torch.int32, torch.float32, torch.uint8
         new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         peer = self._peer
+        if self.profile:
+            self._marks = []
+        self._mark("start")
         status = torch.zeros(4, dtype=i32, device=dev)
         offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
         stats = new(2 * E, dtype=f32)                                   # [amax | counts]
@@ -202,6 +225,7 @@ class ExpertParallelMoE:
                                           pos.data_ptr(), row_slot.data_ptr(), row_expert.data_ptr(),
                                           stats[:E].data_ptr(), status.data_ptr(), scratch.data_ptr(), st))
         stats[E:].view(i32).copy_(offsets[1:] - offsets[:-1])
+        self._mark("plan")
         gathered = new(G * 2 * E, dtype=f32)
         dist.all_gather_into_tensor(gathered, stats, group=self.group)
         gathered = gathered.view(G, 2 * E)
@@ -221,11 +245,15 @@ class ExpertParallelMoE:
         offsets_l[1:] = torch.cumsum(seg, 0, dtype=i32)
         R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
         assert R <= peer["cap"], (R, peer["cap"])
+        self._mark("counts+maps")
 
         peer["hx"].barrier()             # every rank is done with the previous step's buffers
+        self._mark("barrier A")
         _lib.check(lib.bwmoe_scatter_quant_peers(x.data_ptr(), pos.data_ptr(), indices.data_ptr(), scale_x.data_ptr(),
                                                  delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, st))
+        self._mark("quantise+store")
         peer["hx"].barrier()             # every row of this step has landed
+        self._mark("barrier B")
         if R > 0:
             row_expert_l = torch.repeat_interleave(torch.arange(el, device=dev, dtype=i32), seg.to(torch.int64),
                                                    output_size=R)
@@ -240,13 +268,28 @@ class ExpertParallelMoE:
             _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
             _lib.check(lib.bwmoe_requant(h.data_ptr(), row_expert_l.data_ptr(), scale_h.data_ptr(), R, H,
                                          hq.data_ptr(), st))
-            _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
-                                      self.sd.data_ptr(), R, D, H, el, peer["y"].data_ptr(), status.data_ptr(),
-                                      gs.data_ptr(), st))
-        peer["hy"].barrier()             # every rank's result rows are complete
+            if self.way_back == "push":
+                home_counts = counts[:, rank * el:(rank + 1) * el].contiguous()
+                home_first = (torch.cumsum(counts, 1, dtype=i32) - counts)[:, rank * el:(rank + 1) * el].contiguous()
+                _lib.check(lib.bwmoe_down_peers(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(),
+                                                self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
+                                                home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"], G,
+                                                status.data_ptr(), st))
+            else:
+                _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
+                                          self.sd.data_ptr(), R, D, H, el, peer["y"].data_ptr(), status.data_ptr(),
+                                          gs.data_ptr(), st))
+        self._mark("gate/up+requant+down")
+        peer["hy"].barrier()             # every rank's result rows are complete (and, pushed, at home)
+        self._mark("barrier C")
         out = new(T, D, dtype=torch.bfloat16)
-        _lib.check(lib.bwmoe_combine_peers(peer["y_ptrs"], G, pos.data_ptr(), indices.data_ptr(), weights.data_ptr(),
-                                           delta.data_ptr(), el, T, D, K, out.data_ptr(), st))
+        if self.way_back == "push":
+            _lib.check(lib.bwmoe_combine(peer["y"].data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K,
+                                         out.data_ptr(), st))
+        else:
+            _lib.check(lib.bwmoe_combine_peers(peer["y_ptrs"], G, pos.data_ptr(), indices.data_ptr(),
+                                               weights.data_ptr(), delta.data_ptr(), el, T, D, K, out.data_ptr(), st))
+        self._mark("combine")
         self.last_status = status
         return self._finish(out, host_in)
 

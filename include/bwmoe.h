@@ -329,6 +329,17 @@ int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights,
  * The caller orders the steps across ranks (a barrier before the stores, one after them, one before
  * the loads).  At most 8 ranks.
  */
+/*
+ * bwmoe_down with the expert-parallel way back fused into its epilogue: segment e holds the rows that
+ * ranks 0..n_ranks-1 sent (in that order, d_home_counts[s*E+e] from rank s); each finished row is stored
+ * straight to row d_home_first[s*E+e] + i of rank s's result buffer h_y_of_rank[s], where a plain
+ * bwmoe_combine over the home rank's own permutation picks it up.  One barrier between this call and
+ * the combine.  No split-K in this form.
+ */
+int bwmoe_down_peers(const void* d_hq, const int32_t* d_offsets, const float* d_scales_h, const void* d_w_down,
+                     const float* d_scales_down, int M, int D, int H, int E, const int32_t* d_home_counts,
+                     const int32_t* d_home_first, void* const* h_y_of_rank, int n_ranks, int32_t* d_status,
+                     void* stream);
 int bwmoe_scatter_quant_peers(const void* d_x, const int32_t* d_pos, const int32_t* d_indices,
                               const float* d_scales, const int32_t* d_delta, int T, int D, int K,
                               int experts_per_rank, void* const* h_dst_of_rank, int n_ranks, void* stream);

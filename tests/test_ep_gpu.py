@@ -45,6 +45,8 @@ def _worker(rank, world, port, ret):
         # rows stored straight into the owner's memory, results loaded from it (symmetric memory)
         cases += [(s, "peer") for s in ((96, 256, 8, 2, 256, 2048), (33, 512, 16, 4, 384, 2048),
                                         (700, 256, 4, 2, 128, 2048), (301, 256, 2, 2, 128, 2048))]
+        # the same, with the result rows loaded by the combine instead of stored by the down projection
+        cases += [(s, "peer-pull") for s in ((96, 256, 8, 2, 256, 2048), (700, 256, 4, 2, 128, 2048))]
         for (T, D, E, K, H, min_tok), transport in cases:
             inp = make_inputs(world * T, D, E, K, H, seed=T + E, keep_bf16=False)
             c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
@@ -53,14 +55,15 @@ def _worker(rank, world, port, ret):
             ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c["s_gate"][sl],
                                    c["s_up"][sl], c["s_down"][sl], num_experts=E, top_k=K)
             ep.micro_batch_min_tokens = min_tok
-            ep.transport = transport
+            ep.transport = transport.split("-")[0]
+            ep.way_back = "pull" if transport.endswith("pull") else "push"
             out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
             assert int(ep.last_status[0]) == 0
             full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
             dist.all_gather_into_tensor(full, out)
             ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"],
                                      c["s_down"], top_k=K)
-            if transport == "peer":
+            if transport.startswith("peer"):
                 assert ep._peer, "the peer transport was not set up"
                 out2 = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())     # buffers are reused
                 if not torch.equal(out2, out):
