@@ -281,7 +281,8 @@ def run_ours(args):
         torch.cuda.synchronize(dev)
 
     # L2 hygiene: when one step touches less than ~4x the 126 MB L2 (decode sizes), flush between steps
-    touched = min(E, T * K) * 3.0 * D * H / world
+    # (weights of the experts a step can reach, plus the permuted activation rows it writes and re-reads)
+    touched = min(E, T * K) * 3.0 * D * H / world + 3.0 * T * K * D
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev) if touched < 4 * 126e6 else None
     for _ in range(max(3, args.warmup)):
         step()

@@ -540,6 +540,23 @@ int bwmoe_down_peers(const void* hq, const int32_t* offsets, const float* sh, co
                      nullptr, nullptr, &route);
 }
 
+int bwmoe_down_block_peers(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
+                           const float* inv_d, int M, int D, int H, int E, const int32_t* home_counts,
+                           const int32_t* home_first, void* const* y_of_rank, int n_ranks, int32_t* status,
+                           void* stream) {
+  BWMOE_REQUIRE(y_of_rank != nullptr && n_ranks >= 1 && n_ranks <= 8, BWMOE_ERR_UNSUPPORTED, "down_block_peers: %d ranks", n_ranks);
+  const HomeRoute route{n_ranks, home_counts, home_first, y_of_rank};
+  return launch_down_block(hq, h_inv, offsets, wd, inv_d, M, D, H, E, y_of_rank[0], status,
+                           static_cast<cudaStream_t>(stream), &route);
+}
+
+int bwmoe_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos, const int32_t* indices,
+                                   const int32_t* delta, int T, int D, int K, int experts_per_rank,
+                                   void* const* xq_of_rank, void* const* inv_of_rank, int n_ranks, void* stream) {
+  return launch_scatter_rows_group_peers(xq_tok, inv_tok, pos, indices, delta, T, D, K, experts_per_rank, xq_of_rank,
+                                         inv_of_rank, n_ranks, static_cast<cudaStream_t>(stream));
+}
+
 int bwmoe_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                               const int32_t* delta, int T, int D, int K, int experts_per_rank,
                               void* const* dst_of_rank, int n_ranks, void* stream) {

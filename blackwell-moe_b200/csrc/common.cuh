@@ -110,6 +110,12 @@ struct CombineArgs {
   float scale;
   const void* residual;
 };
+// One device pointer per rank of an expert-parallel group, passed to kernels by value.
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
 // Expert-parallel return route for the down projection's epilogue: counts[s*E+e] rows of segment e came
 // from rank s and go back to rows first[s*E+e]... of home[s] (device pointers valid on this GPU).
 struct HomeRoute {
@@ -131,6 +137,12 @@ int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offse
                         const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
                         int32_t* status, cudaStream_t st);
 int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
-                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st);
+                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st,
+                      const HomeRoute* route = nullptr);
+// token-order codes + group scales -> the rows' places in their owners' buffers (block recipe dispatch)
+int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos,
+                                    const int32_t* indices, const int32_t* delta, int T, int D, int K,
+                                    int experts_per_rank, void* const* xq_of_rank, void* const* inv_of_rank,
+                                    int n_ranks, cudaStream_t st);
 
 }  // namespace bwmoe

@@ -36,6 +36,11 @@ struct BlockGemmParams {
   float* out_inv;           // GATE_UP: [M, nb] inverse scales of hq
   int32_t* status;
   int E, Kdim, N_out, n_tiles, k_blocks, nb;
+  // expert-parallel way back fused into the DOWN epilogue (see HomeRoute); off when n_home == 0
+  int n_home = 0;
+  const int32_t* home_counts = nullptr;
+  const int32_t* home_first = nullptr;
+  void* home[kMaxPeers] = {};
 };
 
 struct Cursor {
@@ -322,7 +327,17 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
       } else {
         if (row_ok) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out + n0 + half * 128;
+          __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out;
+          if (p.n_home > 0) {     // the row's place on its home rank
+            int j = row - p.offsets[e], s = 0;
+            for (; s < p.n_home - 1; ++s) {
+              const int c = p.home_counts[s * p.E + e];
+              if (j < c) break;
+              j -= c;
+            }
+            out_row = static_cast<__nv_bfloat16*>(p.home[s]) + (size_t)(p.home_first[s * p.E + e] + j) * p.N_out;
+          }
+          __nv_bfloat16* dst = out_row + n0 + half * 128;
 #pragma unroll
           for (int v = 0; v < 16; ++v) {
             if (n0 + half * 128 + v * 8 < p.N_out) {
@@ -428,6 +443,32 @@ gather_quantised_rows_kernel(const uint8_t* __restrict__ xq_tok, const float* __
   if (v < groups) x_inv[(size_t)m * groups + v] = inv_tok[t * groups + v];
 }
 
+// Token-major form for expert parallelism: the codes and group scales of token t go to the place of
+// each of its K rows in the owner rank's buffers (row pos[t,k] + delta[expert]); read once, stored K
+// times, remote rows as plain peer stores.
+__global__ void __launch_bounds__(256)
+scatter_quantised_rows_peers_kernel(const uint8_t* __restrict__ xq_tok, const float* __restrict__ inv_tok,
+                                    const int32_t* __restrict__ pos, const int32_t* __restrict__ indices,
+                                    const int32_t* __restrict__ delta, unsigned T, unsigned D, int K, int groups,
+                                    int experts_per_rank, const PeerPtrs xq_dst, const PeerPtrs inv_dst) {
+  const unsigned vec_per_row = D / 16;
+  const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= T * vec_per_row) return;
+  const unsigned t = p / vec_per_row, v = p - t * vec_per_row;
+  const uint4 codes = reinterpret_cast<const uint4*>(xq_tok + (size_t)t * D)[v];
+  const float inv = v < (unsigned)groups ? inv_tok[(size_t)t * groups + v] : 0.f;
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const int row = pos[(size_t)t * K + k];
+    if (row < 0) continue;
+    const int e = indices[(size_t)t * K + k];
+    const int r = e / experts_per_rank;
+    const size_t dst_row = (size_t)(row + delta[e]);
+    reinterpret_cast<uint4*>(static_cast<uint8_t*>(xq_dst.p[r]) + dst_row * D)[v] = codes;
+    if (v < (unsigned)groups) static_cast<float*>(inv_dst.p[r])[dst_row * groups + v] = inv;
+  }
+}
+
 int check_block(const char* who, int M, int D, int H, int E) {
   BWMOE_REQUIRE(M > 0 && D > 0 && H > 0 && E > 0, BWMOE_ERR_BAD_SHAPE, "%s: M=%d D=%d H=%d E=%d", who, M, D, H, E);
   BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
@@ -486,7 +527,8 @@ int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offse
 }
 
 int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
-                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st) {
+                      const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st,
+                      const HomeRoute* route) {
   BWMOE_REQUIRE(hq && h_inv && offsets && wd && inv_d && y && status, BWMOE_ERR_NULL, "down_block: null pointer");
   if (int rc = check_block("down_block", M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(hq) && aligned16(y) && aligned16(wd), BWMOE_ERR_BAD_ALIGN,
@@ -496,7 +538,44 @@ int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets
   if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;
   BlockGemmParams p{offsets, h_inv, inv_d, nullptr, y, nullptr, status, E, H, D, ceil_div(D, BN),
                     ceil_div(H, BK), ceil_div(D, 128)};
+  if (route != nullptr) {
+    BWMOE_REQUIRE(route->n_ranks >= 1 && route->n_ranks <= kMaxPeers && route->counts && route->first && route->home,
+                  BWMOE_ERR_UNSUPPORTED, "down_block: home route with %d ranks", route->n_ranks);
+    p.n_home = route->n_ranks;
+    p.home_counts = route->counts;
+    p.home_first = route->first;
+    for (int r = 0; r < route->n_ranks; ++r) {
+      BWMOE_REQUIRE(route->home[r] != nullptr && aligned16(route->home[r]), BWMOE_ERR_BAD_ALIGN,
+                    "down_block: result buffer of rank %d", r);
+      p.home[r] = route->home[r];
+    }
+  }
   return launch_block_gemm<false>(ma, mb, mb, p, M, st);
+}
+
+int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos,
+                                    const int32_t* indices, const int32_t* delta, int T, int D, int K,
+                                    int experts_per_rank, void* const* xq_of_rank, void* const* inv_of_rank,
+                                    int n_ranks, cudaStream_t st) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_rows_group_peers: T=%d D=%d K=%d", T, D, K);
+  BWMOE_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers && experts_per_rank >= 1, BWMOE_ERR_UNSUPPORTED,
+                "scatter_rows_group_peers: %d ranks (at most %d)", n_ranks, kMaxPeers);
+  BWMOE_REQUIRE(xq_tok && inv_tok && pos && indices && delta && xq_of_rank && inv_of_rank, BWMOE_ERR_NULL,
+                "scatter_rows_group_peers: null pointer");
+  const int groups = ceil_div(D, 128);
+  BWMOE_REQUIRE(groups <= D / 16, BWMOE_ERR_BAD_SHAPE, "scatter_rows_group_peers: D=%d too narrow", D);
+  PeerPtrs px{}, pi{};
+  for (int r = 0; r < n_ranks; ++r) {
+    BWMOE_REQUIRE(xq_of_rank[r] && inv_of_rank[r] && aligned16(xq_of_rank[r]), BWMOE_ERR_BAD_ALIGN,
+                  "scatter_rows_group_peers: buffers of rank %d", r);
+    px.p[r] = xq_of_rank[r];
+    pi.p[r] = inv_of_rank[r];
+  }
+  const size_t n = (size_t)T * (D / 16);
+  scatter_quantised_rows_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint8_t*>(xq_tok), inv_tok, pos, indices, delta, T, D, K, groups, experts_per_rank, px, pi);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
 }
 
 }  // namespace bwmoe

@@ -277,10 +277,6 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restr
 // are ordinary local stores).  dst[r] is rank r's receive buffer; the row lands at
 // pos[t, k] + delta[e], which is its place in the owner's per-expert segments ordered by (source rank,
 // source row).  No multicast, no bulk copies: plain 16-byte stores.
-constexpr int kMaxPeers = 8;
-struct PeerPtrs {
-  void* p[kMaxPeers];
-};
 __global__ void __launch_bounds__(256)
 scatter_quant_peers_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos,
                            const int32_t* __restrict__ indices, const float* __restrict__ scales,

@@ -145,7 +145,12 @@ class ExpertParallelMoE:
     #: way back of the peer transport.  "push": the down projection's epilogue stores each finished row
     #: into its home rank's buffer (the transfer overlaps the GEMM) and the combine is local.  "pull": the
     #: down projection writes locally and the combine kernel loads the rows from their owners.
-    way_back = "push"
+    #: The epilogue's stores are 16 bytes per lane and cross NVLink at only ~150 GB/s, so "push" pays
+    #: when the down GEMM spends long enough on a row to hide that (wide H); "auto" pushes for H >= 8192.
+    way_back = "auto"
+
+    def _push(self) -> bool:
+        return self.way_back == "push" or (self.way_back == "auto" and self.H >= 8192)
     _peer = None
     #: when True, the peer-memory forward records a CUDA event at every phase boundary;
     #: :meth:`phase_times` turns the last step's events into milliseconds
@@ -183,6 +188,10 @@ class ExpertParallelMoE:
             peer = dict(cap=rows_cap, xq=xq, y=y, hx=hx, hy=hy,
                         xq_ptrs=(C.c_void_p * G)(*[int(p) for p in hx.buffer_ptrs]),
                         y_ptrs=(C.c_void_p * G)(*[int(p) for p in hy.buffer_ptrs]))
+            if self.block:               # per-row group scales travel with the codes
+                xinv = symm.empty(rows_cap * ((self.D + 127) // 128), dtype=torch.float32, device=self.dev)
+                hi = symm.rendezvous(xinv, group)
+                peer.update(xinv=xinv, hi=hi, xinv_ptrs=(C.c_void_p * G)(*[int(p) for p in hi.buffer_ptrs]))
         except Exception as ex:      # noqa: BLE001 - any failure means "use NCCL", agreed on below
             ok, peer = 0, repr(ex)
         flag = torch.tensor([ok], dtype=torch.int32, device=self.dev)
@@ -197,12 +206,101 @@ class ExpertParallelMoE:
         return True
 
     def _use_peers(self, T: int) -> bool:
-        if self.transport == "nccl" or self.block or self.dev.type != "cuda" or self.world > 8:
+        if self.transport == "nccl" or self.dev.type != "cuda" or self.world > 8:
             return False
         ok = self._peer_setup(self.world * T * self.K)       # worst case: every row of every rank lands here
         if not ok and self.transport == "peer":
             raise RuntimeError("transport='peer' requested but symmetric memory could not be set up")
         return ok
+
+    def _peer_maps(self, counts, offsets):
+        """From the [G, E] row counts: where my rows of expert e land on e's owner relative to my own
+        permuted order (delta[E]), my local segments, and the way home of the rows I will hold."""
+        G, rank, el, E, dev, i32 = self.world, self.rank, self.el, self.E, self.dev, torch.int32
+        total = counts.sum(0, dtype=i32).view(G, el)
+        seg_start = (torch.cumsum(total, 1, dtype=i32) - total).view(E)
+        below = counts[:rank].sum(0, dtype=i32) if rank > 0 else torch.zeros(E, dtype=i32, device=dev)
+        delta = (seg_start + below - offsets[:E]).contiguous()
+        offsets_l = torch.zeros(el + 1, dtype=i32, device=dev)
+        offsets_l[1:] = torch.cumsum(total[rank], 0, dtype=i32)
+        home_counts = counts[:, rank * el:(rank + 1) * el].contiguous()
+        home_first = (torch.cumsum(counts, 1, dtype=i32) - counts)[:, rank * el:(rank + 1) * el].contiguous()
+        return delta, offsets_l, home_counts, home_first
+
+    def _forward_block_peers(self, x, weights, indices, host_in):
+        """Block-scale recipe over peer memory: tokens are quantised once in token order, their codes and
+        group scales stored to the owners; the block GEMMs run locally and the down epilogue stores the
+        result rows at home."""
+        lib, dev, E, K, D, H, el = _lib.lib(), self.dev, self.E, self.K, self.D, self.H, self.el
+        G, rank, T = self.world, self.rank, x.shape[0]
+        M = T * K
+        st = torch.cuda.current_stream(dev).cuda_stream
+        i32, f32, u8 = torch.int32, torch.float32, torch.uint8
+        new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
+        peer = self._peer
+        if self.profile:
+            self._marks = []
+        self._mark("start")
+        status = torch.zeros(4, dtype=i32, device=dev)
+        offsets, pos, row_slot, row_expert = new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32), new(M, dtype=i32)
+        scratch = new(lib.bwmoe_plan_scratch_bytes(T, E, K), dtype=u8)
+        _lib.check(lib.bwmoe_permute_plan(indices.data_ptr(), None, T, E, K, offsets.data_ptr(), pos.data_ptr(),
+                                          row_slot.data_ptr(), row_expert.data_ptr(), None, status.data_ptr(),
+                                          scratch.data_ptr(), st))
+        nd, nh = (D + 127) // 128, (H + 127) // 128
+        xq_tok, inv_tok = new(T, D, dtype=u8), new(T, nd, dtype=f32)
+        _lib.check(lib.bwmoe_gather_quant_group(x.data_ptr(), None, T, D, 1, xq_tok.data_ptr(), inv_tok.data_ptr(), st))
+        self._mark("plan+quantise")
+        counts = new(G * E, dtype=i32)
+        dist.all_gather_into_tensor(counts, (offsets[1:] - offsets[:-1]).contiguous(), group=self.group)
+        counts = counts.view(G, E)
+        counts_host = counts.cpu()                                      # the step's one host synchronisation
+        delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
+        R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
+        assert R <= peer["cap"], (R, peer["cap"])
+        self._mark("counts+maps")
+        peer["hx"].barrier()
+        self._mark("barrier A")
+        _lib.check(lib.bwmoe_scatter_rows_group_peers(xq_tok.data_ptr(), inv_tok.data_ptr(), pos.data_ptr(),
+                                                      indices.data_ptr(), delta.data_ptr(), T, D, K, el,
+                                                      peer["xq_ptrs"], peer["xinv_ptrs"], G, st))
+        self._mark("store rows")
+        peer["hx"].barrier()
+        self._mark("barrier B")
+        if R > 0:
+            hq, h_inv = new(R, H, dtype=u8), new(R, nh, dtype=f32)
+            # The epilogue warps re-read a row's group scales for every K block and rely on L1 for it; loads
+            # from peer-mapped memory were measured not to get that (GEMM phase 5.0 ms against 1.9 ms), so
+            # the scales (64 bytes per row) are first copied into ordinary device memory.
+            xinv_l = peer["xinv"][:R * nd].clone()
+            self._mark("copy scales")
+            _lib.check(lib.bwmoe_gateup_swiglu_block(peer["xq"].data_ptr(), xinv_l.data_ptr(), offsets_l.data_ptr(),
+                                                     self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                                     self.su.data_ptr(), R, D, H, el, hq.data_ptr(), h_inv.data_ptr(),
+                                                     status.data_ptr(), st))
+            self._mark("gate/up")
+            if self._push():
+                _lib.check(lib.bwmoe_down_block_peers(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
+                                                      self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
+                                                      home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"],
+                                                      G, status.data_ptr(), st))
+            else:
+                _lib.check(lib.bwmoe_down_block(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
+                                                self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
+                                                peer["y"].data_ptr(), status.data_ptr(), st))
+        self._mark("down")
+        peer["hy"].barrier()
+        self._mark("barrier C")
+        out = new(T, D, dtype=torch.bfloat16)
+        if self._push():
+            _lib.check(lib.bwmoe_combine(peer["y"].data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K,
+                                         out.data_ptr(), st))
+        else:
+            _lib.check(lib.bwmoe_combine_peers(peer["y_ptrs"], G, pos.data_ptr(), indices.data_ptr(),
+                                               weights.data_ptr(), delta.data_ptr(), el, T, D, K, out.data_ptr(), st))
+        self._mark("combine")
+        self.last_status = status
+        return self._finish(out, host_in)
 
     def _forward_peers(self, x, weights, indices, row_amax, host_in):
         """Per-tensor recipe over peer memory: route/plan locally, exchange counts and maxima, then
@@ -235,14 +333,8 @@ class ExpertParallelMoE:
         scale_x = new(E, dtype=f32)
         _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
         sx_local = scale_x[rank * el:(rank + 1) * el].contiguous()
-        # where my rows of expert e start inside e's segment on its owner, relative to my own permuted order
-        total = counts.sum(0, dtype=i32).view(G, el)
-        seg_start = (torch.cumsum(total, 1, dtype=i32) - total).view(E)
-        below = counts[:rank].sum(0, dtype=i32) if rank > 0 else torch.zeros(E, dtype=i32, device=dev)
-        delta = (seg_start + below - offsets[:E]).contiguous()
-        seg = total[rank]
-        offsets_l = torch.zeros(el + 1, dtype=i32, device=dev)
-        offsets_l[1:] = torch.cumsum(seg, 0, dtype=i32)
+        delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
+        seg = offsets_l[1:] - offsets_l[:-1]
         R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
         assert R <= peer["cap"], (R, peer["cap"])
         self._mark("counts+maps")
@@ -268,9 +360,7 @@ class ExpertParallelMoE:
             _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
             _lib.check(lib.bwmoe_requant(h.data_ptr(), row_expert_l.data_ptr(), scale_h.data_ptr(), R, H,
                                          hq.data_ptr(), st))
-            if self.way_back == "push":
-                home_counts = counts[:, rank * el:(rank + 1) * el].contiguous()
-                home_first = (torch.cumsum(counts, 1, dtype=i32) - counts)[:, rank * el:(rank + 1) * el].contiguous()
+            if self._push():
                 _lib.check(lib.bwmoe_down_peers(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(),
                                                 self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
                                                 home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"], G,
@@ -283,7 +373,7 @@ class ExpertParallelMoE:
         peer["hy"].barrier()             # every rank's result rows are complete (and, pushed, at home)
         self._mark("barrier C")
         out = new(T, D, dtype=torch.bfloat16)
-        if self.way_back == "push":
+        if self._push():
             _lib.check(lib.bwmoe_combine(peer["y"].data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K,
                                          out.data_ptr(), st))
         else:
@@ -307,12 +397,15 @@ class ExpertParallelMoE:
         rs = new(need, dtype=u8) if need else None
         _lib.check(lib.bwmoe_router(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, weights.data_ptr(),
                                     indices.data_ptr(), row_amax.data_ptr(), rs.data_ptr() if need else None, need, st))
+        peers = self._use_peers(T)
         if self.block:
+            if peers:
+                return self._forward_block_peers(x, weights, indices, host_in)
             M = T * K
             offsets, pos, row_slot, row_expert = (new(E + 1, dtype=i32), new(M, dtype=i32), new(M, dtype=i32),
                                                   new(M, dtype=i32))
             return self._forward_block(x, weights, indices, offsets, pos, row_slot, row_expert, host_in)
-        if self._use_peers(T):
+        if peers:
             return self._forward_peers(x, weights, indices, row_amax, host_in)
 
         # ---- plan every micro-batch, exchange counts and activation maxima once ----

@@ -340,6 +340,20 @@ int bwmoe_down_peers(const void* d_hq, const int32_t* d_offsets, const float* d_
                      const float* d_scales_down, int M, int D, int H, int E, const int32_t* d_home_counts,
                      const int32_t* d_home_first, void* const* h_y_of_rank, int n_ranks, int32_t* d_status,
                      void* stream);
+/* The same for the block-scale recipe: the epilogue of bwmoe_down_block stores the rows at home. */
+int bwmoe_down_block_peers(const void* d_hq, const float* d_h_inv, const int32_t* d_offsets, const void* d_w_down,
+                           const float* d_inv_down, int M, int D, int H, int E, const int32_t* d_home_counts,
+                           const int32_t* d_home_first, void* const* h_y_of_rank, int n_ranks, int32_t* d_status,
+                           void* stream);
+/*
+ * Block-scale dispatch over peer memory: the codes d_xq_tok[T,D] and group scales d_inv_tok[T,ceil(D/128)]
+ * of the tokens (token order, from bwmoe_gather_quant_group with no slot map) are stored to the place of
+ * each of their K rows (d_pos[t*K+k] + d_delta[expert]) in the owner rank's code and scale buffers.
+ */
+int bwmoe_scatter_rows_group_peers(const void* d_xq_tok, const float* d_inv_tok, const int32_t* d_pos,
+                                   const int32_t* d_indices, const int32_t* d_delta, int T, int D, int K,
+                                   int experts_per_rank, void* const* h_xq_of_rank, void* const* h_inv_of_rank,
+                                   int n_ranks, void* stream);
 int bwmoe_scatter_quant_peers(const void* d_x, const int32_t* d_pos, const int32_t* d_indices,
                               const float* d_scales, const int32_t* d_delta, int T, int D, int K,
                               int experts_per_rank, void* const* h_dst_of_rank, int n_ranks, void* stream);

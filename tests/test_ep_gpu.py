@@ -56,7 +56,7 @@ def _worker(rank, world, port, ret):
                                    c["s_up"][sl], c["s_down"][sl], num_experts=E, top_k=K)
             ep.micro_batch_min_tokens = min_tok
             ep.transport = transport.split("-")[0]
-            ep.way_back = "pull" if transport.endswith("pull") else "push"
+            ep.way_back = "pull" if transport.endswith("pull") else "push"       # ("auto" picks by H)
             out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
             assert int(ep.last_status[0]) == 0
             full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
@@ -73,6 +73,29 @@ def _worker(rank, world, port, ret):
             host = ep.forward(inp["x"][rank * T:(rank + 1) * T].contiguous().pin_memory())
             if not torch.equal(host, out.cpu()):
                 msgs.append(f"shape {(T, D, E, K, H)}: host-buffer path differs")
+        # block-scale recipe (per-token group scales travel with the codes), both transports
+        from test_block_gpu import make_block_inputs
+        for (T, D, E, K, H), transport in [((64, 256, 8, 2, 256), "nccl"), ((64, 256, 8, 2, 256), "peer"),
+                                           ((150, 512, 16, 4, 384), "peer"), ((150, 512, 16, 4, 384), "peer-pull")]:
+            inp = make_block_inputs(world * T, D, E, K, H, seed=T + H)
+            c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
+            el = E // world
+            sl = slice(rank * el, (rank + 1) * el)
+            ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c["inv_gate"][sl],
+                                   c["inv_up"][sl], c["inv_down"][sl], num_experts=E, top_k=K)
+            ep.transport = transport.split("-")[0]
+            ep.way_back = "pull" if transport.endswith("pull") else "push"
+            out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())
+            out = ep.forward(c["x"][rank * T:(rank + 1) * T].contiguous())        # second step: buffers reused
+            assert int(ep.last_status[0]) == 0
+            assert transport == "nccl" or ep._peer, "the peer transport was not set up"
+            full = torch.empty(world * T, D, dtype=out.dtype, device=dev)
+            dist.all_gather_into_tensor(full, out)
+            ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["inv_gate"],
+                                     c["inv_up"], c["inv_down"], top_k=K)
+            if not torch.equal(full, ref):
+                msgs.append(f"block shape {(T, D, E, K, H)} {transport}: max diff "
+                            f"{(full.float() - ref.float()).abs().max().item()}")
         ret[rank] = "ok" if not msgs else "; ".join(msgs)
     except Exception as e:  # noqa: BLE001
         import traceback
