@@ -557,6 +557,12 @@ int bwmoe_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, con
                                          inv_of_rank, n_ranks, static_cast<cudaStream_t>(stream));
 }
 
+int bwmoe_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, int E, int rank, int32_t* delta,
+                  int32_t* offsets_local, int32_t* home_counts, int32_t* home_first, void* stream) {
+  return launch_ep_maps(counts, offsets, n_ranks, E, rank, delta, offsets_local, home_counts, home_first,
+                        static_cast<cudaStream_t>(stream));
+}
+
 int bwmoe_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                               const int32_t* delta, int T, int D, int K, int experts_per_rank,
                               void* const* dst_of_rank, int n_ranks, void* stream) {

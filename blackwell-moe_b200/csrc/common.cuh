@@ -81,6 +81,8 @@ int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, 
                           cudaStream_t st);
 int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indices, const float* scales, int T,
                          int D, int K, void* xq, cudaStream_t st);
+int launch_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, int E, int rank, int32_t* delta,
+                   int32_t* offsets_local, int32_t* home_counts, int32_t* home_first, cudaStream_t st);
 int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                                const int32_t* delta, int T, int D, int K, int experts_per_rank, void* const* dst,
                                int n_ranks, cudaStream_t st);

@@ -300,30 +300,57 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
           out_row = static_cast<__nv_bfloat16*>(p.home[s]) + (size_t)(p.home_first[s * p.E + e] + j) * p.N_out;
         }
+        // Stores are issued transposed: the eight lanes of a group exchange their 16-byte pieces so that one
+        // instruction writes 128 contiguous bytes of each of four rows (a lane per row would emit 16-byte
+        // writes; over NVLink those reach only ~140 GB/s).  Lane l of a group ends up with piece (l & 7)
+        // of the group's eight rows, and needs those rows' destinations.
+        const unsigned ok_rows = __ballot_sync(0xffffffffu, row_ok);
+        const int g0 = lane & ~7, piece = lane & 7;
+        unsigned long long row_ptr[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          row_ptr[k] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(out_row), g0 + k);
 #pragma unroll 1
         for (int c2 = half * (BN / 128); c2 < (half + 1) * (BN / 128); ++c2) {
           uint32_t a[2][32];                           // two 32-column loads per wait
           tmem_ld32(t_row + c2 * 64, a[0]);
           tmem_ld32(t_row + c2 * 64 + 32, a[1]);
           tmem_ld_wait();
+          uint4 v[8];                                  // this lane's row: 64 columns as eight 16-byte pieces
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int c = 2 * c2 + q;
-            uint32_t packed[16];
+          for (int pc = 0; pc < 8; ++pc) {
+            uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[q][2 * j]) * inv,
-                                                        __uint_as_float(a[q][2 * j + 1]) * inv);
-              packed[j] = *reinterpret_cast<uint32_t*>(&b2);
+            for (int j = 0; j < 4; ++j) {
+              const int i = (pc & 3) * 8 + 2 * j;
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[pc >> 2][i]) * inv,
+                                                        __uint_as_float(a[pc >> 2][i + 1]) * inv);
+              w[j] = *reinterpret_cast<uint32_t*>(&b2);
             }
-            if (row_ok) {
-              __nv_bfloat16* dst = out_row + n0 + c * 32;
+            v[pc] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          // 8 x 8 transpose across the group's lanes (butterfly over lane bits 4, 2, 1)
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                if (n0 + c * 32 + v * 8 < p.N_out)
-                  reinterpret_cast<uint4*>(dst)[v] =
-                      make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-              }
+          for (int sft = 4; sft >= 1; sft >>= 1) {
+            const bool upper = (lane & sft) != 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if (k & sft) continue;
+              const uint4 send = upper ? v[k] : v[k | sft];
+              uint4 recv;
+              recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+              recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+              recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+              recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+              if (upper) v[k] = recv; else v[k | sft] = recv;
+            }
+          }
+          const int col = n0 + c2 * 64 + piece * 8;
+          if (col < p.N_out) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if ((ok_rows >> (g0 + k)) & 1u)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
             }
           }
         }

@@ -272,6 +272,47 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restr
   }
 }
 
+// Index maps of one expert-parallel step, from the gathered [G, E] row counts (one block):
+//   delta[e]       where this rank's rows of expert e land inside e's segment on its owner, minus where
+//                  they start in this rank's own permuted order (offsets[e])
+//   offsets_l      the local experts' segments (exclusive scan of their total rows)
+//   home_counts / home_first [G, el]   rows of local expert j that came from rank s, and the row of
+//                  rank s's own permuted order they return to
+__global__ void __launch_bounds__(256)
+ep_maps_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets, int G, int E, int rank,
+               int32_t* __restrict__ delta, int32_t* __restrict__ offsets_l, int32_t* __restrict__ home_counts,
+               int32_t* __restrict__ home_first) {
+  __shared__ int total[256], below[256], seg_start[256];
+  const int el = E / G;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (int s = 0; s < G; ++s) {
+      const int c = counts[s * E + e];
+      t += c;
+      if (s < rank) b += c;
+    }
+    total[e] = t, below[e] = b;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {      // exclusive scan inside the owner's expert range
+    const int first = (e / el) * el;
+    int acc = 0;
+    for (int j = first; j < e; ++j) acc += total[j];
+    seg_start[e] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = seg_start[e] + below[e] - offsets[e];
+  for (int j = threadIdx.x; j <= el; j += blockDim.x)
+    offsets_l[j] = j < el ? seg_start[rank * el + j] : seg_start[rank * el + el - 1] + total[rank * el + el - 1];
+  for (int i = threadIdx.x; i < G * el; i += blockDim.x) {
+    const int s = i / el, e = rank * el + i % el;
+    int first = 0;
+    for (int j = 0; j < e; ++j) first += counts[s * E + j];
+    home_counts[i] = counts[s * E + e];
+    home_first[i] = first;
+  }
+}
+
 // Expert-parallel dispatch fused into the quantisation: the row of slot (t, k), bound for expert e, is
 // written straight into the memory of the rank that owns e (peer stores over NVLink; the owner's own rows
 // are ordinary local stores).  dst[r] is rank r's receive buffer; the row lands at
@@ -595,6 +636,17 @@ int launch_combine_peers(void* const* src, int n_ranks, const int32_t* pos, cons
   const size_t n = (size_t)T * (D / 8);
   combine_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(pp, pos, indices, weights, delta, experts_per_rank,
                                                                     T, D, K, static_cast<__nv_bfloat16*>(out));
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, int E, int rank, int32_t* delta,
+                   int32_t* offsets_local, int32_t* home_counts, int32_t* home_first, cudaStream_t st) {
+  BWMOE_REQUIRE(n_ranks >= 1 && E >= 1 && E <= 256 && E % n_ranks == 0 && rank >= 0 && rank < n_ranks,
+                BWMOE_ERR_BAD_SHAPE, "ep_maps: ranks=%d E=%d rank=%d", n_ranks, E, rank);
+  BWMOE_REQUIRE(counts && offsets && delta && offsets_local && home_counts && home_first, BWMOE_ERR_NULL,
+                "ep_maps: null pointer");
+  ep_maps_kernel<<<1, 256, 0, st>>>(counts, offsets, n_ranks, E, rank, delta, offsets_local, home_counts, home_first);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

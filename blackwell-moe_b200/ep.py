@@ -217,14 +217,22 @@ class ExpertParallelMoE:
         """From the [G, E] row counts: where my rows of expert e land on e's owner relative to my own
         permuted order (delta[E]), my local segments, and the way home of the rows I will hold."""
         G, rank, el, E, dev, i32 = self.world, self.rank, self.el, self.E, self.dev, torch.int32
-        total = counts.sum(0, dtype=i32).view(G, el)
-        seg_start = (torch.cumsum(total, 1, dtype=i32) - total).view(E)
-        below = counts[:rank].sum(0, dtype=i32) if rank > 0 else torch.zeros(E, dtype=i32, device=dev)
-        delta = (seg_start + below - offsets[:E]).contiguous()
-        offsets_l = torch.zeros(el + 1, dtype=i32, device=dev)
-        offsets_l[1:] = torch.cumsum(total[rank], 0, dtype=i32)
-        home_counts = counts[:, rank * el:(rank + 1) * el].contiguous()
-        home_first = (torch.cumsum(counts, 1, dtype=i32) - counts)[:, rank * el:(rank + 1) * el].contiguous()
+        if dev.type != "cuda":           # the same arithmetic in torch (CPU tests of the protocol)
+            total = counts.sum(0, dtype=i32).view(G, el)
+            seg_start = (torch.cumsum(total, 1, dtype=i32) - total).view(E)
+            below = counts[:rank].sum(0, dtype=i32) if rank > 0 else torch.zeros(E, dtype=i32, device=dev)
+            delta = (seg_start + below - offsets[:E]).contiguous()
+            offsets_l = torch.zeros(el + 1, dtype=i32, device=dev)
+            offsets_l[1:] = torch.cumsum(total[rank], 0, dtype=i32)
+            home_counts = counts[:, rank * el:(rank + 1) * el].contiguous()
+            home_first = (torch.cumsum(counts, 1, dtype=i32) - counts)[:, rank * el:(rank + 1) * el].contiguous()
+            return delta, offsets_l, home_counts, home_first
+        buf = torch.empty(E + el + 1 + 2 * G * el, dtype=i32, device=dev)
+        delta, offsets_l = buf[:E], buf[E:E + el + 1]
+        home_counts, home_first = buf[E + el + 1:E + el + 1 + G * el], buf[E + el + 1 + G * el:]
+        _lib.check(_lib.lib().bwmoe_ep_maps(counts.data_ptr(), offsets.data_ptr(), G, E, rank, delta.data_ptr(),
+                                            offsets_l.data_ptr(), home_counts.data_ptr(), home_first.data_ptr(),
+                                            torch.cuda.current_stream(dev).cuda_stream))
         return delta, offsets_l, home_counts, home_first
 
     def _forward_block_peers(self, x, weights, indices, host_in):

@@ -318,7 +318,7 @@ int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights,
 /*
  * Expert-parallel transport over peer memory (one process per GPU, the buffers of every rank mapped
  * into each process; the host pointer arrays hold one device pointer per rank).  No counterpart in
- * the reference, which is single-GPU (docs/DESIGN.md:24 names expert parallelism as future work).
+ * the reference, which is single-GPU (its docs/DESIGN.md:24 names expert parallelism as future work).
  *
  * bwmoe_scatter_quant_peers: quantise the token rows (as bwmoe_gather_quant does) and store the row of
  *   slot (t,k), routed to expert e, into row d_pos[t*K+k] + d_delta[e] of the receive buffer of rank
@@ -329,6 +329,15 @@ int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights,
  * The caller orders the steps across ranks (a barrier before the stores, one after them, one before
  * the loads).  At most 8 ranks.
  */
+/*
+ * Index maps of one expert-parallel step from the all-gathered row counts d_counts[n_ranks, E]
+ * (d_counts[s*E+e] = rows rank s has for expert e) and the caller's own d_offsets[E+1]:
+ * d_delta[E] (see bwmoe_scatter_quant_peers), d_offsets_local[E/n_ranks + 1] (segments of the experts
+ * this rank owns), d_home_counts / d_home_first [n_ranks, E/n_ranks] (see bwmoe_down_peers).
+ */
+int bwmoe_ep_maps(const int32_t* d_counts, const int32_t* d_offsets, int n_ranks, int E, int rank,
+                  int32_t* d_delta, int32_t* d_offsets_local, int32_t* d_home_counts, int32_t* d_home_first,
+                  void* stream);
 /*
  * bwmoe_down with the expert-parallel way back fused into its epilogue: segment e holds the rows that
  * ranks 0..n_ranks-1 sent (in that order, d_home_counts[s*E+e] from rank s); each finished row is stored

@@ -20,7 +20,9 @@ import numpy as np
 import torch
 
 sys.dont_write_bytecode = True
-REF = os.environ.get("REFERENCE_SRC", "/root/reference/src")
+REF = os.environ.get("REFERENCE_SRC")          # the `src` directory of a blackwell-moe checkout
+if not REF:
+    sys.exit("set REFERENCE_SRC to the src/ directory of the reference checkout")
 sys.path.insert(0, REF)
 OUT = Path(__file__).resolve().parent
 

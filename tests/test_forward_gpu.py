@@ -128,7 +128,7 @@ def test_out_of_range_expert_ids_are_reported_not_trapped():
 
 
 def test_full_size_mixtral_block_via_duplicated_tokens():
-    """BASELINE-size check (T=16384, D=4096, H=14336, E=8, top-2) that needs the oracle
+    """Full-size check of the headline workload (T=16384, D=4096, H=14336, E=8, top-2) that needs the oracle
     on 64 rows only: the 16384 tokens are 256 copies of 64 distinct rows.  Copies do
     not change any segment's amax, so every copy must reproduce, bit for bit, the row
     it duplicates, and the distinct rows must match the oracle run on the 64 rows."""
