@@ -326,29 +326,60 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (half == 0) p.out_inv[(size_t)row * p.nb + n_idx] = __fdiv_rn(amax, kFp8Max);
         }
       } else {
-        if (row_ok) {
-          __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out;
-          if (p.n_home > 0) {     // the row's place on its home rank
-            int j = row - p.offsets[e], s = 0;
-            for (; s < p.n_home - 1; ++s) {
-              const int c = p.home_counts[s * p.E + e];
-              if (j < c) break;
-              j -= c;
-            }
-            out_row = static_cast<__nv_bfloat16*>(p.home[s]) + (size_t)(p.home_first[s * p.E + e] + j) * p.N_out;
+        // where this lane's row goes: the local result buffer, or the row's place on its home rank
+        __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out;
+        if (p.n_home > 0 && row_ok) {
+          int j = row - p.offsets[e], s = 0;
+          for (; s < p.n_home - 1; ++s) {
+            const int c = p.home_counts[s * p.E + e];
+            if (j < c) break;
+            j -= c;
           }
-          __nv_bfloat16* dst = out_row + n0 + half * 128;
+          out_row = static_cast<__nv_bfloat16*>(p.home[s]) + (size_t)(p.home_first[s * p.E + e] + j) * p.N_out;
+        }
+        // transposed stores: the eight lanes of a group exchange 16-byte pieces so that one instruction
+        // writes 128 contiguous bytes of each of four rows (16-byte writes cross NVLink at ~140 GB/s only)
+        const unsigned ok_rows = __ballot_sync(0xffffffffu, row_ok);
+        const int g0 = lane & ~7, piece = lane & 7;
+        unsigned long long row_ptr[8];
 #pragma unroll
-          for (int v = 0; v < 16; ++v) {
-            if (n0 + half * 128 + v * 8 < p.N_out) {
-              const float* src = v < 8 ? accA + v * 8 : accB + (v - 8) * 8;
-              uint32_t w[4];
+        for (int k = 0; k < 8; ++k)
+          row_ptr[k] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(out_row), g0 + k);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(src[2 * q], src[2 * q + 1]);
-                w[q] = *reinterpret_cast<uint32_t*>(&b2);
-              }
-              reinterpret_cast<uint4*>(dst)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int part = 0; part < 2; ++part) {          // accA then accB: 64 columns each
+          const float* src = part == 0 ? accA : accB;
+          uint4 v[8];
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(src[pc * 8 + 2 * q], src[pc * 8 + 2 * q + 1]);
+              w[q] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            v[pc] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+#pragma unroll
+          for (int sft = 4; sft >= 1; sft >>= 1) {
+            const bool upper = (lane & sft) != 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if (k & sft) continue;
+              const uint4 send = upper ? v[k] : v[k | sft];
+              uint4 recv;
+              recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+              recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+              recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+              recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+              if (upper) v[k] = recv; else v[k | sft] = recv;
+            }
+          }
+          const int col = n0 + half * 128 + part * 64 + piece * 8;
+          if (col < p.N_out) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if ((ok_rows >> (g0 + k)) & 1u)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
             }
           }
         }

@@ -145,12 +145,13 @@ class ExpertParallelMoE:
     #: way back of the peer transport.  "push": the down projection's epilogue stores each finished row
     #: into its home rank's buffer (the transfer overlaps the GEMM) and the combine is local.  "pull": the
     #: down projection writes locally and the combine kernel loads the rows from their owners.
-    #: The epilogue's stores are 16 bytes per lane and cross NVLink at only ~150 GB/s, so "push" pays
-    #: when the down GEMM spends long enough on a row to hide that (wide H); "auto" pushes for H >= 8192.
-    way_back = "auto"
+    #: The epilogue transposes its stores so that each one writes 128 contiguous bytes of a row (with one
+    #: 16-byte store per lane the rows crossed NVLink at ~140 GB/s and the GEMM waited for them).
+    way_back = "push"
 
     def _push(self) -> bool:
-        return self.way_back == "push" or (self.way_back == "auto" and self.H >= 8192)
+        return self.way_back != "pull"
+
     _peer = None
     #: when True, the peer-memory forward records a CUDA event at every phase boundary;
     #: :meth:`phase_times` turns the last step's events into milliseconds
