@@ -340,11 +340,9 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // transposed stores: the eight lanes of a group exchange 16-byte pieces so that one instruction
         // writes 128 contiguous bytes of each of four rows (16-byte writes cross NVLink at ~140 GB/s only)
         const unsigned ok_rows = __ballot_sync(0xffffffffu, row_ok);
-        const int g0 = lane & ~7, piece = lane & 7;
+        const int piece = lane & 7;
         unsigned long long row_ptr[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          row_ptr[k] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(out_row), g0 + k);
+        group8_row_pointers(out_row, lane, row_ptr);
 #pragma unroll
         for (int part = 0; part < 2; ++part) {          // accA then accB: 64 columns each
           const float* src = part == 0 ? accA : accB;
@@ -359,29 +357,9 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
             v[pc] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-#pragma unroll
-          for (int sft = 4; sft >= 1; sft >>= 1) {
-            const bool upper = (lane & sft) != 0;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              if (k & sft) continue;
-              const uint4 send = upper ? v[k] : v[k | sft];
-              uint4 recv;
-              recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
-              recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
-              recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
-              recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
-              if (upper) v[k] = recv; else v[k | sft] = recv;
-            }
-          }
+          group8_transpose(v, lane);
           const int col = n0 + half * 128 + part * 64 + piece * 8;
-          if (col < p.N_out) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              if ((ok_rows >> (g0 + k)) & 1u)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
-            }
-          }
+          if (col < p.N_out) group8_store(v, row_ptr, ok_rows, lane, col);
         }
       }
     }

@@ -248,37 +248,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float inv_u = 1.0f / (sa * p.scale_b1[e]);
         const int n0 = n_idx * BN_HALF;
         float amax = 0.f;
-#pragma unroll 1
-        for (int c = half * (BN_HALF / 64); c < (half + 1) * (BN_HALF / 64); ++c) {
+        const unsigned ok_rows = __ballot_sync(0xffffffffu, row_ok);
+        unsigned long long row_ptr[8];
+        group8_row_pointers(out + (size_t)row * p.N_out, lane, row_ptr);
+        uint4 v[8];                                    // this warp's 64 columns of h as eight 16-byte pieces
+#pragma unroll
+        for (int cc = 0; cc < BN_HALF / 64; ++cc) {
+          const int c = half * (BN_HALF / 64) + cc;
           uint32_t g[32], u[32];
           tmem_ld32(t_row + c * 32, g);
           tmem_ld32(t_row + BN_HALF + c * 32, u);
           tmem_ld_wait();
-          uint32_t packed[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float hv[2];
+          for (int pc = 0; pc < 4; ++pc) {
+            uint32_t w[4];
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              // the reference's bf16 rounding points: gate, up, silu(gate), product
-              const float gate = bf16_round(__uint_as_float(g[2 * j + q]) * inv_g);
-              const float up = bf16_round(__uint_as_float(u[2 * j + q]) * inv_u);
-              const float act = bf16_round(silu_f(gate));
-              hv[q] = bf16_round(act * up);
-              amax = fmaxf(amax, fabsf(hv[q]));
+            for (int j = 0; j < 4; ++j) {
+              float hv[2];
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                // the reference's bf16 rounding points: gate, up, silu(gate), product
+                const float gate = bf16_round(__uint_as_float(g[pc * 8 + 2 * j + q]) * inv_g);
+                const float up = bf16_round(__uint_as_float(u[pc * 8 + 2 * j + q]) * inv_u);
+                const float act = bf16_round(silu_f(gate));
+                hv[q] = bf16_round(act * up);
+                amax = fmaxf(amax, fabsf(hv[q]));
+              }
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[0], hv[1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&b2);
             }
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[0], hv[1]);
-            packed[j] = *reinterpret_cast<uint32_t*>(&b2);
+            v[cc * 4 + pc] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if (row_ok) {
-            __nv_bfloat16* dst = out + (size_t)row * p.N_out + n0 + c * 32;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (n0 + c * 32 + v * 8 < p.N_out)
-                reinterpret_cast<uint4*>(dst)[v] =
-                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-            }
-          }
+        }
+        static_assert(BN_HALF / 64 == 2, "two 32-column chunks per epilogue warp make the eight pieces");
+        group8_transpose(v, lane);
+        {
+          const int col = n0 + half * 64 + (lane & 7) * 8;
+          if (col < p.N_out) group8_store(v, row_ptr, ok_rows, lane, col);
         }
         // rows past the segment and columns past H hold other data / zero fill: exclude them
         // (zero-filled columns give h = 0, which cannot raise the maximum)
@@ -305,11 +311,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // writes; over NVLink those reach only ~140 GB/s).  Lane l of a group ends up with piece (l & 7)
         // of the group's eight rows, and needs those rows' destinations.
         const unsigned ok_rows = __ballot_sync(0xffffffffu, row_ok);
-        const int g0 = lane & ~7, piece = lane & 7;
+        const int piece = lane & 7;
         unsigned long long row_ptr[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          row_ptr[k] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(out_row), g0 + k);
+        group8_row_pointers(out_row, lane, row_ptr);
 #pragma unroll 1
         for (int c2 = half * (BN / 128); c2 < (half + 1) * (BN / 128); ++c2) {
           uint32_t a[2][32];                           // two 32-column loads per wait
@@ -329,30 +333,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             v[pc] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          // 8 x 8 transpose across the group's lanes (butterfly over lane bits 4, 2, 1)
-#pragma unroll
-          for (int sft = 4; sft >= 1; sft >>= 1) {
-            const bool upper = (lane & sft) != 0;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              if (k & sft) continue;
-              const uint4 send = upper ? v[k] : v[k | sft];
-              uint4 recv;
-              recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
-              recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
-              recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
-              recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
-              if (upper) v[k] = recv; else v[k | sft] = recv;
-            }
-          }
+          group8_transpose(v, lane);
           const int col = n0 + c2 * 64 + piece * 8;
-          if (col < p.N_out) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              if ((ok_rows >> (g0 + k)) & 1u)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
-            }
-          }
+          if (col < p.N_out) group8_store(v, row_ptr, ok_rows, lane, col);
         }
       }
       // hand the accumulator buffer back to the MMA warp

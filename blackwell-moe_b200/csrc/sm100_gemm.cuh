@@ -171,6 +171,45 @@ __device__ __forceinline__ uint64_t desc_nmajor(uint32_t saddr) {
 
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
+// Eight 16-byte pieces per lane, transposed across the eight lanes of a group (butterfly over lane bits
+// 4, 2, 1): afterwards v[k] of lane l is what lane (l & ~7) + k held in v[l & 7].  Epilogues use it so
+// that one store instruction writes 128 contiguous bytes of a row (eight lanes x 16 bytes) instead of 16
+// bytes of 32 different rows.
+__device__ __forceinline__ void group8_transpose(uint4 (&v)[8], int lane) {
+#pragma unroll
+  for (int sft = 4; sft >= 1; sft >>= 1) {
+    const bool upper = (lane & sft) != 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k & sft) continue;
+      const uint4 send = upper ? v[k] : v[k | sft];
+      uint4 recv;
+      recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+      recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+      recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+      recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+      if (upper) v[k] = recv; else v[k | sft] = recv;
+    }
+  }
+}
+// v[k] -> 16 bytes at element column `col` of the row whose pointer lane (l & ~7) + k holds; rows whose
+// bit in ok_rows is clear are skipped.
+__device__ __forceinline__ void group8_store(const uint4 (&v)[8], const unsigned long long (&row_ptr)[8],
+                                             unsigned ok_rows, int lane, int col) {
+  const int g0 = lane & ~7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if ((ok_rows >> (g0 + k)) & 1u)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
+  }
+}
+__device__ __forceinline__ void group8_row_pointers(const void* my_row, int lane, unsigned long long (&row_ptr)[8]) {
+  const int g0 = lane & ~7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    row_ptr[k] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(my_row), g0 + k);
+}
+
 // ---------------------------------------------------------------- host side
 inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
