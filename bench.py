@@ -75,6 +75,8 @@ def parse():
     ap.add_argument("--workload", default="mixtral-8x7b", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's prefill size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="one GPU: also time the forward captured once in a CUDA graph and replayed")
     ap.add_argument("--ep-transport", default=None, choices=["auto", "nccl", "peer"],
                     help="expert-parallel exchange (N > 1): NCCL all-to-all or stores/loads over peer memory")
     return ap.parse_args()
@@ -389,6 +391,36 @@ def run_ours(args):
                     "kernel_ms": k_secs * 1e3, "flops_per_launch": flops,
                     "peak_basis": ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it has no FP8 entry)"
                                    if bf16_sus else "2 x 1400 TFLOP/s fallback (sustained bf16 of the profiling recipe)")}
+        # decode sizes stream weights: the same launch against the HBM roofline (gate+up weights of the experts
+        # that were selected; the loop above re-reads them from L2 when they fit, so these launches are flushed)
+        if M <= 128 * E:      # at most 128 rows per expert on average: the weights, not the math, set the time
+            off = bw.moe_stage_views(dev, T, D, H, E, K, block=block)["offsets"].cpu()
+            used = int(((off[1:] - off[:-1]) > 0).sum())
+            kflush = flush if flush is not None else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+            k_secs = time_region(gateup, args.steps, stream, kflush) / args.steps
+            hbm = peaks.get("hbm_gbs")
+            wbytes = used * 2.0 * D * H
+            roofline = {"bound": "hbm", "achieved": wbytes / k_secs / 1e9, "peak": hbm or 6650.0, "unit": "GB/s",
+                        "frac": wbytes / k_secs / 1e9 / (hbm or 6650.0), "traffic": None, "kernel": kernel_name,
+                        "kernel_ms": k_secs * 1e3, "bytes_per_launch": wbytes,
+                        "peak_basis": ("hbm_gbs of MEASURED_PEAKS.json" if hbm else "6.65 TB/s fallback of the profiling recipe")}
+
+    graph_ms = None
+    if world == 1 and args.graph:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()
+        stream.wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize(dev)
+        gflush = flush if flush is not None else None
+        graph_ms = time_region(g.replay, args.steps, stream, gflush) / args.steps * 1e3
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -415,6 +447,8 @@ def run_ours(args):
                          + (1 if world > 1 and not block else 0)) * args.steps,
         "clocks": clocks.summary(),
     }
+    if graph_ms is not None:
+        line["graph_ms_per_step"] = graph_ms
     if roofline is not None:
         line["roofline"] = roofline
     if cpu is not None:
