@@ -41,6 +41,10 @@ SIGNATURES = {
     "bwmoe_moe_forward_ex": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [C.c_float, _vp, _vp, _vp, _sz, _vp]),
     "bwmoe_dense_mlp": (_i, [_vp] * 4 + [_fp] * 3 + [_i] * 3 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed": (_i, [_vp, _fp, _ip] + [_vp] * 3 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
+    "bwmoe_moe_forward_routed_remap": (_i, [_vp, _fp, _ip, _ip, _i] + [_vp] * 3 + [_fp] * 3 + [_i] * 5
+                                       + [_vp, _vp, _sz, _vp]),
+    "bwmoe_moe_forward_block_routed": (_i, [_vp, _fp, _ip, _ip, _i] + [_vp] * 3 + [_fp] * 3 + [_i] * 5
+                                       + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_host": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_workspace_bytes_block": (_sz, [_i] * 5),
     "bwmoe_workspace_view_block": (_i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_sz)]),

@@ -22,7 +22,9 @@ int set_error(int code, const char* fmt, ...) {
 }
 
 namespace {
-int g_sm_reserve = 0;   // SMs the persistent GEMM grids leave free (for collectives running beside them)
+// SMs the persistent GEMM grids leave free (for collectives running beside them).  Per calling thread:
+// the launches of one forward are issued by one thread, so two threads never see each other's setting.
+thread_local int g_sm_reserve = 0;
 }
 int gemm_sm_budget() { return std::max(1, sm_count() - g_sm_reserve); }
 
@@ -191,6 +193,58 @@ __global__ void row_amax_kernel(const __nv_bfloat16* __restrict__ x, int T, int 
   for (int d = lane; d < D; d += 32) m = fmaxf(m, fabsf(__bfloat162float(x[(size_t)t * D + d])));
   for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
   if (lane == 0) row_amax[t] = m;
+}
+
+// Expert ids of the whole model -> slots of a resident expert pool.  An id outside [0, n_ids) or an
+// expert without a slot (remap < 0) becomes -1, which the plan reports as BWMOE_STATUS_BAD_EXPERT.
+__global__ void remap_ids_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ remap, int n_ids,
+                                 int n, int32_t* __restrict__ slots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  slots[i] = (id >= 0 && id < n_ids) ? remap[id] : -1;
+}
+
+// The block-scale pipeline behind the routing: plan -> per-token group quantisation -> rows into expert
+// order -> gate/up (+ SwiGLU + requant) -> down -> combine.
+int run_block_pipeline(const void* x, const float* weights, const int32_t* indices, const void* wg, const void* wu,
+                       const void* wd, const float* inv_g, const float* inv_u, const float* inv_d, int T, int D,
+                       int H, int E, int K, void* out, void* ws, const BlockLayout& L, cudaStream_t st) {
+  const int M = T * K;
+  int32_t* status = at<int32_t>(ws, L.status);
+  int32_t* offsets = at<int32_t>(ws, L.offsets);
+  int rc;
+  if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
+                        at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
+    return rc;
+  if ((rc = launch_quant_then_gather_group(x, at<int32_t>(ws, L.row_slot), T, D, K, at<void>(ws, L.xq_tok),
+                                           at<float>(ws, L.inv_tok), at<void>(ws, L.xq), at<float>(ws, L.x_inv), st)))
+    return rc;
+  if ((rc = launch_gateup_block(at<void>(ws, L.xq), at<float>(ws, L.x_inv), offsets, wg, wu, inv_g, inv_u, M, D, H, E,
+                                at<void>(ws, L.hq), at<float>(ws, L.h_inv), status, st)))
+    return rc;
+  if ((rc = launch_down_block(at<void>(ws, L.hq), at<float>(ws, L.h_inv), offsets, wd, inv_d, M, D, H, E,
+                              at<void>(ws, L.y), status, st)))
+    return rc;
+  return launch_combine(at<void>(ws, L.y), at<int32_t>(ws, L.pos), weights, T, D, K, out, st);
+}
+
+int check_block_args(const char* who, const void* x, const void* wg, const void* wu, const void* wd,
+                     const float* inv_g, const float* inv_u, const float* inv_d, int T, int D, int H, int E, int K,
+                     void* out, void* ws, size_t ws_bytes, BlockLayout* L) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && H > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "%s: T=%d D=%d H=%d E=%d K=%d", who,
+                T, D, H, E, K);
+  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
+  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "%s: E=%d > 256 experts", who, E);
+  BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "%s: top_k=%d must be <= min(E,32)", who, K);
+  BWMOE_REQUIRE(x && wg && wu && wd && inv_g && inv_u && inv_d && out, BWMOE_ERR_NULL, "%s: null pointer", who);
+  BWMOE_REQUIRE(make_block_layout(T, D, H, E, K, L), BWMOE_ERR_BAD_SHAPE, "%s: shape not representable", who);
+  BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L->total, BWMOE_ERR_WORKSPACE,
+                "%s: workspace of %zu bytes given, %zu needed", who, ws_bytes, L->total);
+  BWMOE_REQUIRE(aligned16(x) && aligned16(out) && aligned16(wg) && aligned16(wu) && aligned16(wd) &&
+                    (reinterpret_cast<uintptr_t>(ws) % 256 == 0),
+                BWMOE_ERR_BAD_ALIGN, "%s: tensors must be 16-byte and the workspace 256-byte aligned", who);
+  return BWMOE_OK;
 }
 
 }  // namespace
@@ -365,6 +419,30 @@ int bwmoe_moe_forward_routed(const void* x, const float* weights, const int32_t*
   return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
 }
 
+int bwmoe_moe_forward_routed_remap(const void* x, const float* weights, const int32_t* expert_ids,
+                                   const int32_t* remap, int n_experts_total, const void* wg, const void* wu,
+                                   const void* wd, const float* sg, const float* su, const float* sd, int T, int D,
+                                   int H, int n_slots, int K, void* out, void* ws, size_t ws_bytes, void* stream) {
+  Layout L;
+  if (int rc = check_forward_args("moe_forward_routed_remap", x, wg, wu, wd, sg, su, sd, T, D, H, n_slots, K, out, ws,
+                                  ws_bytes, &L, 0))
+    return rc;
+  BWMOE_REQUIRE(weights && expert_ids && remap, BWMOE_ERR_NULL, "moe_forward_routed_remap: routing or remap is null");
+  BWMOE_REQUIRE(n_experts_total > 0, BWMOE_ERR_BAD_SHAPE, "moe_forward_routed_remap: %d experts", n_experts_total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = T * K;
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* row_amax = at<float>(ws, L.row_amax);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  int32_t* slots = at<int32_t>(ws, L.topk_idx);                 // the workspace's routing view holds slot ids
+  remap_ids_kernel<<<ceil_div(M, 256), 256, 0, st>>>(expert_ids, remap, n_experts_total, M, slots);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_w), weights, sizeof(float) * (size_t)M,
+                                cudaMemcpyDeviceToDevice, st));
+  return run_pipeline(x, weights, slots, row_amax, wg, wu, wd, sg, su, sd, T, D, H, n_slots, K, out, ws, L, st);
+}
+
 int bwmoe_moe_forward_host(const void* h_x, const void* w_gate, const void* wg, const void* wu, const void* wd,
                            const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
                            void* h_out, void* ws, size_t ws_bytes, void* stream) {
@@ -422,44 +500,45 @@ int bwmoe_moe_forward_block(const void* x, const void* w_gate, const void* wg, c
                             const float* inv_g, const float* inv_u, const float* inv_d, int T, int D, int H, int E,
                             int K, void* out, void* ws, size_t ws_bytes, void* stream) {
   BlockLayout L;
-  BWMOE_REQUIRE(T > 0 && D > 0 && H > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE,
-                "moe_forward_block: T=%d D=%d H=%d E=%d K=%d", T, D, H, E, K);
-  BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE,
-                "moe_forward_block: D=%d and H=%d must be multiples of 16", D, H);
-  BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "moe_forward_block: E=%d > 256 experts", E);
-  BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "moe_forward_block: top_k=%d must be <= min(E,32)", K);
-  BWMOE_REQUIRE(x && w_gate && wg && wu && wd && inv_g && inv_u && inv_d && out, BWMOE_ERR_NULL,
-                "moe_forward_block: null pointer");
-  BWMOE_REQUIRE(make_block_layout(T, D, H, E, K, &L), BWMOE_ERR_BAD_SHAPE, "moe_forward_block: shape not representable");
-  BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L.total, BWMOE_ERR_WORKSPACE,
-                "moe_forward_block: workspace of %zu bytes given, %zu needed", ws_bytes, L.total);
-  BWMOE_REQUIRE(aligned16(x) && aligned16(out) && aligned16(wg) && aligned16(wu) && aligned16(wd) &&
-                    (reinterpret_cast<uintptr_t>(ws) % 256 == 0),
-                BWMOE_ERR_BAD_ALIGN, "moe_forward_block: tensors must be 16-byte and the workspace 256-byte aligned");
+  if (int rc = check_block_args("moe_forward_block", x, wg, wu, wd, inv_g, inv_u, inv_d, T, D, H, E, K, out, ws,
+                                ws_bytes, &L))
+    return rc;
+  BWMOE_REQUIRE(w_gate != nullptr, BWMOE_ERR_NULL, "moe_forward_block: w_gate is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int M = T * K;
   BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
   float* weights = at<float>(ws, L.topk_w);
   int32_t* indices = at<int32_t>(ws, L.topk_idx);
-  int32_t* status = at<int32_t>(ws, L.status);
-  int32_t* offsets = at<int32_t>(ws, L.offsets);
-  int rc;
-  if ((rc = launch_router(x, w_gate, T, D, E, K, weights, indices, nullptr, st, at<void>(ws, L.router_scratch),
-                          L.router_scratch_bytes, status)))
+  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, nullptr, st, at<void>(ws, L.router_scratch),
+                             L.router_scratch_bytes, at<int32_t>(ws, L.status)))
     return rc;
-  if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
-                        at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
+  return run_block_pipeline(x, weights, indices, wg, wu, wd, inv_g, inv_u, inv_d, T, D, H, E, K, out, ws, L, st);
+}
+
+int bwmoe_moe_forward_block_routed(const void* x, const float* weights, const int32_t* expert_ids,
+                                   const int32_t* remap, int n_experts_total, const void* wg, const void* wu,
+                                   const void* wd, const float* inv_g, const float* inv_u, const float* inv_d, int T,
+                                   int D, int H, int n_slots, int K, void* out, void* ws, size_t ws_bytes,
+                                   void* stream) {
+  BlockLayout L;
+  if (int rc = check_block_args("moe_forward_block_routed", x, wg, wu, wd, inv_g, inv_u, inv_d, T, D, H, n_slots, K,
+                                out, ws, ws_bytes, &L))
     return rc;
-  if ((rc = launch_quant_then_gather_group(x, at<int32_t>(ws, L.row_slot), T, D, K, at<void>(ws, L.xq_tok),
-                                           at<float>(ws, L.inv_tok), at<void>(ws, L.xq), at<float>(ws, L.x_inv), st)))
-    return rc;
-  if ((rc = launch_gateup_block(at<void>(ws, L.xq), at<float>(ws, L.x_inv), offsets, wg, wu, inv_g, inv_u, M, D, H, E,
-                                at<void>(ws, L.hq), at<float>(ws, L.h_inv), status, st)))
-    return rc;
-  if ((rc = launch_down_block(at<void>(ws, L.hq), at<float>(ws, L.h_inv), offsets, wd, inv_d, M, D, H, E,
-                              at<void>(ws, L.y), status, st)))
-    return rc;
-  return launch_combine(at<void>(ws, L.y), at<int32_t>(ws, L.pos), weights, T, D, K, out, st);
+  BWMOE_REQUIRE(weights && expert_ids, BWMOE_ERR_NULL, "moe_forward_block_routed: routing is null");
+  BWMOE_REQUIRE(remap == nullptr || n_experts_total > 0, BWMOE_ERR_BAD_SHAPE,
+                "moe_forward_block_routed: remap given with %d experts", n_experts_total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = T * K;
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  int32_t* slots = at<int32_t>(ws, L.topk_idx);
+  if (remap != nullptr) {
+    remap_ids_kernel<<<ceil_div(M, 256), 256, 0, st>>>(expert_ids, remap, n_experts_total, M, slots);
+    BWMOE_CUDA_OK(cudaGetLastError());
+  } else {
+    BWMOE_CUDA_OK(cudaMemcpyAsync(slots, expert_ids, sizeof(int32_t) * (size_t)M, cudaMemcpyDeviceToDevice, st));
+  }
+  BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_w), weights, sizeof(float) * (size_t)M,
+                                cudaMemcpyDeviceToDevice, st));
+  return run_block_pipeline(x, weights, slots, wg, wu, wd, inv_g, inv_u, inv_d, T, D, H, n_slots, K, out, ws, L, st);
 }
 
 int bwmoe_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,

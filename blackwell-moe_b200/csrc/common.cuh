@@ -28,6 +28,21 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int sm_count();
 int gemm_sm_budget();   // sm_count() minus the SMs reserved through bwmoe_set_sm_reserve
 
+// The dynamic shared-memory limit of a kernel is a per-device attribute: raise it once on every
+// device the kernel is launched on.  `done` is one flag array per kernel (a function-local static
+// of the caller); setting the attribute twice from two racing threads is harmless.
+template <class Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, unsigned char (&done)[64]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[dev] = 1;
+  return e;
+}
+
 // ---- arithmetic shared by several kernels ---------------------------------
 constexpr float kFp8Max = 448.0f;
 // The reference clamps amax in the tensor's own dtype (bf16), so the floor is

@@ -377,13 +377,8 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 template <bool GATE_UP>
 int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1,
                       const BlockGemmParams& p, int M, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(block_gemm_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
-  });
-  BWMOE_CUDA_OK(attr_err);
+  static unsigned char smem_set[64] = {0};
+  BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_kernel<GATE_UP>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
   block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, st>>>(ma, mb0, mb1, p);

@@ -377,8 +377,9 @@ swiglu_from_partials_kernel(const float* __restrict__ partial, int S, int M, int
                             const float* __restrict__ su, __nv_bfloat16* __restrict__ h, float* __restrict__ seg_amax) {
   const int vec_per_row = H / 4;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool live = gid < (size_t)M * vec_per_row;
+  bool live = gid < (size_t)M * vec_per_row;
   const int m = live ? (int)(gid / vec_per_row) : 0, v = live ? (int)(gid % vec_per_row) : 0;
+  live = live && m < offsets[E];              // rows past the last segment belong to no expert
   const int e = expert_of_row(offsets, E, m);
   float amax = 0.f;
   if (live) {
@@ -429,6 +430,7 @@ down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)M * vec_per_row) return;
   const int m = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
+  if (m >= offsets[E]) return;                // rows past the last segment belong to no expert
   const int e = expert_of_row(offsets, E, m);
   float a[4] = {0.f, 0.f, 0.f, 0.f};
   float4 t[kSplitMax];
@@ -481,10 +483,9 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
     acc[2] += bf16_round(f1.x * w);
     acc[3] += bf16_round(f1.y * w);
   }
-  if (scale != 1.0f) {
-    const float sb = bf16_round(scale);
+  if (scale != 1.0f) {     // bf16 tensor times a Python scalar: fp32 product with the unrounded scalar
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * sb);
+    for (int i = 0; i < 4; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * scale);
   }
   if (residual != nullptr) {
     const uint2 raw = reinterpret_cast<const uint2*>(residual + (size_t)t * D)[v];
@@ -520,13 +521,8 @@ SplitPlan choose_split(int M, int E, int k_blocks, int n_tiles) {
 template <bool GATE_UP, bool RAW>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const GemmParams& p,
                 int M, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_kernel<GATE_UP, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
-  });
-  BWMOE_CUDA_OK(attr_err);
+  static unsigned char smem_set[64] = {0};
+  BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, RAW>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
   grouped_gemm_kernel<GATE_UP, RAW><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);

@@ -80,10 +80,12 @@ plan_scan_kernel(int32_t* __restrict__ block_hist, int B, int E, int32_t* __rest
 // ---- pass 3: stable rank of every slot inside its block -> permuted row ----
 __global__ void __launch_bounds__(kPlanThreads)
 plan_rank_kernel(const int32_t* __restrict__ indices, int M, int E, const int32_t* __restrict__ block_base,
-                 int32_t* __restrict__ pos, int32_t* __restrict__ row_slot, int32_t* __restrict__ row_expert) {
+                 const int32_t* __restrict__ offsets, int32_t* __restrict__ pos, int32_t* __restrict__ row_slot,
+                 int32_t* __restrict__ row_expert) {
   extern __shared__ int cnt[];            // [32 warps][E] counts of this round, then exclusive prefixes
   __shared__ int round_base[kMaxE];       // slots of earlier rounds in this block, per expert
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_rows = offsets[E];          // rows that exist (slots with a valid expert id)
   for (int e = threadIdx.x; e < E; e += blockDim.x) round_base[e] = block_base[(size_t)blockIdx.x * E + e];
   const int s0 = blockIdx.x * kSlotsPerBlock;
   for (int r = 0; r < kSlotsPerBlock / kPlanThreads; ++r) {
@@ -119,6 +121,9 @@ plan_rank_kernel(const int32_t* __restrict__ indices, int M, int E, const int32_
     } else if (s < M) {
       pos[s] = -1;
     }
+    // slots with an expert id out of range own no row: the rows past the last segment are marked
+    // so that the row-wise kernels behind the plan skip them
+    if (s < M && s >= n_rows) row_slot[s] = -1, row_expert[s] = -1;
     __syncthreads();
     for (int ee = threadIdx.x; ee < E; ee += blockDim.x) round_base[ee] += cnt[32 * E + ee];
     __syncthreads();
@@ -183,6 +188,8 @@ plan_small_kernel(const int32_t* __restrict__ indices, const float* __restrict__
   } else if (s < M) {
     pos[s] = -1;
   }
+  // rows past the last segment (slots with an out-of-range expert id own none): marked as absent
+  if (s < M && s >= start[E]) row_slot[s] = -1, row_expert[s] = -1;
 }
 
 __global__ void segment_scales_kernel(const float* __restrict__ seg_amax, const int32_t* __restrict__ offsets,
@@ -233,10 +240,11 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= M * per_row) return;
   const unsigned m = p / per_row, c = p - m * per_row;
+  const int expert = row_expert[m];
+  if (expert < 0) return;                        // a row no slot owns (expert id out of range)
   const size_t srow = SRC_BY_SLOT ? (size_t)(row_slot[m] / K) : (size_t)m;
   const uint4* in = reinterpret_cast<const uint4*>(src + srow * W) + 2 * c;
   const uint4 r0 = in[0], r1 = in[1];
-  const int expert = row_expert[m];
   float scale = scales[expert];
   if (FROM_AMAX) {
     scale = scale_from_amax(scale);
@@ -421,10 +429,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
       }
     }
   }
-  if (scale != 1.0f) {
-    const float sb = bf16_round(scale);
+  if (scale != 1.0f) {     // bf16 tensor times a Python scalar: torch multiplies in fp32 by the unrounded scalar
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * sb);
+    for (int i = 0; i < 8; ++i) acc[i] = bf16_round(bf16_round(acc[i]) * scale);
   }
   if (residual != nullptr) {
     const uint4 raw = reinterpret_cast<const uint4*>(residual + (size_t)t * D)[v];
@@ -475,7 +482,7 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
                                                row_amax ? seg_amax : nullptr, status);
   plan_scan_kernel<<<1, kMaxE, 0, st>>>(block_hist, B, E, offsets);
   const size_t smem = (size_t)33 * E * sizeof(int);
-  plan_rank_kernel<<<B, kPlanThreads, smem, st>>>(indices, M, E, block_hist, pos, row_slot, row_expert);
+  plan_rank_kernel<<<B, kPlanThreads, smem, st>>>(indices, M, E, block_hist, offsets, pos, row_slot, row_expert);
   BWMOE_CUDA_OK(cudaGetLastError());
   if (scales_out != nullptr) return launch_segment_scales(seg_amax, offsets, E, scales_out, st);
   return BWMOE_OK;

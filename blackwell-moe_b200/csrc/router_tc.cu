@@ -403,8 +403,10 @@ TcScratch tc_layout(int T, int D, int E) {
 
 }  // namespace
 
+// D <= 4096: the trust bound kTcTrust on the tensor-core logits is argued for sums of at most 4096
+// products; wider hidden sizes take the SIMT routers, whose error bound scales with D by construction.
 bool router_tc_applicable(int T, int D, int E, int K) {
-  return T >= 1024 && E >= 8 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0;
+  return T >= 1024 && E >= 8 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0 && D <= 4096;
 }
 
 size_t router_tc_scratch_bytes(int T, int D, int E) { return tc_layout(T, D, E).total; }
@@ -433,12 +435,8 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   CUtensorMap mx, mw;
   if (int rc = make_map_bf16(&mx, x, T, D, R_BK, BM)) return rc;
   if (int rc = make_map_bf16(&mw, wg, D, E, 64, R_BK)) return rc;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(tc_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM_BYTES);
-  });
-  BWMOE_CUDA_OK(attr_err);
+  static unsigned char smem_set[64] = {0};
+  BWMOE_CUDA_OK(ensure_dynamic_smem(tc_logits_kernel, R_SMEM_BYTES, smem_set));
   TcParams p{logits, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16};
   const int grid = std::min(sm_count(), ceil_div(T, BM));
   tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, st>>>(mx, mw, p);

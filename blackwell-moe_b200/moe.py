@@ -159,29 +159,80 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
 
 
 def fp8_moe_forward_routed(x, router_weights, expert_indices, experts_w_gate, experts_w_up, experts_w_down,
-                           scales_gate, scales_up, scales_down) -> torch.Tensor:
+                           scales_gate, scales_up, scales_down, remap=None) -> torch.Tensor:
     """Same block with caller-supplied routing (``router_weights[T,K] fp32``,
-    ``expert_indices[T,K] int32`` into the E weight slots) - the entry point an
-    expert-residency cache uses after remapping expert ids to slots
-    (src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-55)."""
+    ``expert_indices[T,K] int32``) - the entry point an expert-residency cache uses
+    (src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-55).
+
+    Without ``remap`` the indices address the E weight slots directly.  With
+    ``remap[E_total] int32`` they are expert ids of the whole model and
+    ``remap[id]`` is the slot that holds the expert (``-1``: not resident); the
+    lookup runs on the device.  3-D ``scales_*`` select the block-scale recipe."""
     T, D, H, E = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down,
                                 scales_gate, scales_up, scales_down)
     assert router_weights.shape == expert_indices.shape and router_weights.shape[0] == T
     K = router_weights.shape[1]
+    block = scales_gate.dim() == 3
     tensors = [_contig(t, "tensor") for t in (x, router_weights.to(torch.float32), expert_indices.to(torch.int32),
                                               experts_w_gate, experts_w_up, experts_w_down,
                                               scales_gate, scales_up, scales_down)]
     dev = _require_cuda(*tensors)
+    n_total = 0
+    if remap is not None:
+        remap = _contig(remap.to(torch.int32), "remap")
+        _require_cuda(x, remap)
+        n_total = remap.numel()
     lib = _lib.lib()
     with torch.cuda.device(dev):
-        need = lib.bwmoe_workspace_bytes(T, D, H, E, K)
+        need = (lib.bwmoe_workspace_bytes_block if block else lib.bwmoe_workspace_bytes)(T, D, H, E, K)
         if need == 0:
             raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={K}")
         ws = _workspace(dev, need)
         out = torch.empty_like(x)
-        _lib.check(lib.bwmoe_moe_forward_routed(*[t.data_ptr() for t in tensors], T, D, H, E, K,
-                                                out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)))
+        p = [t.data_ptr() for t in tensors]
+        tail = (T, D, H, E, K, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev))
+        if block:
+            _lib.check(lib.bwmoe_moe_forward_block_routed(p[0], p[1], p[2], remap.data_ptr() if remap is not None else None,
+                                                          n_total, *p[3:], *tail))
+        elif remap is not None:
+            _lib.check(lib.bwmoe_moe_forward_routed_remap(p[0], p[1], p[2], remap.data_ptr(), n_total, *p[3:], *tail))
+        else:
+            _lib.check(lib.bwmoe_moe_forward_routed(*p, *tail))
     return out
+
+
+def fp8_moe_forward_fastcache(x, router_weights, expert_indices, remap, cache_g, cache_u, cache_d,
+                              cache_sg, cache_su, cache_sd, n_slots: int, top_k: int = 8) -> torch.Tensor:
+    """Signature of the reference's ``fp8_moe_forward_fastcache``
+    (src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-29): original expert ids plus the
+    cache's ``remap`` tensor, experts taken from the ``[n_slots, ...]`` pool tensors."""
+    assert cache_g.shape[0] == n_slots and expert_indices.shape[1] == top_k, (cache_g.shape, n_slots, top_k)
+    return fp8_moe_forward_routed(x, router_weights, expert_indices, cache_g, cache_u, cache_d,
+                                  cache_sg, cache_su, cache_sd, remap=remap)
+
+
+def streaming_moe_forward(x, w_gate, cache, layer_idx: int, top_k: int, prefetch_next_layer=None) -> torch.Tensor:
+    """MoE-block forward over an expert-residency cache, with the call protocol of the reference's
+    ``streaming_moe_forward`` (src/blackwell_moe/runtime/streaming_moe.py:32-107).  ``cache`` is any
+    object with the interface of ``ThreeTierExpertCache``
+    (src/blackwell_moe/runtime/disk_expert_pool.py:89-268): ``gpu`` (dict of ``[gpu_slots, ...]``
+    pool tensors ``gate_q/up_q/down_q/scale_g/scale_u/scale_d``), ``gpu_slots``, ``n_experts``,
+    ``fetch(layer_idx, expert_ids) -> slot tensor`` and ``prefetch_layer``; the cache itself stays
+    host-side code and is not part of this package.
+
+    The router, the id -> slot lookup and the whole pipeline run in the library; what remains on the
+    host is what the cache's interface demands: the list of distinct expert ids of the batch."""
+    if prefetch_next_layer is not None:
+        cache.prefetch_layer(prefetch_next_layer)
+    weights, indices = top_k_router(x, w_gate, top_k)
+    unique_eids = torch.unique(indices.flatten())
+    slots = cache.fetch(layer_idx, unique_eids.tolist())
+    n_total = max(int(w_gate.shape[1]), int(getattr(cache, "n_experts", 0)))
+    remap = torch.full((n_total,), -1, dtype=torch.int32, device=x.device)
+    remap[unique_eids.long()] = slots.to(device=x.device, dtype=torch.int32)
+    gpu = cache.gpu
+    return fp8_moe_forward_routed(x, weights, indices, gpu["gate_q"], gpu["up_q"], gpu["down_q"],
+                                  gpu["scale_g"], gpu["scale_u"], gpu["scale_d"], remap=remap)
 
 
 _VIEWS = {

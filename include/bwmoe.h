@@ -74,8 +74,9 @@ enum {
 
 int bwmoe_version(void);
 
-/* Process-wide: the persistent GEMM kernels launch on (SM count - n) SMs, leaving n free for
- * kernels that must run beside them (NCCL collectives of the expert-parallel path).  Default 0.
+/* For the calling thread: the persistent GEMM kernels it launches from now on use (SM count - n) SMs,
+ * leaving n free for kernels that must run beside them (the dispatch of the next token chunk, or NCCL
+ * collectives, of the expert-parallel path).  Default 0.  Other threads keep their own setting.
  * No counterpart in the reference (it is single-GPU). */
 int bwmoe_set_sm_reserve(int n);
 
@@ -167,6 +168,25 @@ int bwmoe_moe_forward_routed(const void* d_x, const float* d_weights, const int3
                              void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The routed form for an expert-residency cache: d_expert_ids[T,K] int32 are expert ids of the whole
+ * model and d_remap[n_experts_total] int32 maps each id to its slot in the resident pool (the
+ * [n_slots, ...] weight tensors), -1 for an expert that is not resident.  The lookup runs on the
+ * device; a slot of -1 (or an id outside [0, n_experts_total)) is skipped and raises
+ * BWMOE_STATUS_BAD_EXPERT.  Workspace: bwmoe_workspace_bytes(T, D, H, n_slots, K).
+ * replaces: the `remap[expert_indices]` gather of fp8_moe_forward_fastcache,
+ *           src/blackwell_moe/kernels/fp8_moe_fastcache.py:16-34, and the per-expert Python loop that
+ *           builds slot ids in streaming_moe_forward, src/blackwell_moe/runtime/streaming_moe.py:61-76.
+ */
+int bwmoe_moe_forward_routed_remap(const void* d_x, const float* d_weights, const int32_t* d_expert_ids,
+                                   const int32_t* d_remap, int n_experts_total,
+                                   const void* d_slots_w_gate, const void* d_slots_w_up,
+                                   const void* d_slots_w_down,
+                                   const float* d_scales_gate, const float* d_scales_up,
+                                   const float* d_scales_down,
+                                   int T, int D, int H, int n_slots, int K,
+                                   void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
  * bwmoe_moe_forward for callers that hold activations in host memory: copies
  * h_x[T,D] to the device (into the workspace), runs the block, copies the result
  * to h_out[T,D] and waits for it.  Weights stay device-resident.  The workspace
@@ -202,6 +222,21 @@ int bwmoe_moe_forward_block(const void* d_x, const void* d_w_gate,
                             const float* d_inv_gate, const float* d_inv_up, const float* d_inv_down,
                             int T, int D, int H, int E, int K,
                             void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * bwmoe_moe_forward_block with the routing decided by the caller.  d_remap may be null (the ids then
+ * index the n_slots weight slots directly); otherwise as in bwmoe_moe_forward_routed_remap.
+ * Workspace: bwmoe_workspace_bytes_block(T, D, H, n_slots, K).
+ * replaces: the per-expert loop of StreamingQwenMoE.forward over resident experts,
+ *           src/blackwell_moe/runtime/qwen_patch.py:100-136.
+ */
+int bwmoe_moe_forward_block_routed(const void* d_x, const float* d_weights, const int32_t* d_expert_ids,
+                                   const int32_t* d_remap, int n_experts_total,
+                                   const void* d_slots_w_gate, const void* d_slots_w_up,
+                                   const void* d_slots_w_down,
+                                   const float* d_inv_gate, const float* d_inv_up, const float* d_inv_down,
+                                   int T, int D, int H, int n_slots, int K,
+                                   void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /* Stages of the block-scale recipe (d_row_slot may be null: rows are then taken in order). */
 int bwmoe_gather_quant_group(const void* d_x, const int32_t* d_row_slot, int M, int D, int K,

@@ -85,20 +85,36 @@ def block_gemm(aq, a_inv, wq, w_inv):
 
 
 def moe_forward_block_recipe(x, w_gate, wq_gate, wq_up, wq_down, inv_gate, inv_up, inv_down,
-                             top_k=8, routing=None, intermediates=None):
-    """Block-scale MoE forward; scales ``inv_*`` are ``[E, ceil(in/128), ceil(out/128)]``."""
+                             top_k=8, routing=None, intermediates=None, experts=None, num_experts=None):
+    """Block-scale MoE forward; scales ``inv_*`` are ``[E, ceil(in/128), ceil(out/128)]``.
+
+    ``experts`` restricts the per-expert work (activation quantisation included) to the given
+    segments, for shapes whose full forward is too slow on CPU; routing and permutation still
+    cover every row and the other segments' rows stay zero.  The weight and scale arguments may
+    then be dicts ``{expert id: tensor}`` with ``num_experts`` giving E."""
     T, D = x.shape
-    E, _, H = wq_gate.shape
+    if isinstance(wq_gate, dict):
+        E, H = int(num_experts), next(iter(wq_gate.values())).shape[1]
+    else:
+        E, _, H = wq_gate.shape
     if routing is None:
         routing = router_canonical(x, w_gate, top_k)
     weights, indices = routing
     sort_perm, inverse_idx, offsets = permutation(indices, E)
     M = sort_perm.numel()
-    x_perm = x[inverse_idx]
-    xq, x_inv = quant_act_group_128(x_perm)
+    g = (D + BLOCK - 1) // BLOCK
+    if experts is None:
+        xq, x_inv = quant_act_group_128(x[inverse_idx])
+    else:       # quantisation is per row, so doing it segment by segment gives the same codes
+        xq = torch.zeros(M, D, dtype=torch.float8_e4m3fn)
+        x_inv = torch.zeros(M, g, dtype=torch.float32)
+        for e in experts:
+            s, t = int(offsets[e]), int(offsets[e + 1])
+            if t > s:
+                xq[s:t], x_inv[s:t] = quant_act_group_128(x[inverse_idx[s:t]])
     y_perm = torch.zeros(M, D, dtype=torch.bfloat16)
     hq_all = torch.zeros(M, H, dtype=torch.float8_e4m3fn)
-    for e in range(E):
+    for e in (range(E) if experts is None else experts):
         s, t = int(offsets[e]), int(offsets[e + 1])
         if t <= s:
             continue

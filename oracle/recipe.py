@@ -138,11 +138,20 @@ def moe_forward_bf16(x, w_gate, experts_w_gate, experts_w_up, experts_w_down, to
 # grouped_fp8_gateup.py:91-101).
 # --------------------------------------------------------------------------
 def moe_forward_fp8_recipe(x, w_gate, wq_gate, wq_up, wq_down, s_gate, s_up, s_down,
-                           top_k=8, routing=None, intermediates=None):
+                           top_k=8, routing=None, intermediates=None, experts=None):
     """Per-expert-segment FP8 recipe.  ``intermediates`` (a dict) receives the
-    permutation, FP8 codes and scales for stage-level parity checks."""
+    permutation, FP8 codes and scales for stage-level parity checks.
+
+    ``experts`` (an iterable of expert ids) restricts the per-expert work to those
+    segments, for shapes whose full forward is too slow on CPU: routing and
+    permutation are still computed for every row, the rows of the other segments
+    stay zero, and the weight tensors may then be dicts ``{expert id: tensor}``
+    holding the chosen experts only (the ``[E]`` scale tensors stay whole)."""
     T, D = x.shape
-    E, _, H = wq_gate.shape
+    if isinstance(wq_gate, dict):
+        E, H = int(s_gate.shape[0]), next(iter(wq_gate.values())).shape[1]
+    else:
+        E, _, H = wq_gate.shape
     if routing is None:
         routing = router_canonical(x, w_gate, top_k)
     weights, indices = routing
@@ -156,7 +165,7 @@ def moe_forward_fp8_recipe(x, w_gate, wq_gate, wq_up, wq_down, s_gate, s_up, s_d
     y_perm = torch.zeros(M, D, dtype=torch.bfloat16)
     sx_all = torch.ones(E, dtype=torch.float32)   # empty segment -> 1.0 (segment_ops.py:27-29)
     sh_all = torch.ones(E, dtype=torch.float32)
-    for e in range(E):
+    for e in (range(E) if experts is None else experts):
         s, t = int(offsets[e]), int(offsets[e + 1])
         if t <= s:
             continue

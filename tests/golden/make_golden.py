@@ -132,6 +132,34 @@ def block_and_shared_cases():
         s_sg=sh.s_gate.numpy(), s_su=sh.s_up.numpy(), s_sd=sh.s_down.numpy())
 
 
+def expert_file_cases():
+    """Per-expert files written by the reference's own save_expert_to_disk
+    (src/blackwell_moe/runtime/disk_expert_pool.py:38-56), with the tensors that went in and the
+    reference's FP8 forward over them, for the weight-format adapter tests."""
+    from blackwell_moe.runtime.disk_expert_pool import save_expert_to_disk
+    from blackwell_moe.kernels.fp8_quant import quant_fp8_e4m3
+    from blackwell_moe.kernels.fp8_moe_torch import fp8_moe_forward_torch
+    T, D, E, K, H, layer = 48, 128, 4, 2, 96, 2
+    g = gen(500)
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(D, E, generator=g) * 0.02).to(torch.bfloat16)
+    qs = {"g": [], "u": [], "d": []}
+    ss = {"g": [], "u": [], "d": []}
+    root = OUT / "expert_files"
+    for e in range(E):
+        for key, shape in (("g", (D, H)), ("u", (D, H)), ("d", (H, D))):
+            q, s = quant_fp8_e4m3((torch.randn(shape, generator=g) * 0.02).to(torch.bfloat16))
+            qs[key].append(q), ss[key].append(s)
+        save_expert_to_disk(root, layer, e, qs["g"][e], qs["u"][e], qs["d"][e], ss["g"][e], ss["u"][e], ss["d"][e])
+    stack = lambda xs: torch.stack(xs)                                          # noqa: E731
+    eg8, eu8, ed8 = stack(qs["g"]), stack(qs["u"]), stack(qs["d"])
+    sg, su, sd = stack(ss["g"]), stack(ss["u"]), stack(ss["d"])
+    y_fp8 = fp8_moe_forward_torch(x, wg, eg8, eu8, ed8, sg, su, sd, K)
+    np.savez_compressed(OUT / "expert_files.npz", x=bits(x), wg=bits(wg), eg8=bits(eg8), eu8=bits(eu8), ed8=bits(ed8),
+                        sg=sg.numpy(), su=su.numpy(), sd=sd.numpy(), y_fp8=bits(y_fp8), k=np.int32(K),
+                        layer=np.int32(layer))
+
+
 if __name__ == "__main__":
     import blackwell_moe
     print("reference version", blackwell_moe.__version__, "torch", torch.__version__)
@@ -139,5 +167,6 @@ if __name__ == "__main__":
     quant_cases()
     forward_cases()
     block_and_shared_cases()
+    expert_file_cases()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -73,3 +73,56 @@ def check_against_oracle(inp, out, views, ref_out, inter, tol=1e-2):
     err = oracle.rel_l1(out, ref_out)
     assert err < tol, f"rel-L1 vs FP8 recipe oracle {err:.4f} >= {tol}"
     return err
+
+
+# ---- full-size shapes: weights are made and quantised on the GPU (seconds instead of minutes), and the
+# oracle receives copies of the experts it checks only ----
+def make_gpu_weights(E, D, H, seed, block=False, dev="cuda:0", w_scale=0.02):
+    """Expert weights ~N(0, w_scale^2) bf16 generated expert by expert on the device and quantised there
+    with the package's load-time quantisers (plain torch ops): per expert matrix, or 128x128 blocks.
+    The codes and scales are *inputs* of both the CUDA path and the oracle."""
+    import blackwell_moe_b200 as bw
+    g = torch.Generator(device=dev)
+    out = {"q_gate": [], "q_up": [], "q_down": [], "s_gate": [], "s_up": [], "s_down": []}
+    for e in range(E):
+        for i, (name, shape) in enumerate((("gate", (D, H)), ("up", (D, H)), ("down", (H, D)))):
+            g.manual_seed(seed * 100003 + e * 7 + i)
+            w = (torch.randn(shape, generator=g, device=dev) * w_scale).to(BF16)
+            q, s = bw.quant_fp8_block_128(w) if block else bw.quant_fp8_e4m3(w)
+            out["q_" + name].append(q), out["s_" + name].append(s)
+    res = {k: torch.stack(v).contiguous() for k, v in out.items()}
+    for k in ("s_gate", "s_up", "s_down"):
+        res[k] = res[k].to(torch.float32)
+    return res
+
+
+def make_activations(T, D, E, seed, zipf=False):
+    """CPU x ~N(0,1) and w_gate ~N(0,0.02^2) in bf16.  zipf: expert popularity ~ Zipf(1.1) produced inside the
+    plain API by a constant input feature and a log-rank row of w_gate."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, D, generator=g).to(BF16)
+    w_gate = (torch.randn(D, E, generator=g) * 0.02).to(BF16)
+    if zipf:
+        ranks = torch.randperm(E, generator=g).float() + 1.0
+        bias = -1.1 * torch.log(ranks)
+        x[:, 0] = 1.0
+        w_gate[0] = (bias - bias.mean()).to(BF16)
+    return x, w_gate
+
+
+def expert_subset(W, experts):
+    """CPU copies of the chosen experts' codes as {expert id: tensor}; scales whole."""
+    sub = {}
+    for k in ("q_gate", "q_up", "q_down"):
+        sub[k] = {int(e): W[k][int(e)].cpu() for e in experts}
+    for k in ("s_gate", "s_up", "s_down"):
+        sub[k] = W[k].cpu()
+    return sub
+
+
+def combine_on_cpu(y, weights, sort_perm, inverse_idx, T):
+    """The combine of fp8_moe_v3.py:70-73 applied to given result rows (bf16 products, bf16 index_add_)."""
+    flat_w = weights.reshape(-1)[sort_perm].to(BF16).unsqueeze(-1)
+    out = torch.zeros(T, y.shape[1], dtype=BF16)
+    out.index_add_(0, inverse_idx, (y * flat_w).to(BF16))
+    return out

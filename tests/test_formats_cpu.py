@@ -31,3 +31,17 @@ def test_hf_block_fp8_transposition_preserves_the_dequantised_weight(golden):
     deq = oracle.dequant_block_128(codes[1], inv[1])             # [in, out]
     ref = from_bits(g["deq"], torch.bfloat16)                    # reference _dequant_block_fp8, [out, in]
     assert torch.equal(deq.t().contiguous().view(torch.int16), ref.view(torch.int16))
+
+
+def test_files_written_by_the_reference_load_into_stacked_tensors(golden):
+    """tests/golden/expert_files/ was written by the reference's own save_expert_to_disk
+    (src/blackwell_moe/runtime/disk_expert_pool.py:38-56); the adapter must return exactly the tensors
+    that went in (stored beside the files by the same script)."""
+    from conftest import GOLDEN, from_bits
+    g = golden("expert_files")
+    E = g["eg8"].shape[0]
+    got = formats.load_layer_experts(GOLDEN / "expert_files", int(g["layer"]), E)
+    for a, key in zip(got[:3], ("eg8", "eu8", "ed8")):
+        assert a.dtype == FP8 and torch.equal(a.view(torch.uint8), from_bits(g[key], FP8).view(torch.uint8))
+    for a, key in zip(got[3:], ("sg", "su", "sd")):
+        assert a.dtype == torch.float32 and torch.equal(a, torch.from_numpy(g[key]))

@@ -106,25 +106,43 @@ def test_routed_entry_point_matches_full_forward():
     assert torch.equal(full, routed)
 
 
-def test_out_of_range_expert_ids_are_reported_not_trapped():
+@pytest.mark.parametrize("T", [40, 700])          # one-block plan and split-K GEMMs / three-pass plan
+def test_out_of_range_expert_ids_are_reported_not_trapped(T):
     """Caller-supplied routing with an expert id outside [0, E): the kernels skip the slot, finish
-    normally and raise the BAD_EXPERT bit of the status word; the context stays usable."""
+    normally and raise the BAD_EXPERT bit of the status word; the context stays usable.  The bad call
+    runs FIRST, on a workspace filled with 0x7f bytes, so that nothing a good call left behind can
+    stand in for the rows the bad slots do not own; the tokens with valid routing must come out
+    exactly as in a clean call."""
     import blackwell_moe_b200 as bw
-    inp = make_inputs(40, 256, 8, 2, 128, seed=15)
+    from blackwell_moe_b200 import moe as bwmoe
+    inp = make_inputs(T, 256, 8, 2, 128, seed=15)
     c = to_cuda(inp)
     args = (c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"], c["s_down"])
     w, idx = bw.top_k_router(c["x"], c["w_gate"], 2)
-    good = bw.fp8_moe_forward_routed(c["x"], w, idx, *args)
-    assert int(bw.moe_stage_views("cuda:0", 40, 256, 128, 8, 2)["status"][0]) == 0
+    torch.cuda.synchronize()
+    bw.moe.release_workspaces()
+    dev = torch.device("cuda:0")
+    bwmoe._workspace(dev, bw.lib().bwmoe_workspace_bytes(T, 256, 128, 8, 2)).fill_(0x7f)
     bad = idx.clone()
     bad[3, 1] = 99
     bad[17, 0] = -5
     out = bw.fp8_moe_forward_routed(c["x"], w, bad, *args)
-    v = bw.moe_stage_views("cuda:0", 40, 256, 128, 8, 2)
+    v = bw.moe_stage_views("cuda:0", T, 256, 128, 8, 2)
     assert int(v["status"][0]) & 2, "BAD_EXPERT bit not set"
     assert torch.isfinite(out.float()).all()
-    assert int(v["offsets"][-1]) == 40 * 2 - 2          # the two bad slots own no row
-    assert torch.equal(bw.fp8_moe_forward_routed(c["x"], w, idx, *args), good)   # and the next call is clean
+    n_rows = T * 2 - 2
+    assert int(v["offsets"][-1]) == n_rows              # the two bad slots own no row
+    assert torch.all(v["row_slot"][n_rows:] == -1) and torch.all(v["row_expert"][n_rows:] == -1)
+    good = bw.fp8_moe_forward_routed(c["x"], w, idx, *args)          # the next call is clean
+    assert int(bw.moe_stage_views("cuda:0", T, 256, 128, 8, 2)["status"][0]) == 0
+    # A bad slot removes one row from its expert's segment, which can move that segment's amax; tokens
+    # none of whose experts lost a row must be bit-identical to the clean call.
+    hit = torch.zeros(8, dtype=torch.bool, device=idx.device)
+    hit[idx[3, 1]] = True
+    hit[idx[17, 0]] = True
+    clean_tok = ~hit[idx.long()].any(dim=1)
+    assert clean_tok.any()
+    assert torch.equal(out[clean_tok], good[clean_tok])
 
 
 def test_full_size_mixtral_block_via_duplicated_tokens():

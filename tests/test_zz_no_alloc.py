@@ -5,9 +5,10 @@ allocate device memory where they call from (an allocator callback, a plugin
 that only receives its inputs and outputs, a loop that has frozen its memory
 pool).  For them the library carries a fixed 64 KiB scratch array of its own.
 This test drives that entry point through the C ABI and requires exactly the
-results of the regular entry point, twice in a row with different inputs, so
-that whatever the first call left in the shared array cannot leak into the
-second.  The file sorts last on purpose: a run that stops at the first failure
+results of the regular entry point, three times in a row with different expert
+counts and block counts, every call large enough to take the multi-pass plan
+that uses the array, so that whatever one call left in the shared array cannot
+leak into the next.  The file sorts last on purpose: a run that stops at the first failure
 has then already executed every other test.
 """
 
@@ -44,8 +45,10 @@ def test_static_scratch_plan_matches_regular_plan_twice():
     lib = bw.lib()
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(21)
-    # two calls in a row: a large one that fills many scratch blocks, then a small one
-    for T, E, K in ((9000, 64, 6), (37, 200, 3)):
+    # Three calls in a row, each with more than 1024 slots (smaller plans run in one block and never touch
+    # the array): 14 blocks x 64 experts, then 3 blocks x 200 experts over the same words, then the first
+    # shape again over what the second left behind.
+    for T, E, K in ((9000, 64, 6), (3000, 200, 3), (9000, 64, 6)):
         scores = torch.rand(T, E, generator=g)
         indices = scores.topk(K, dim=-1).indices.to(torch.int32).to(dev).contiguous()
         row_amax = torch.rand(T, generator=g).to(dev)
