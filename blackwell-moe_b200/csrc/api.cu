@@ -1,6 +1,7 @@
 // extern "C" surface of libbwmoe.so: argument checks, workspace layout, and the
 // composition of the stage kernels into the whole-block forward.
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -26,6 +27,11 @@ namespace {
 // the launches of one forward are issued by one thread, so two threads never see each other's setting.
 thread_local int g_sm_reserve = 0;
 }
+namespace {
+std::atomic<long long> g_launches{0};
+}
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 int gemm_sm_budget() { return std::max(1, sm_count() - g_sm_reserve); }
 
 int sm_count() {
@@ -262,6 +268,8 @@ int bwmoe_set_sm_reserve(int n) {
   return BWMOE_OK;
 }
 
+long long bwmoe_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
 int bwmoe_last_error(char* buf, size_t len) {
   const size_t n = strlen(g_error);
   if (buf != nullptr && len > 0) {
@@ -380,7 +388,7 @@ int bwmoe_dense_mlp(const void* x, const void* wg, const void* wu, const void* w
   float* row_amax = at<float>(ws, L.row_amax);
   int32_t* offsets = at<int32_t>(ws, L.offsets);
   int32_t* status = at<int32_t>(ws, L.status);
-  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
   BWMOE_CUDA_OK(cudaGetLastError());
   int rc;
   if ((rc = launch_dense_prepare(row_amax, T, offsets, at<float>(ws, L.amax_x), st))) return rc;
@@ -409,7 +417,7 @@ int bwmoe_moe_forward_routed(const void* x, const float* weights, const int32_t*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
   float* row_amax = at<float>(ws, L.row_amax);
-  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
   BWMOE_CUDA_OK(cudaGetLastError());
   // keep a copy of the routing in the workspace so that the views stay meaningful
   BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_idx), indices, sizeof(int32_t) * (size_t)T * K,
@@ -433,10 +441,10 @@ int bwmoe_moe_forward_routed_remap(const void* x, const float* weights, const in
   const int M = T * K;
   BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
   float* row_amax = at<float>(ws, L.row_amax);
-  row_amax_kernel<<<ceil_div(T, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
+  row_amax_kernel<<<ceil_div(T, 8), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), T, D, row_amax);
   BWMOE_CUDA_OK(cudaGetLastError());
   int32_t* slots = at<int32_t>(ws, L.topk_idx);                 // the workspace's routing view holds slot ids
-  remap_ids_kernel<<<ceil_div(M, 256), 256, 0, st>>>(expert_ids, remap, n_experts_total, M, slots);
+  remap_ids_kernel<<<ceil_div(M, 256), 256, 0, counted(st)>>>(expert_ids, remap, n_experts_total, M, slots);
   BWMOE_CUDA_OK(cudaGetLastError());
   BWMOE_CUDA_OK(cudaMemcpyAsync(at<void>(ws, L.topk_w), weights, sizeof(float) * (size_t)M,
                                 cudaMemcpyDeviceToDevice, st));
@@ -531,7 +539,7 @@ int bwmoe_moe_forward_block_routed(const void* x, const float* weights, const in
   BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
   int32_t* slots = at<int32_t>(ws, L.topk_idx);
   if (remap != nullptr) {
-    remap_ids_kernel<<<ceil_div(M, 256), 256, 0, st>>>(expert_ids, remap, n_experts_total, M, slots);
+    remap_ids_kernel<<<ceil_div(M, 256), 256, 0, counted(st)>>>(expert_ids, remap, n_experts_total, M, slots);
     BWMOE_CUDA_OK(cudaGetLastError());
   } else {
     BWMOE_CUDA_OK(cudaMemcpyAsync(slots, expert_ids, sizeof(int32_t) * (size_t)M, cudaMemcpyDeviceToDevice, st));

@@ -23,6 +23,14 @@ int set_error(int code, const char* fmt, ...);
     if (!(cond)) return ::bwmoe::set_error(code, __VA_ARGS__); \
   } while (0)
 
+// Kernels this library has launched in the process so far (bwmoe_launch_count).  Every launch passes its
+// stream through counted(), so the figure is a count of launches, not an estimate.
+void note_launch();
+inline cudaStream_t counted(cudaStream_t st) {
+  note_launch();
+  return st;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int sm_count();

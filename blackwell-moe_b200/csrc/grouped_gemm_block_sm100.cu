@@ -381,7 +381,7 @@ int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUten
   BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_kernel<GATE_UP>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -491,7 +491,7 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
   int threads = 32;
   while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
   const unsigned grid = (unsigned)((size_t)M * ceil_div(vecs_per_row, threads * kGroupVecs));
-  quant_group_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
+  quant_group_rows_kernel<<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
                                                     static_cast<uint8_t*>(xq), x_inv);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -507,7 +507,7 @@ int launch_quant_then_gather_group(const void* x, const int32_t* row_slot, int T
   int threads = 32;
   while (threads < 256 && threads < vec_per_row) threads <<= 1;
   const unsigned grid = (unsigned)((size_t)M * ceil_div(vec_per_row, threads));
-  gather_quantised_rows_kernel<<<grid, threads, 0, st>>>(static_cast<const uint8_t*>(xq_tok), inv_tok, row_slot, M, D,
+  gather_quantised_rows_kernel<<<grid, threads, 0, counted(st)>>>(static_cast<const uint8_t*>(xq_tok), inv_tok, row_slot, M, D,
                                                         K, groups, static_cast<uint8_t*>(xq), x_inv);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -576,7 +576,7 @@ int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, co
     pi.p[r] = inv_of_rank[r];
   }
   const size_t n = (size_t)T * (D / 16);
-  scatter_quantised_rows_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+  scatter_quantised_rows_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
       static_cast<const uint8_t*>(xq_tok), inv_tok, pos, indices, delta, T, D, K, groups, experts_per_rank, px, pi);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;

@@ -525,7 +525,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap
   BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, RAW>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  grouped_gemm_kernel<GATE_UP, RAW><<<grid, GEMM_THREADS, SMEM_BYTES, st>>>(ma, mb0, mb1, p);
+  grouped_gemm_kernel<GATE_UP, RAW><<<grid, GEMM_THREADS, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -564,7 +564,7 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
   p.partial = static_cast<float*>(scratch);
   if (int rc = launch_gemm<true, true>(ma, mg, mu, p, M, st)) return rc;
   const size_t n = (size_t)M * (H / 4);
-  swiglu_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+  swiglu_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
       p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<__nv_bfloat16*>(h), amax_h);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -602,7 +602,7 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
   if (int rc = launch_gemm<false, true>(ma, mb, mb, p, M, st)) return rc;
   if (combine != nullptr && fused != nullptr && combine->T * combine->K == M) {
     const size_t nt = (size_t)combine->T * (D / 4);
-    down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, st>>>(
+    down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, counted(st)>>>(
         p.partial, sp.split_k, M, D, offsets, E, sh, sd, static_cast<__nv_bfloat16*>(y), combine->pos,
         combine->weights, combine->T, combine->K, static_cast<__nv_bfloat16*>(combine->out), combine->scale,
         static_cast<const __nv_bfloat16*>(combine->residual));
@@ -611,7 +611,7 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
     return BWMOE_OK;
   }
   const size_t n = (size_t)M * (D / 4);
-  down_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.partial, sp.split_k, M, D, offsets, E, sh,
+  down_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(p.partial, sp.split_k, M, D, offsets, E, sh,
                                                                         sd, static_cast<__nv_bfloat16*>(y));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;

@@ -470,7 +470,7 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
                 "plan: null pointer");
   const int M = T * K;
   if (M <= kPlanThreads) {
-    plan_small_kernel<<<1, kPlanThreads, (size_t)32 * E * sizeof(int), st>>>(
+    plan_small_kernel<<<1, kPlanThreads, (size_t)32 * E * sizeof(int), counted(st)>>>(
         indices, row_amax, M, E, K, offsets, pos, row_slot, row_expert, seg_amax, scales_out, status);
     BWMOE_CUDA_OK(cudaGetLastError());
     return BWMOE_OK;
@@ -478,11 +478,11 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
   const int B = ceil_div(M, kSlotsPerBlock);
   int32_t* block_hist = static_cast<int32_t*>(scratch);
   if (seg_amax != nullptr) BWMOE_CUDA_OK(cudaMemsetAsync(seg_amax, 0, sizeof(float) * E, st));
-  plan_hist_kernel<<<B, kPlanThreads, 0, st>>>(indices, row_amax, M, E, K, block_hist,
+  plan_hist_kernel<<<B, kPlanThreads, 0, counted(st)>>>(indices, row_amax, M, E, K, block_hist,
                                                row_amax ? seg_amax : nullptr, status);
-  plan_scan_kernel<<<1, kMaxE, 0, st>>>(block_hist, B, E, offsets);
+  plan_scan_kernel<<<1, kMaxE, 0, counted(st)>>>(block_hist, B, E, offsets);
   const size_t smem = (size_t)33 * E * sizeof(int);
-  plan_rank_kernel<<<B, kPlanThreads, smem, st>>>(indices, M, E, block_hist, offsets, pos, row_slot, row_expert);
+  plan_rank_kernel<<<B, kPlanThreads, smem, counted(st)>>>(indices, M, E, block_hist, offsets, pos, row_slot, row_expert);
   BWMOE_CUDA_OK(cudaGetLastError());
   if (scales_out != nullptr) return launch_segment_scales(seg_amax, offsets, E, scales_out, st);
   return BWMOE_OK;
@@ -532,7 +532,7 @@ int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, 
                           cudaStream_t st) {
   BWMOE_REQUIRE(E > 0, BWMOE_ERR_BAD_SHAPE, "segment_scales: E=%d", E);
   BWMOE_REQUIRE(seg_amax && scales, BWMOE_ERR_NULL, "segment_scales: null pointer");
-  segment_scales_kernel<<<ceil_div(E, 128), 128, 0, st>>>(seg_amax, offsets, E, scales);
+  segment_scales_kernel<<<ceil_div(E, 128), 128, 0, counted(st)>>>(seg_amax, offsets, E, scales);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -542,7 +542,7 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
   BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant: M=%d D=%d K=%d", M, D, K);
   BWMOE_REQUIRE(x && row_slot && row_expert && scales && xq, BWMOE_ERR_NULL, "gather_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant: pointers must be 16-byte aligned");
-  quant_rows_kernel<true, false><<<quant_grid(M, D), 256, 0, st>>>(
+  quant_rows_kernel<true, false><<<quant_grid(M, D), 256, 0, counted(st)>>>(
       static_cast<const __nv_bfloat16*>(x), row_slot, row_expert, scales, nullptr, M, D, K, static_cast<uint8_t*>(xq));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -553,7 +553,7 @@ int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indic
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_quant: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(x && pos && indices && scales && xq, BWMOE_ERR_NULL, "scatter_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "scatter_quant: pointers must be 16-byte aligned");
-  scatter_quant_kernel<<<quant_grid(T, D), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), pos, indices, scales,
+  scatter_quant_kernel<<<quant_grid(T, D), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), pos, indices, scales,
                                                          T, D, K, static_cast<uint8_t*>(xq));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -565,11 +565,11 @@ int launch_requant(const void* h, const int32_t* row_expert, const float* scales
   BWMOE_REQUIRE(h && row_expert && scales_h && hq, BWMOE_ERR_NULL, "requant: null pointer");
   BWMOE_REQUIRE(aligned16(h) && aligned16(hq), BWMOE_ERR_BAD_ALIGN, "requant: pointers must be 16-byte aligned");
   if (scales_from_amax_out != nullptr)   // scales_h holds the segment amax; scales are derived and published
-    quant_rows_kernel<false, true><<<quant_grid(M, H), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
+    quant_rows_kernel<false, true><<<quant_grid(M, H), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
                                                                      row_expert, scales_h, scales_from_amax_out, M, H, 1,
                                                                      static_cast<uint8_t*>(hq));
   else
-    quant_rows_kernel<false, false><<<quant_grid(M, H), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
+    quant_rows_kernel<false, false><<<quant_grid(M, H), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
                                                                       row_expert, scales_h, nullptr, M, H, 1,
                                                                       static_cast<uint8_t*>(hq));
   BWMOE_CUDA_OK(cudaGetLastError());
@@ -595,7 +595,7 @@ dense_prepare_kernel(const float* __restrict__ row_amax, int T, int32_t* __restr
 }
 
 int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* seg_amax, cudaStream_t st) {
-  dense_prepare_kernel<<<1, 1024, 0, st>>>(row_amax, T, offsets, seg_amax);
+  dense_prepare_kernel<<<1, 1024, 0, counted(st)>>>(row_amax, T, offsets, seg_amax);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -603,7 +603,7 @@ int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* 
 // rows in place (no gather), scale derived from the segment amax and published
 int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
                                 void* xq, float* scales_out, cudaStream_t st) {
-  quant_rows_kernel<false, true><<<quant_grid(M, W), 256, 0, st>>>(
+  quant_rows_kernel<false, true><<<quant_grid(M, W), 256, 0, counted(st)>>>(
       static_cast<const __nv_bfloat16*>(x), nullptr, row_expert, seg_amax, scales_out, M, W, 1,
       static_cast<uint8_t*>(xq));
   BWMOE_CUDA_OK(cudaGetLastError());
@@ -616,7 +616,7 @@ int launch_combine(const void* y, const int32_t* pos, const float* weights, int 
   BWMOE_REQUIRE(y && pos && weights && out, BWMOE_ERR_NULL, "combine: null pointer");
   BWMOE_REQUIRE(aligned16(y) && aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine: pointers must be 16-byte aligned");
   const size_t n = (size_t)T * (D / 8);
-  combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(y), pos,
+  combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(y), pos,
                                                               weights, T, D, K,
                                                               static_cast<__nv_bfloat16*>(out), scale,
                                                               static_cast<const __nv_bfloat16*>(residual));
@@ -637,7 +637,7 @@ int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t*
     pp.p[r] = dst[r];
   }
   BWMOE_REQUIRE(aligned16(x), BWMOE_ERR_BAD_ALIGN, "scatter_quant_peers: x must be 16-byte aligned");
-  scatter_quant_peers_kernel<<<quant_grid(T, D), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), pos, indices,
+  scatter_quant_peers_kernel<<<quant_grid(T, D), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), pos, indices,
                                                                scales, delta, T, D, K, experts_per_rank, pp);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -657,7 +657,7 @@ int launch_combine_peers(void* const* src, int n_ranks, const int32_t* pos, cons
   }
   BWMOE_REQUIRE(aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine_peers: out must be 16-byte aligned");
   const size_t n = (size_t)T * (D / 8);
-  combine_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(pp, pos, indices, weights, delta, experts_per_rank,
+  combine_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(pp, pos, indices, weights, delta, experts_per_rank,
                                                                     T, D, K, static_cast<__nv_bfloat16*>(out));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
@@ -669,7 +669,7 @@ int launch_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, i
                 BWMOE_ERR_BAD_SHAPE, "ep_maps: ranks=%d E=%d rank=%d", n_ranks, E, rank);
   BWMOE_REQUIRE(counts && offsets && delta && offsets_local && home_counts && home_first, BWMOE_ERR_NULL,
                 "ep_maps: null pointer");
-  ep_maps_kernel<<<1, 256, 0, st>>>(counts, offsets, n_ranks, E, rank, delta, offsets_local, home_counts, home_first);
+  ep_maps_kernel<<<1, 256, 0, counted(st)>>>(counts, offsets, n_ranks, E, rank, delta, offsets_local, home_counts, home_first);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

@@ -645,7 +645,7 @@ router_fallback_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 int launch_router_fallback(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
                            int32_t* indices, const int32_t* list, const int32_t* count, cudaStream_t st) {
   (void)T;
-  router_fallback_kernel<<<64, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+  router_fallback_kernel<<<64, 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x),
                                              static_cast<const __nv_bfloat16*>(wg), D, E, K, weights, indices, list,
                                              count);
   BWMOE_CUDA_OK(cudaGetLastError());
@@ -673,17 +673,17 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
   const bool vec_gate = (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) & 15u) == 0);
   const bool vec_x = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
   if (vec_gate && vec_x && E <= 16 && T >= 1024) {
-    router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, st>>>(xp, wp, T, D, E, K, weights,
+    router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, counted(st)>>>(xp, wp, T, D, E, K, weights,
                                                                                  indices, row_amax);
   } else if (vec_gate && T < 1024) {
     const int threads = (E >= 128 || T <= 64) ? 1024 : 256;   // few tokens: spread each row over more threads
-    router_token_kernel<<<T, threads, 0, st>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
+    router_token_kernel<<<T, threads, 0, counted(st)>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
   } else if (T >= 2048) {
     constexpr int TOK = 16;
-    router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, st>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
+    router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, counted(st)>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
   } else {
     constexpr int TOK = 4;
-    router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, st>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
+    router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, counted(st)>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
   }
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;

@@ -428,7 +428,7 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   auto* fb_list = reinterpret_cast<int32_t*>(base + L.fb_list);
   BWMOE_CUDA_OK(cudaMemsetAsync(base, 0, L.wgt, st));        // column norms, fallback counter, private status word
   if (status == nullptr) status = fb_count + 1;
-  transpose_gate_kernel<<<dim3(ceil_div(D, 32), ceil_div(E, 32)), 256, 0, st>>>(
+  transpose_gate_kernel<<<dim3(ceil_div(D, 32), ceil_div(E, 32)), 256, 0, counted(st)>>>(
       static_cast<const __nv_bfloat16*>(wg), D, E, wgt, wnorm2);
   BWMOE_CUDA_OK(cudaGetLastError());
 
@@ -439,21 +439,21 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   BWMOE_CUDA_OK(ensure_dynamic_smem(tc_logits_kernel, R_SMEM_BYTES, smem_set));
   TcParams p{logits, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16};
   const int grid = std::min(sm_count(), ceil_div(T, BM));
-  tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, st>>>(mx, mw, p);
+  tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, counted(st)>>>(mx, mw, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   auto xb = static_cast<const __nv_bfloat16*>(x);
   const unsigned rgrid = (unsigned)ceil_div(T, 8);
   if (E <= 32)
-    refine_kernel<1><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+    refine_kernel<1><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
                                             fb_count, fb_list);
   else if (E <= 64)
-    refine_kernel<2><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+    refine_kernel<2><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
                                             fb_count, fb_list);
   else if (E <= 128)
-    refine_kernel<4><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+    refine_kernel<4><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
                                             fb_count, fb_list);
   else
-    refine_kernel<8><<<rgrid, 256, 0, st>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+    refine_kernel<8><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
                                             fb_count, fb_list);
   BWMOE_CUDA_OK(cudaGetLastError());
   return launch_router_fallback(x, wg, T, D, E, K, weights, indices, fb_list, fb_count, st);

@@ -1,11 +1,13 @@
 """nn.Module drop-ins that sit either side of the MoE-block forward.
 
-They mirror, attribute for attribute, the modules the reference installs into
-Hugging Face models - ``FP8SharedExpert`` / ``patch_shared_experts``
-(src/blackwell_moe/runtime/shared_expert_fp8.py:33-81), ``FP8MoELayer`` /
-``patch_deepseek_moe_with_store`` (src/blackwell_moe/runtime/deepseek_patch.py:15-73)
-and the ``(out, zeros(1))`` contract of the Mixtral block
-(src/blackwell_moe/runtime/mixtral_patch.py:39-48) - but run on libbwmoe.
+Drop-in replacements must keep the attribute names, buffer names and the lookup of the patched
+modules by class-name string, so the following parts FOLLOW THE REFERENCE LINE FOR LINE:
+``FP8SharedExpert.__init__`` and ``patch_shared_experts``
+(src/blackwell_moe/runtime/shared_expert_fp8.py:36-55,71-81), ``FP8MoELayer.__init__`` and
+``patch_deepseek_moe_with_store`` (src/blackwell_moe/runtime/deepseek_patch.py:15-37,56-73).
+Everything that computes is new and runs on libbwmoe: the ``forward`` methods, ``fp8_dense_mlp``,
+and ``FP8MixtralSparseMoeBlock`` (which keeps only the ``(out, zeros(1))`` return contract of
+src/blackwell_moe/runtime/mixtral_patch.py:39-48).
 """
 
 from __future__ import annotations
@@ -108,21 +110,9 @@ class FP8MoELayer(nn.Module):
         shape = hidden_states.shape
         x = hidden_states.reshape(-1, self.hidden_dim).to(torch.bfloat16).contiguous()
         shared_out = self.shared_experts(hidden_states).reshape(-1, self.hidden_dim).to(torch.bfloat16).contiguous()
-        T, D = x.shape
-        E, _, H = self.experts_w_gate_fp8.shape
-        dev = x.device
-        lib = _lib.lib()
-        with torch.cuda.device(dev):
-            need = lib.bwmoe_workspace_bytes(T, D, H, E, self.top_k)
-            if need == 0:
-                raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E} top_k={self.top_k}")
-            ws = _workspace(dev, need)
-            out = torch.empty_like(x)
-            ts = (x, self.w_router, self.experts_w_gate_fp8, self.experts_w_up_fp8, self.experts_w_down_fp8,
-                  self.scales_gate, self.scales_up, self.scales_down)
-            _lib.check(lib.bwmoe_moe_forward_ex(*[t.data_ptr() for t in ts], T, D, H, E, self.top_k,
-                                                float(self.routed_scale), shared_out.data_ptr(), out.data_ptr(),
-                                                ws.data_ptr(), ws.numel(), _stream(dev)))
+        out = fp8_moe_forward(x, self.w_router, self.experts_w_gate_fp8, self.experts_w_up_fp8,
+                              self.experts_w_down_fp8, self.scales_gate, self.scales_up, self.scales_down,
+                              top_k=self.top_k, routed_scale=float(self.routed_scale), residual=shared_out)
         return out.reshape(shape)
 
 

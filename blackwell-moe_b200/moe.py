@@ -98,7 +98,8 @@ def _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate,
 
 
 def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
-                    scales_gate, scales_up, scales_down, top_k: int = 8) -> torch.Tensor:
+                    scales_gate, scales_up, scales_down, top_k: int = 8, *,
+                    routed_scale: float = 1.0, residual=None) -> torch.Tensor:
     """FP8 MoE-block forward: ``x[T,D] bf16 -> out[T,D] bf16``.
 
     ``scales_*`` of shape ``[E]`` select the reference's per-tensor recipe (forward
@@ -108,7 +109,12 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
     ``x`` on the GPU: everything stays on the device and the result is a new
     CUDA tensor.  ``x`` in (pinned) host memory: the library copies it in,
     runs the block and copies the result back into a new pinned host tensor
-    (weights must still be CUDA tensors)."""
+    (weights must still be CUDA tensors).
+
+    Keyword-only extras (per-tensor recipe, device activations): ``routed_scale`` and
+    ``residual[T,D] bf16`` fuse the tail of the reference's DeepSeek layer into the combine,
+    ``out = bf16(bf16(routed * routed_scale) + residual)``
+    (src/blackwell_moe/runtime/deepseek_patch.py:51-53)."""
     T, D, H, E = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down,
                                 scales_gate, scales_up, scales_down)
     assert w_gate.shape == (D, E) and w_gate.dtype == torch.bfloat16, (w_gate.shape, w_gate.dtype)
@@ -119,6 +125,9 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
     x = _contig(x, "x")
     with torch.cuda.device(dev):
         ptrs = [t.data_ptr() for t in weights]
+        if routed_scale != 1.0 or residual is not None:
+            if scales_gate.dim() == 3 or not x.is_cuda:
+                raise ValueError("routed_scale / residual are available for the per-tensor recipe on device activations")
         if scales_gate.dim() == 3:
             host_x = not x.is_cuda
             if host_x:      # host activations: copy in, run, copy out and wait (pinned memory makes the copies async)
@@ -145,6 +154,15 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
                                  "(D and H must be multiples of 16, E <= 256, top_k <= min(E, 32))")
             ws = _workspace(dev, need)
             out = torch.empty_like(x)
+            if routed_scale != 1.0 or residual is not None:
+                if residual is not None:
+                    assert residual.shape == x.shape and residual.dtype == torch.bfloat16, (residual.shape, residual.dtype)
+                    residual = _contig(residual, "residual")
+                    _require_cuda(x, residual)
+                _lib.check(lib.bwmoe_moe_forward_ex(x.data_ptr(), *ptrs, T, D, H, E, top_k, float(routed_scale),
+                                                    residual.data_ptr() if residual is not None else None,
+                                                    out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)))
+                return out
             _lib.check(lib.bwmoe_moe_forward(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
                                              ws.data_ptr(), ws.numel(), _stream(dev)))
             return out

@@ -80,6 +80,11 @@ int bwmoe_version(void);
  * No counterpart in the reference (it is single-GPU). */
 int bwmoe_set_sm_reserve(int n);
 
+/* Number of kernels the library has launched in this process so far (all threads, all devices).
+ * For benchmarks that report how many of the library's kernels ran inside a timed region.
+ * No counterpart in the reference. */
+long long bwmoe_launch_count(void);
+
 /* Copies the calling thread's last error message (NUL-terminated, truncated to
  * `len`) and returns its length. */
 int bwmoe_last_error(char* buf, size_t len);
