@@ -6,8 +6,11 @@ import ctypes as C
 import threading
 from pathlib import Path
 
+import os
+
 _HERE = Path(__file__).resolve().parent
-_LIB_PATH = _HERE / "libbwmoe.so"
+# BWMOE_LIBRARY selects another build of the same library (A/B timing of kernel variants)
+_LIB_PATH = Path(os.environ["BWMOE_LIBRARY"]) if os.environ.get("BWMOE_LIBRARY") else _HERE / "libbwmoe.so"
 _lock = threading.Lock()
 _lib = None
 

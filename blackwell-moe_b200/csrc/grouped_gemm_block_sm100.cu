@@ -15,8 +15,15 @@
 //             (a tile's 128 h columns are exactly one group) - no bf16 intermediate is written
 //   DOWN    : y = bf16(acc)
 //
-// CTA = 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue (two warps per
-// tensor-memory lane quarter; each thread owns one row and 2 x 64 accumulator columns).
+// CTA = 384 threads in three warpgroups: warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle),
+// warps 4..11 fold + epilogue (two warps per tensor-memory lane quarter; each thread owns one row
+// and 2 x 64 accumulator columns).  The first warpgroup hands most of its registers to the other
+// two (setmaxnreg), so that a fold thread can hold its 128 fp32 accumulators and 64 words of
+// tensor-memory loads in flight without spilling.
+// The scales never stall the fold: a row's activation scales for the NEXT tile are copied into
+// shared memory with cp.async while the current tile is folded (three buffers, so that the copy
+// never lands in a buffer the partner warp of the same rows may still read), and the per-K-block
+// weight scales of a tile sit in registers, one K block per lane, broadcast by a shuffle.
 // Every barrier wait is bounded exactly as in the per-tensor kernel.
 #include "sm100_gemm.cuh"
 
@@ -24,8 +31,33 @@ namespace bwmoe {
 namespace {
 using namespace sm100;
 
-constexpr int NUM_THREADS_BLK = 320;
+constexpr int NUM_THREADS_BLK = 384;      // 3 warpgroups: {TMA, MMA, 2 idle}, 2 x 4 fold warps
+constexpr int FOLD_WARP0 = 4;             // first fold warp
+constexpr int REGS_SMALL = 40;            // per thread after setmaxnreg: first warpgroup
+constexpr int REGS_FOLD = 232;            //                              fold warpgroups  (128*40 + 256*232 = 384*168)
+constexpr int SCALE_KB_MAX = 16;          // K blocks whose activation scales the shared-memory staging holds
 constexpr float kGroupAmaxFloor = 1e-4f;
+
+__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// two fp32 -> bf16 (round to nearest even) -> back to fp32, with one packed conversion
+__device__ __forceinline__ void bf16_round2(float& a, float& b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  a = __uint_as_float(r << 16);
+  b = __uint_as_float(r & 0xffff0000u);
+}
+// four fp32 -> four E4M3 codes; the conversion saturates at +-448, which is the clamp of the recipe
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
 
 struct BlockGemmParams {
   const int32_t* offsets;   // [E+1]
@@ -45,7 +77,7 @@ struct BlockGemmParams {
 
 struct Cursor {
   const int* cum;
-  const int32_t* offsets;
+  const int* offsets;     // shared-memory copy of the segment offsets
   int E, n_tiles, e;
   __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx) {
     while (e < E && tile >= cum[e + 1]) ++e;
@@ -85,24 +117,29 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   const __grid_constant__ CUtensorMap map_b1, const BlockGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_cum[257];
+  __shared__ int s_off[257];              // segment offsets: every role looks tiles up without touching global memory
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_amax[2][2][BM];     // [tile parity][column half][row]
   __shared__ int s_seq[2][BM];           // tiles whose amax each (half, row) thread has published
+  __shared__ float s_ainv[3][SCALE_KB_MAX][BM];   // [tile % 3][K block][row] activation scales of a tile's rows
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
   const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
-  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  // accumulator barriers: [K-block parity][column half]; gate/up tiles use the first of each pair for the whole buffer
+  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &s_abort;
 
   for (int e = threadIdx.x; e < 256; e += NUM_THREADS_BLK) {
     int t = 0;
     if (e < p.E) {
-      const int rows = p.offsets[e + 1] - p.offsets[e];
-      t = ((rows + BM - 1) / BM) * p.n_tiles;
+      const int o0 = p.offsets[e], o1 = p.offsets[e + 1];
+      t = ((o1 - o0 + BM - 1) / BM) * p.n_tiles;
+      s_off[e] = o0;
+      if (e == p.E - 1) s_off[p.E] = o1;
     }
     s_cum[e + 1] = t;
   }
@@ -113,9 +150,11 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 4; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, 8);      // one arrival per epilogue warp
+      // one arrival per fold warp that reads the (half-)buffer: all eight for a gate/up buffer, the four
+      // warps that own the column half for a down half-buffer
+      mbar_init(bar_tempty + 8 * b, GATE_UP ? 8 : 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -145,10 +184,14 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int total_tiles = s_cum[p.E];
   const int k_blocks = p.k_blocks;
 
+  // Register hand-over between the warpgroups: every warp of a warpgroup executes its instruction, and
+  // each does so at the top of its own branch (after a common point the compiler would have to assume
+  // the smaller budget for everything that follows).
   if (warp == 0) {
     // ===================== TMA producer =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));
     if (lane == 0) {
-      Cursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+      Cursor cur{s_cum, s_off, p.E, p.n_tiles, 0};
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -171,64 +214,134 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer: one fresh accumulator per K block =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t buf = it & 1u, use = it >> 1;
-          if (!(ok = mbar_wait_spin(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
-          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + buf * BN;
-          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
-          const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES);
+          if constexpr (GATE_UP) {
+            // one 256-column accumulator per K block (every fold thread needs gate and up of its columns)
+            if (!(ok = mbar_wait_spin(bar_tempty + 16 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
+            if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+            const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k)
-            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, k > 0 ? 1u : 0u);
+            for (int k = 0; k < BK / 32; ++k)
+              mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, k > 0 ? 1u : 0u);
+            mma_commit(bar_tfull + 16 * buf);
+          } else {
+            // Down tiles: the K block is issued as two 128-column halves, each into its own half-buffer with its
+            // own "full" signal.  A fold warp reads one half only, so a half-buffer is recycled as soon as its
+            // four readers are done and the fold of the first half runs while the tensor pipe works on the
+            // second (measured 8 % faster than whole buffers here; for gate/up tiles, where every warp needs
+            // both halves, the extra barrier round per K block cost more than it gave).
+            for (uint32_t h = 0; ok && h < 2; ++h) {
+              const uint32_t hb = buf * 2 + h;
+              if (!(ok = mbar_wait_spin(bar_tempty + 8 * hb, (use & 1u) ^ 1u, abort_flag, p.status))) break;
+              if (h == 0 && !(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
+              tc_fence_after();
+              const uint32_t d_tmem = tmem_base + buf * BN + h * BN_HALF;
+              const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+              const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES + h * B_HALF_BYTES);
+#pragma unroll
+              for (int k = 0; k < BK / 32; ++k)
+                mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC_HALF, k > 0 ? 1u : 0u);
+              mma_commit(bar_tfull + 8 * hb);
+            }
+          }
+          if (!ok) break;
           mma_commit(bar_empty + 8 * stage);
-          mma_commit(bar_tfull + 8 * buf);
           if (++stage == STAGES) stage = 0, phase ^= 1u;
         }
       }
     }
     __syncwarp();
+  } else if (warp < FOLD_WARP0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));     // idle warps of the first warpgroup
   } else {
-    // ===================== epilogue: fold K blocks into registers, then finish the tile =====================
+    // ===================== fold K blocks into registers, then finish the tile =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_FOLD));
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                 // which 2 x 64 columns this warp owns
+    const int half = (warp - FOLD_WARP0) >> 2;        // which 2 x 64 columns this warp owns
     const int r_in_tile = quarter * 32 + lane;
     // accumulator column offsets of this thread's two 64-column chunks
     const int colA = GATE_UP ? half * 64 : half * 128;
     const int colB = GATE_UP ? BN_HALF + half * 64 : half * 128 + 64;
-    Cursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+    Cursor cur{s_cum, s_off, p.E, p.n_tiles, 0};
+    Cursor ahead{s_cum, s_off, p.E, p.n_tiles, 0};
     uint32_t it = 0, local = 0;
     bool ok = true;
+    // Scales staged ahead of the fold when the K loop has 3..16 blocks (with fewer, a fast warp could run two
+    // tiles ahead of its partner and overwrite a buffer still in use; with more, the staging does not fit).
+    const bool staged = k_blocks >= 3 && k_blocks <= SCALE_KB_MAX;
+    const uint32_t ainv_s = smem_u32(&s_ainv[0][0][0]);
+    // a tile's scales of row `r_in_tile` -> s_ainv[buf][kb][r_in_tile]; rows past the segment take the first row's
+    auto stage_row_scales = [&](uint32_t buf, int row0, int row_end) {
+      const int row = row0 + r_in_tile;
+      const float* src = p.a_inv + (size_t)(row < row_end ? row : row0) * k_blocks;
+      const uint32_t dst = ainv_s + (uint32_t)((buf * SCALE_KB_MAX) * BM + r_in_tile) * 4u;
+      for (int kb = 0; kb < k_blocks; ++kb) cp_async4(dst + (uint32_t)(kb * BM) * 4u, src + kb);
+    };
+    // weight scales of a tile: lane kb holds K block kb's (k_blocks <= 32)
+    auto load_w_scales = [&](int e, int n_idx, float& wa, float& wb) {
+      const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
+      const int nbA = GATE_UP ? n_idx : min(n0 / 128 + half, p.nb - 1);
+      const size_t at = ((size_t)e * k_blocks + min(lane, k_blocks - 1)) * p.nb + nbA;
+      wa = p.w0_inv[at];
+      wb = GATE_UP ? p.w1_inv[at] : wa;
+    };
+    float wA_nx_reg = 0.f, wB_nx_reg = 0.f;
+    if (staged && (int)blockIdx.x < total_tiles) {
+      int e, row0, row_end, n_idx;
+      if (ahead.locate(blockIdx.x, e, row0, row_end, n_idx)) {
+        stage_row_scales(0u, row0, row_end);
+        load_w_scales(e, n_idx, wA_nx_reg, wB_nx_reg);
+      }
+      cp_async_commit();
+    }
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
       int e, row0, row_end, n_idx;
       if (!cur.locate(tile, e, row0, row_end, n_idx)) break;
       const int row = row0 + r_in_tile;
       const bool row_ok = row < row_end;
       const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
-      // weight-scale block column of each chunk
-      const int nbA = GATE_UP ? n_idx : min(n0 / 128 + half, p.nb - 1);
-      const float* wA = p.w0_inv + (size_t)e * k_blocks * p.nb + nbA;
-      const float* wB = GATE_UP ? p.w1_inv + (size_t)e * k_blocks * p.nb + nbA : wA;
-      const float* ai = p.a_inv + (size_t)(row_ok ? row : row0) * k_blocks;
+      const float wA_reg = wA_nx_reg, wB_reg = wB_nx_reg;
+      const float* sa_row = &s_ainv[local % 3u][0][r_in_tile];
+      if (staged) {
+        // the next tile's scales travel while this tile is folded
+        int e2, r2, re2, n2;
+        if (tile + (int)gridDim.x < total_tiles && ahead.locate(tile + gridDim.x, e2, r2, re2, n2)) {
+          stage_row_scales((local + 1u) % 3u, r2, re2);
+          load_w_scales(e2, n2, wA_nx_reg, wB_nx_reg);
+        }
+        cp_async_commit();
+        cp_async_wait_but_one();           // everything but the group just committed has landed: this tile's scales
+      }
       unsigned long long accA2[32], accB2[32];      // 2 x 64 fp32 accumulators, packed in pairs
 #pragma unroll
       for (int j = 0; j < 32; ++j) accA2[j] = 0ull, accB2[j] = 0ull;
-      // scales of the next K block are fetched while the current one is folded in
-      float a_nx = ai[0], wA_nx = wA[0], wB_nx = wB[0];
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const uint32_t buf = it & 1u, use = it >> 1;
-        const float sA = a_nx * wA_nx, sB = a_nx * wB_nx;
-        if (kb + 1 < k_blocks) {
-          a_nx = ai[kb + 1];
-          wA_nx = wA[(size_t)(kb + 1) * p.nb];
-          wB_nx = wB[(size_t)(kb + 1) * p.nb];
+        float sA, sB;
+        if (staged) {
+          const float a = sa_row[kb * BM];
+          sA = a * __shfl_sync(0xffffffffu, wA_reg, kb);
+          sB = a * __shfl_sync(0xffffffffu, wB_reg, kb);
+        } else {
+          // weight-scale block column of each chunk
+          const int nbA = GATE_UP ? n_idx : min(n0 / 128 + half, p.nb - 1);
+          const size_t at = ((size_t)e * k_blocks + kb) * p.nb + nbA;
+          const float a = p.a_inv[(size_t)(row_ok ? row : row0) * k_blocks + kb];
+          sA = a * p.w0_inv[at];
+          sB = GATE_UP ? a * p.w1_inv[at] : sA;
         }
-        ok = mbar_wait_spin(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
+        // barrier pair of this warp's columns: the whole buffer (gate/up), or the half that holds them (down)
+        const uint32_t hbA = buf * 2 + (GATE_UP ? 0u : (uint32_t)half);
+        ok = mbar_wait_spin(bar_tfull + 8 * hbA, use & 1u, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -259,7 +372,7 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * hbA);
       }
       if (!ok) break;
       float accA[64], accB[64];
@@ -273,11 +386,16 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // h for this thread's 64 columns; the row's group amax needs the other half too
         float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float gate = bf16_round(accA[j]);
-          const float up = bf16_round(accB[j]);
-          accA[j] = bf16_round(bf16_round(silu_f(gate)) * up);
-          amax = fmaxf(amax, fabsf(accA[j]));
+        for (int j = 0; j < 64; j += 2) {
+          float g0 = accA[j], g1 = accA[j + 1], u0 = accB[j], u1 = accB[j + 1];
+          bf16_round2(g0, g1);                       // the reference's rounding points: gate, up,
+          bf16_round2(u0, u1);
+          float a0 = silu_f(g0), a1 = silu_f(g1);
+          bf16_round2(a0, a1);                       // silu(gate),
+          a0 *= u0, a1 *= u1;
+          bf16_round2(a0, a1);                       // and the product
+          accA[j] = a0, accA[j + 1] = a1;
+          amax = fmaxf(amax, fmaxf(fabsf(a0), fabsf(a1)));
         }
         // publish this half's maximum, then wait (bounded) for the thread that owns the other half of
         // the row.  The parity buffer cannot be overwritten early: its owner reaches tile local+2 only
@@ -317,8 +435,7 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const int j = v * 16 + q * 4;
-                w[q] = (uint32_t)to_e4m3x2(accA[j] * s, accA[j + 1] * s) |
-                       ((uint32_t)to_e4m3x2(accA[j + 2] * s, accA[j + 3] * s) << 16);
+                w[q] = e4m3x4(accA[j] * s, accA[j + 1] * s, accA[j + 2] * s, accA[j + 3] * s);
               }
               reinterpret_cast<uint4*>(dst)[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -329,7 +446,7 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // where this lane's row goes: the local result buffer, or the row's place on its home rank
         __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.N_out;
         if (p.n_home > 0 && row_ok) {
-          int j = row - p.offsets[e], s = 0;
+          int j = row - s_off[e], s = 0;
           for (; s < p.n_home - 1; ++s) {
             const int c = p.home_counts[s * p.E + e];
             if (j < c) break;
@@ -363,6 +480,7 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
       }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");     // no copy into the scale staging may outlive the CTA
   }
 
   if (*abort_flag) {

@@ -32,6 +32,10 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 constexpr uint32_t IDESC = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) |
                            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
+// the same with N = 128 (one weight box)
+constexpr uint32_t IDESC_HALF = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) |
+                                ((uint32_t)(BN_HALF >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
