@@ -70,8 +70,9 @@ SIGNATURES = {
     "bwmoe_down_peers": (_i, [_vp, _ip, _fp, _vp, _fp, _i, _i, _i, _i, _ip, _ip, C.POINTER(C.c_void_p), _i, _ip, _vp]),
     "bwmoe_down_block_peers": (_i, [_vp, _fp, _ip, _vp, _fp, _i, _i, _i, _i, _ip, _ip, C.POINTER(C.c_void_p), _i, _ip, _vp]),
     "bwmoe_scatter_rows_group_peers": (_i, [_vp, _fp, _ip, _ip, _ip, _i, _i, _i, _i, C.POINTER(C.c_void_p),
-                                           C.POINTER(C.c_void_p), _i, _vp]),
-    "bwmoe_scatter_quant_peers": (_i, [_vp, _ip, _ip, _fp, _ip, _i, _i, _i, _i, C.POINTER(C.c_void_p), _i, _vp]),
+                                           C.POINTER(C.c_void_p), _i, _i, _ip, _vp]),
+    "bwmoe_scatter_quant_peers": (_i, [_vp, _ip, _ip, _fp, _ip, _i, _i, _i, _i, C.POINTER(C.c_void_p), _i, _i, _ip,
+                                       _vp]),
     "bwmoe_combine_peers": (_i, [C.POINTER(C.c_void_p), _i, _ip, _ip, _fp, _ip, _i, _i, _i, _i, _vp, _vp]),
 }
 

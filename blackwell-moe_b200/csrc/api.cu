@@ -639,9 +639,10 @@ int bwmoe_down_block_peers(const void* hq, const float* h_inv, const int32_t* of
 
 int bwmoe_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos, const int32_t* indices,
                                    const int32_t* delta, int T, int D, int K, int experts_per_rank,
-                                   void* const* xq_of_rank, void* const* inv_of_rank, int n_ranks, void* stream) {
+                                   void* const* xq_of_rank, void* const* inv_of_rank, int n_ranks, int rows_cap,
+                                   int32_t* status, void* stream) {
   return launch_scatter_rows_group_peers(xq_tok, inv_tok, pos, indices, delta, T, D, K, experts_per_rank, xq_of_rank,
-                                         inv_of_rank, n_ranks, static_cast<cudaStream_t>(stream));
+                                         inv_of_rank, n_ranks, rows_cap, status, static_cast<cudaStream_t>(stream));
 }
 
 int bwmoe_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, int E, int rank, int32_t* delta,
@@ -652,9 +653,9 @@ int bwmoe_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, in
 
 int bwmoe_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                               const int32_t* delta, int T, int D, int K, int experts_per_rank,
-                              void* const* dst_of_rank, int n_ranks, void* stream) {
+                              void* const* dst_of_rank, int n_ranks, int rows_cap, int32_t* status, void* stream) {
   return launch_scatter_quant_peers(x, pos, indices, scales, delta, T, D, K, experts_per_rank, dst_of_rank, n_ranks,
-                                    static_cast<cudaStream_t>(stream));
+                                    rows_cap, status, static_cast<cudaStream_t>(stream));
 }
 
 int bwmoe_combine_peers(void* const* y_of_rank, int n_ranks, const int32_t* pos, const int32_t* indices,

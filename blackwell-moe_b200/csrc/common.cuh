@@ -108,7 +108,7 @@ int launch_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, i
                    int32_t* offsets_local, int32_t* home_counts, int32_t* home_first, cudaStream_t st);
 int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                                const int32_t* delta, int T, int D, int K, int experts_per_rank, void* const* dst,
-                               int n_ranks, cudaStream_t st);
+                               int n_ranks, int rows_cap, int32_t* status, cudaStream_t st);
 int launch_combine_peers(void* const* src, int n_ranks, const int32_t* pos, const int32_t* indices,
                          const float* weights, const int32_t* delta, int experts_per_rank, int T, int D, int K,
                          void* out, cudaStream_t st);
@@ -168,6 +168,6 @@ int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets
 int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos,
                                     const int32_t* indices, const int32_t* delta, int T, int D, int K,
                                     int experts_per_rank, void* const* xq_of_rank, void* const* inv_of_rank,
-                                    int n_ranks, cudaStream_t st);
+                                    int n_ranks, int rows_cap, int32_t* status, cudaStream_t st);
 
 }  // namespace bwmoe

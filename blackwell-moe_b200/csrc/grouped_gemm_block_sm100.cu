@@ -572,7 +572,8 @@ __global__ void __launch_bounds__(256)
 scatter_quantised_rows_peers_kernel(const uint8_t* __restrict__ xq_tok, const float* __restrict__ inv_tok,
                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ indices,
                                     const int32_t* __restrict__ delta, unsigned T, unsigned D, int K, int groups,
-                                    int experts_per_rank, const PeerPtrs xq_dst, const PeerPtrs inv_dst) {
+                                    int experts_per_rank, const PeerPtrs xq_dst, const PeerPtrs inv_dst, int rows_cap,
+                                    int32_t* __restrict__ status) {
   const unsigned vec_per_row = D / 16;
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= T * vec_per_row) return;
@@ -585,7 +586,12 @@ scatter_quantised_rows_peers_kernel(const uint8_t* __restrict__ xq_tok, const fl
     if (row < 0) continue;
     const int e = indices[(size_t)t * K + k];
     const int r = e / experts_per_rank;
-    const size_t dst_row = (size_t)(row + delta[e]);
+    const int dr = row + delta[e];
+    if (dr < 0 || dr >= rows_cap) {                // the owner's buffer is smaller than what the ranks send it
+      if (v == 0 && status != nullptr) atomicOr(status, BWMOE_STATUS_EP_OVERFLOW);
+      continue;
+    }
+    const size_t dst_row = (size_t)dr;
     reinterpret_cast<uint4*>(static_cast<uint8_t*>(xq_dst.p[r]) + dst_row * D)[v] = codes;
     if (v < (unsigned)groups) static_cast<float*>(inv_dst.p[r])[dst_row * groups + v] = inv;
   }
@@ -678,7 +684,7 @@ int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets
 int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, const int32_t* pos,
                                     const int32_t* indices, const int32_t* delta, int T, int D, int K,
                                     int experts_per_rank, void* const* xq_of_rank, void* const* inv_of_rank,
-                                    int n_ranks, cudaStream_t st) {
+                                    int n_ranks, int rows_cap, int32_t* status, cudaStream_t st) {
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_rows_group_peers: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers && experts_per_rank >= 1, BWMOE_ERR_UNSUPPORTED,
                 "scatter_rows_group_peers: %d ranks (at most %d)", n_ranks, kMaxPeers);
@@ -695,7 +701,8 @@ int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, co
   }
   const size_t n = (size_t)T * (D / 16);
   scatter_quantised_rows_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
-      static_cast<const uint8_t*>(xq_tok), inv_tok, pos, indices, delta, T, D, K, groups, experts_per_rank, px, pi);
+      static_cast<const uint8_t*>(xq_tok), inv_tok, pos, indices, delta, T, D, K, groups, experts_per_rank, px, pi,
+      rows_cap, status);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(256)
 scatter_quant_peers_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos,
                            const int32_t* __restrict__ indices, const float* __restrict__ scales,
                            const int32_t* __restrict__ delta, unsigned T, unsigned W, int K, int experts_per_rank,
-                           const PeerPtrs dst) {
+                           const PeerPtrs dst, int rows_cap, int32_t* __restrict__ status) {
   const unsigned per_row = W / 16;
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= T * per_row) return;
@@ -342,9 +342,14 @@ scatter_quant_peers_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* _
     const int row = pos[(size_t)t * K + k];
     if (row < 0) continue;
     const int e = indices[(size_t)t * K + k];
+    const int dst_row = row + delta[e];
+    if (dst_row < 0 || dst_row >= rows_cap) {      // the owner's buffer is smaller than what the ranks send it
+      if (c == 0 && status != nullptr) atomicOr(status, BWMOE_STATUS_EP_OVERFLOW);
+      continue;
+    }
     const unsigned long long s2 = splat2(scales[e]);
     uint8_t* base = static_cast<uint8_t*>(dst.p[e / experts_per_rank]);
-    reinterpret_cast<uint4*>(base + (size_t)(row + delta[e]) * W)[c] =
+    reinterpret_cast<uint4*>(base + (size_t)dst_row * W)[c] =
         make_uint4(e4m3x4_scaled(r0.x, r0.y, s2), e4m3x4_scaled(r0.z, r0.w, s2), e4m3x4_scaled(r1.x, r1.y, s2),
                    e4m3x4_scaled(r1.z, r1.w, s2));
   }
@@ -626,11 +631,12 @@ int launch_combine(const void* y, const int32_t* pos, const float* weights, int 
 
 int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
                                const int32_t* delta, int T, int D, int K, int experts_per_rank, void* const* dst,
-                               int n_ranks, cudaStream_t st) {
+                               int n_ranks, int rows_cap, int32_t* status, cudaStream_t st) {
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_quant_peers: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers && experts_per_rank >= 1, BWMOE_ERR_UNSUPPORTED,
                 "scatter_quant_peers: %d ranks (at most %d)", n_ranks, kMaxPeers);
   BWMOE_REQUIRE(x && pos && indices && scales && delta && dst, BWMOE_ERR_NULL, "scatter_quant_peers: null pointer");
+  BWMOE_REQUIRE(rows_cap > 0, BWMOE_ERR_BAD_SHAPE, "scatter_quant_peers: rows_cap=%d", rows_cap);
   PeerPtrs pp{};
   for (int r = 0; r < n_ranks; ++r) {
     BWMOE_REQUIRE(dst[r] != nullptr && aligned16(dst[r]), BWMOE_ERR_BAD_ALIGN, "scatter_quant_peers: buffer of rank %d", r);
@@ -638,7 +644,8 @@ int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t*
   }
   BWMOE_REQUIRE(aligned16(x), BWMOE_ERR_BAD_ALIGN, "scatter_quant_peers: x must be 16-byte aligned");
   scatter_quant_peers_kernel<<<quant_grid(T, D), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), pos, indices,
-                                                               scales, delta, T, D, K, experts_per_rank, pp);
+                                                               scales, delta, T, D, K, experts_per_rank, pp, rows_cap,
+                                                               status);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

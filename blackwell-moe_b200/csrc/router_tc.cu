@@ -406,7 +406,7 @@ TcScratch tc_layout(int T, int D, int E) {
 // D <= 4096: the trust bound kTcTrust on the tensor-core logits is argued for sums of at most 4096
 // products; wider hidden sizes take the SIMT routers, whose error bound scales with D by construction.
 bool router_tc_applicable(int T, int D, int E, int K) {
-  return T >= 1024 && E >= 8 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0 && D <= 4096;
+  return (T >= 1024 || (T >= 96 && E >= 64)) && E >= 8 && E <= 256 && E % 8 == 0 && K <= 8 && K < E && D % 64 == 0 && D <= 4096;
 }
 
 size_t router_tc_scratch_bytes(int T, int D, int E) { return tc_layout(T, D, E).total; }

@@ -114,8 +114,14 @@ class ExpertParallelMoE:
     """Holds this rank's expert shard and runs the expert-parallel forward."""
 
     def __init__(self, w_gate, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down,
-                 num_experts: int, top_k: int, group=None):
+                 num_experts: int, top_k: int, group=None, max_tokens_per_rank: int = None):
+        """``max_tokens_per_rank``: the largest batch any rank will ever bring (the same value on every rank).
+        The peer-memory transport sizes its receive buffers from it, for the worst case of every row of every
+        rank landing on one rank.  Without it the ranks agree on the largest batch of their FIRST forward;
+        ranks may bring different numbers of tokens, but none may later exceed the agreed figure."""
         self.group = group
+        self.max_tokens_per_rank = max_tokens_per_rank
+        self._agreed_tokens = None
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.E, self.K = num_experts, top_k
@@ -206,10 +212,24 @@ class ExpertParallelMoE:
         self._peer = peer
         return True
 
+    def _agree_on_capacity(self, T: int) -> int:
+        """Row capacity of every rank's receive buffer, decided once by all ranks together: the largest batch
+        any rank declared (or brought to this first forward), times ranks, times top_k.  A rank never decides
+        alone to enter the collective set-up, and a later batch above the agreed size is refused before any
+        collective of that step is issued."""
+        if self._agreed_tokens is None:
+            t = torch.tensor([max(T, self.max_tokens_per_rank or 0)], dtype=torch.int64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            self._agreed_tokens = int(t.item())
+        if T > self._agreed_tokens:
+            raise ValueError(f"this rank brings {T} tokens but the ranks agreed on at most {self._agreed_tokens} per rank; "
+                             "construct ExpertParallelMoE with max_tokens_per_rank (the same value on every rank)")
+        return self.world * self._agreed_tokens * self.K
+
     def _use_peers(self, T: int) -> bool:
         if self.transport == "nccl" or self.dev.type != "cuda" or self.world > 8:
             return False
-        ok = self._peer_setup(self.world * T * self.K)       # worst case: every row of every rank lands here
+        ok = self._peer_setup(self._agree_on_capacity(T))    # worst case: every row of every rank lands here
         if not ok and self.transport == "peer":
             raise RuntimeError("transport='peer' requested but symmetric memory could not be set up")
         return ok
@@ -263,40 +283,44 @@ class ExpertParallelMoE:
         counts = new(G * E, dtype=i32)
         dist.all_gather_into_tensor(counts, (offsets[1:] - offsets[:-1]).contiguous(), group=self.group)
         counts = counts.view(G, E)
-        counts_host = counts.cpu()                                      # the step's one host synchronisation
         delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
-        R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
-        assert R <= peer["cap"], (R, peer["cap"])
+        # No host synchronisation: the number of rows this rank receives stays on the device.  The GEMMs take
+        # their tiles from the device-side segment offsets, the buffers are sized for the agreed worst case,
+        # and a row beyond it is dropped by the store kernel (status bit), never written past the buffer.
+        cap = peer["cap"]
         self._mark("counts+maps")
         peer["hx"].barrier()
         self._mark("barrier A")
         _lib.check(lib.bwmoe_scatter_rows_group_peers(xq_tok.data_ptr(), inv_tok.data_ptr(), pos.data_ptr(),
                                                       indices.data_ptr(), delta.data_ptr(), T, D, K, el,
-                                                      peer["xq_ptrs"], peer["xinv_ptrs"], G, st))
+                                                      peer["xq_ptrs"], peer["xinv_ptrs"], G, cap, status.data_ptr(), st))
         self._mark("store rows")
         peer["hx"].barrier()
         self._mark("barrier B")
-        if R > 0:
-            hq, h_inv = new(R, H, dtype=u8), new(R, nh, dtype=f32)
-            # The epilogue warps re-read a row's group scales for every K block and rely on L1 for it; loads
-            # from peer-mapped memory were measured not to get that (GEMM phase 5.0 ms against 1.9 ms), so
-            # the scales (64 bytes per row) are first copied into ordinary device memory.
-            xinv_l = peer["xinv"][:R * nd].clone()
+        if "hq" not in peer:
+            peer["hq"], peer["h_inv"] = new(cap, H, dtype=u8), new(cap, nh, dtype=f32)
+        hq, h_inv = peer["hq"], peer["h_inv"]
+        xinv_l = peer["xinv"]
+        if not 3 <= nd <= 16:
+            # The GEMM stages a tile's scales in shared memory (read once per tile) only for 3..16 K blocks;
+            # otherwise its fold warps re-read them per K block and rely on L1, which loads from peer-mapped
+            # memory were measured not to get: copy them into ordinary device memory first.
+            xinv_l = peer["xinv"].clone()
             self._mark("copy scales")
-            _lib.check(lib.bwmoe_gateup_swiglu_block(peer["xq"].data_ptr(), xinv_l.data_ptr(), offsets_l.data_ptr(),
-                                                     self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
-                                                     self.su.data_ptr(), R, D, H, el, hq.data_ptr(), h_inv.data_ptr(),
-                                                     status.data_ptr(), st))
-            self._mark("gate/up")
-            if self._push():
-                _lib.check(lib.bwmoe_down_block_peers(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
-                                                      self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
-                                                      home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"],
-                                                      G, status.data_ptr(), st))
-            else:
-                _lib.check(lib.bwmoe_down_block(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
-                                                self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
-                                                peer["y"].data_ptr(), status.data_ptr(), st))
+        _lib.check(lib.bwmoe_gateup_swiglu_block(peer["xq"].data_ptr(), xinv_l.data_ptr(), offsets_l.data_ptr(),
+                                                 self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                                 self.su.data_ptr(), cap, D, H, el, hq.data_ptr(), h_inv.data_ptr(),
+                                                 status.data_ptr(), st))
+        self._mark("gate/up")
+        if self._push():
+            _lib.check(lib.bwmoe_down_block_peers(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
+                                                  self.wd.data_ptr(), self.sd.data_ptr(), cap, D, H, el,
+                                                  home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"],
+                                                  G, status.data_ptr(), st))
+        else:
+            _lib.check(lib.bwmoe_down_block(hq.data_ptr(), h_inv.data_ptr(), offsets_l.data_ptr(),
+                                            self.wd.data_ptr(), self.sd.data_ptr(), cap, D, H, el,
+                                            peer["y"].data_ptr(), status.data_ptr(), st))
         self._mark("down")
         peer["hy"].barrier()
         self._mark("barrier C")
@@ -344,14 +368,14 @@ class ExpertParallelMoE:
         sx_local = scale_x[rank * el:(rank + 1) * el].contiguous()
         delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
         seg = offsets_l[1:] - offsets_l[:-1]
-        R = int(counts_host[:, rank * el:(rank + 1) * el].sum())
-        assert R <= peer["cap"], (R, peer["cap"])
+        R = min(int(counts_host[:, rank * el:(rank + 1) * el].sum()), peer["cap"])
         self._mark("counts+maps")
 
         peer["hx"].barrier()             # every rank is done with the previous step's buffers
         self._mark("barrier A")
         _lib.check(lib.bwmoe_scatter_quant_peers(x.data_ptr(), pos.data_ptr(), indices.data_ptr(), scale_x.data_ptr(),
-                                                 delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, st))
+                                                 delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, peer["cap"],
+                                                 status.data_ptr(), st))
         self._mark("quantise+store")
         peer["hx"].barrier()             # every row of this step has landed
         self._mark("barrier B")
@@ -496,6 +520,10 @@ class ExpertParallelMoE:
         self.last_status = status
         return self._finish(out, host_in)
 
+    def pipeline(self, max_tokens: int, depth: int = 2) -> "ExpertParallelPipeline":
+        """Streaming interface for activations in (pinned) host memory; see :class:`ExpertParallelPipeline`."""
+        return ExpertParallelPipeline(self, max_tokens, depth)
+
     def _finish(self, out, host_in):
         if host_in:
             host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
@@ -541,3 +569,60 @@ class ExpertParallelMoE:
         _lib.check(lib.bwmoe_combine(y_home.data_ptr(), pos.data_ptr(), weights.data_ptr(), T, D, K, out.data_ptr(), st))
         self.last_status = status
         return self._finish(out, host_in)
+
+
+class ExpertParallelPipeline:
+    """Expert-parallel forward for callers whose activations live in (pinned) host memory: the host->device copy
+    of batch i+1 and the device->host copy of batch i-1 run on their own streams beside the compute (and the
+    exchange) of batch i.  Every rank must submit the same number of batches in the same order (each forward is
+    a collective); numerically a batch is :meth:`ExpertParallelMoE.forward` of that batch.
+
+        pipe = ep.pipeline(max_tokens=16384)
+        t0 = pipe.submit(x0)          # returns without waiting for the GPU where the transport allows it
+        t1 = pipe.submit(x1)
+        y0 = pipe.result(t0)          # pinned host tensor, valid until its slot is reused
+    """
+
+    def __init__(self, ep: ExpertParallelMoE, max_tokens: int, depth: int = 2):
+        self.ep, self.Tmax, self.depth, self.dev = ep, max_tokens, depth, ep.dev
+        if ep.max_tokens_per_rank is None:
+            ep.max_tokens_per_rank = max_tokens
+        with torch.cuda.device(self.dev):
+            self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+            self.slots = [dict(x=torch.empty(max_tokens, ep.D, dtype=torch.bfloat16, device=self.dev),
+                               host=torch.empty(max_tokens, ep.D, dtype=torch.bfloat16, pin_memory=True), y=None,
+                               in_done=torch.cuda.Event(), cmp_done=torch.cuda.Event(), out_done=torch.cuda.Event(), T=0)
+                          for _ in range(depth)]
+        self.ticket = 0
+
+    def submit(self, x_host: torch.Tensor) -> int:
+        assert not x_host.is_cuda and x_host.dtype == torch.bfloat16 and x_host.shape[1] == self.ep.D
+        T = x_host.shape[0]
+        assert 0 < T <= self.Tmax
+        slot = self.slots[self.ticket % self.depth]
+        first_use = self.ticket < self.depth
+        with torch.cuda.device(self.dev):
+            if not first_use:
+                self.s_in.wait_event(slot["cmp_done"])        # the previous batch in this slot has been consumed
+            with torch.cuda.stream(self.s_in):
+                slot["x"][:T].copy_(x_host, non_blocking=True)
+                slot["in_done"].record(self.s_in)
+            self.s_cmp.wait_event(slot["in_done"])
+            if not first_use:
+                self.s_cmp.wait_event(slot["out_done"])       # its previous result has left the device
+            with torch.cuda.stream(self.s_cmp):
+                slot["y"] = self.ep.forward(slot["x"][:T])
+                slot["cmp_done"].record(self.s_cmp)
+            self.s_out.wait_event(slot["cmp_done"])
+            with torch.cuda.stream(self.s_out):
+                slot["host"][:T].copy_(slot["y"], non_blocking=True)
+                slot["out_done"].record(self.s_out)
+        slot["T"] = T
+        self.ticket += 1
+        return self.ticket - 1
+
+    def result(self, ticket: int) -> torch.Tensor:
+        assert self.ticket - self.depth <= ticket < self.ticket, "result no longer (or not yet) available"
+        slot = self.slots[ticket % self.depth]
+        slot["out_done"].synchronize()
+        return slot["host"][:slot["T"]]

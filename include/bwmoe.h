@@ -49,7 +49,9 @@ enum {
 /* Bits of the device status word (bwmoe_read_status). */
 enum {
   BWMOE_STATUS_WAIT_TIMEOUT = 1, /* a bounded barrier wait inside a GEMM kernel gave up */
-  BWMOE_STATUS_BAD_EXPERT = 2    /* an expert id outside [0,E) was met while planning */
+  BWMOE_STATUS_BAD_EXPERT = 2,   /* an expert id outside [0,E) was met while planning */
+  BWMOE_STATUS_EP_OVERFLOW = 4   /* expert parallel: a rank was sent more rows than its receive buffer holds;
+                                    the surplus rows were dropped, not written past the buffer */
 };
 
 /* Selectors for bwmoe_workspace_view: intermediates kept in the workspace after
@@ -367,7 +369,8 @@ int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights,
  * bwmoe_combine_peers: bwmoe_combine, reading the result row of slot (t,k) from the same place in the
  *   result buffer of the rank that owns its expert.
  * The caller orders the steps across ranks (a barrier before the stores, one after them, one before
- * the loads).  At most 8 ranks.
+ * the loads).  At most 8 ranks.  rows_cap is the row capacity of every rank's receive buffer: a row that
+ * would land beyond it is dropped and BWMOE_STATUS_EP_OVERFLOW is raised in d_status (may be null).
  */
 /*
  * Index maps of one expert-parallel step from the all-gathered row counts d_counts[n_ranks, E]
@@ -402,10 +405,11 @@ int bwmoe_down_block_peers(const void* d_hq, const float* d_h_inv, const int32_t
 int bwmoe_scatter_rows_group_peers(const void* d_xq_tok, const float* d_inv_tok, const int32_t* d_pos,
                                    const int32_t* d_indices, const int32_t* d_delta, int T, int D, int K,
                                    int experts_per_rank, void* const* h_xq_of_rank, void* const* h_inv_of_rank,
-                                   int n_ranks, void* stream);
+                                   int n_ranks, int rows_cap, int32_t* d_status, void* stream);
 int bwmoe_scatter_quant_peers(const void* d_x, const int32_t* d_pos, const int32_t* d_indices,
                               const float* d_scales, const int32_t* d_delta, int T, int D, int K,
-                              int experts_per_rank, void* const* h_dst_of_rank, int n_ranks, void* stream);
+                              int experts_per_rank, void* const* h_dst_of_rank, int n_ranks, int rows_cap,
+                              int32_t* d_status, void* stream);
 int bwmoe_combine_peers(void* const* h_y_of_rank, int n_ranks, const int32_t* d_pos, const int32_t* d_indices,
                         const float* d_weights, const int32_t* d_delta, int experts_per_rank, int T, int D,
                         int K, void* d_out, void* stream);

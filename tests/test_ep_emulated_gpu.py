@@ -64,7 +64,7 @@ def _run(world, T, D, E, K, H, push):
         assert torch.equal(s["home_first"].long(), (torch.cumsum(counts, 1) - counts)[:, r * el:(r + 1) * el])
         _lib.check(lib.bwmoe_scatter_quant_peers(s["x"].data_ptr(), s["pos"].data_ptr(), s["idx"].data_ptr(),
                                                  scale_x.data_ptr(), s["delta"].data_ptr(), T, D, K, el,
-                                                 _ptrs(xq_bufs), world, st))
+                                                 _ptrs(xq_bufs), world, cap, status.data_ptr(), st))
     for r, s in enumerate(ranks):               # every rank's experts; result rows pushed home or kept
         sl = slice(r * el, (r + 1) * el)
         R = int(counts[:, sl].sum())

@@ -134,6 +134,59 @@ def _ep_forward_equals_single_process_oracle(rank):
     assert torch.equal(out, ref[rank * T:(rank + 1) * T])
 
 
+def _unequal_batches_agree_on_capacity_and_place_rows(rank):
+    """Ranks bring different numbers of tokens: the receive-buffer capacity is agreed collectively (largest batch),
+    a later batch above it is refused locally before any collective, and the peer-store placement (row
+    pos + delta[expert] in the owner's buffer) reproduces the single-process row order."""
+    import oracle
+    from blackwell_moe_b200.ep import ExpertParallelMoE
+    E, K, D, H = 8, 3, 16, 16
+    el = E // WORLD
+    Ts = [37, 11]
+    T = Ts[rank]
+    f8 = torch.float8_e4m3fn
+    ep = ExpertParallelMoE(torch.zeros(D, E, dtype=torch.bfloat16), torch.zeros(el, D, H).to(f8), torch.zeros(el, D, H).to(f8),
+                           torch.zeros(el, H, D).to(f8), torch.ones(el), torch.ones(el), torch.ones(el),
+                           num_experts=E, top_k=K)
+    cap = ep._agree_on_capacity(T)
+    assert cap == WORLD * max(Ts) * K, cap
+    assert ep._agree_on_capacity(5) == cap                     # smaller batches later: no collective, same answer
+    with pytest.raises(ValueError):
+        ep._agree_on_capacity(max(Ts) + 1)
+    g = torch.Generator().manual_seed(17)
+    idx_all = torch.rand(sum(Ts), E, generator=g).topk(K, dim=-1).indices.to(torch.int32)
+    t0 = sum(Ts[:rank])
+    idx = idx_all[t0:t0 + T]
+    sort_perm, _, offsets = oracle.permutation(idx, E)
+    counts = [torch.empty(E, dtype=torch.int32) for _ in range(WORLD)]
+    dist.all_gather(counts, (offsets[1:] - offsets[:-1]).contiguous())
+    counts = torch.stack(counts)
+    delta, offsets_l, home_counts, home_first = ep._peer_maps(counts, offsets)
+    pos = torch.empty(T * K, dtype=torch.long)
+    pos[sort_perm] = torch.arange(T * K)
+    flat = idx.reshape(-1).long()
+    dst_rank, dst_row = flat // el, pos + delta[flat].long()
+    assert int(dst_row.max()) < cap
+    sent = [None] * WORLD
+    dist.all_gather_object(sent, (dst_rank.tolist(), dst_row.tolist(), (t0 * K + torch.arange(T * K)).tolist()))
+    buf = torch.full((cap,), -1, dtype=torch.long)
+    for ranks_, rows_, slots_ in sent:
+        for r_, row_, slot_ in zip(ranks_, rows_, slots_):
+            if r_ == rank:
+                assert buf[row_] == -1, "two rows stored to one place"
+                buf[row_] = slot_
+    gperm, _, goff = oracle.permutation(idx_all, E)
+    lo, hi = int(goff[rank * el]), int(goff[(rank + 1) * el])
+    assert torch.equal(buf[:hi - lo], gperm[lo:hi])            # (source rank, source row) order = single-process order
+    assert torch.equal(offsets_l.long(), goff[rank * el:(rank + 1) * el + 1].long() - lo)
+    # the way home: rows of local expert j that came from rank s return to rows home_first[s, j]... of rank s
+    assert torch.equal(home_counts, counts[:, rank * el:(rank + 1) * el])
+
+
+def test_unequal_batches_agree_on_capacity_and_place_rows():
+    _run("_unequal_batches_agree_on_capacity_and_place_rows")
+
+
 def test_rows_travel_to_their_experts_and_back():
     _run("_rows_travel_to_their_experts_and_back")
 

@@ -96,6 +96,41 @@ def _worker(rank, world, port, ret):
             if not torch.equal(full, ref):
                 msgs.append(f"block shape {(T, D, E, K, H)} {transport}: max diff "
                             f"{(full.float() - ref.float()).abs().max().item()}")
+            # the streaming interface: same batches through submit/result, one batch in flight behind
+            if transport == "peer":
+                pipe = ep.pipeline(max_tokens=T, depth=2)
+                xs = [c["x"][rank * T:(rank + 1) * T].contiguous().cpu().pin_memory() for _ in range(3)]
+                tickets, got = [], []
+                for i, xb in enumerate(xs):
+                    tickets.append(pipe.submit(xb))
+                    if i >= 1:
+                        got.append(pipe.result(tickets[i - 1]).clone())
+                got.append(pipe.result(tickets[-1]).clone())
+                for y in got:
+                    if not torch.equal(y, out.cpu()):
+                        msgs.append(f"block shape {(T, D, E, K, H)}: pipeline result differs from forward")
+        # ranks bring different numbers of tokens (peer transport, both recipes): capacity agreed collectively
+        for recipe in ("tensor", "block"):
+            Ts = [96, 40][:world] if world == 2 else [64] * world
+            D, E, K, H = 256, 8, 2, 256
+            inp = make_block_inputs(sum(Ts), D, E, K, H, seed=77) if recipe == "block" else \
+                make_inputs(sum(Ts), D, E, K, H, seed=77, keep_bf16=False)
+            c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}
+            names = ("inv_gate", "inv_up", "inv_down") if recipe == "block" else ("s_gate", "s_up", "s_down")
+            el = E // world
+            sl = slice(rank * el, (rank + 1) * el)
+            ep = ExpertParallelMoE(c["w_gate"], c["q_gate"][sl], c["q_up"][sl], c["q_down"][sl], c[names[0]][sl],
+                                   c[names[1]][sl], c[names[2]][sl], num_experts=E, top_k=K)
+            ep.transport = "peer"
+            t0 = sum(Ts[:rank])
+            out = ep.forward(c["x"][t0:t0 + Ts[rank]].contiguous())
+            assert int(ep.last_status[0]) == 0 and ep._agreed_tokens == max(Ts)
+            outs = [torch.empty(t, D, dtype=out.dtype, device=dev) for t in Ts]
+            dist.all_gather(outs, out)
+            ref = bw.fp8_moe_forward(c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c[names[0]], c[names[1]],
+                                     c[names[2]], top_k=K)
+            if not torch.equal(torch.cat(outs), ref):
+                msgs.append(f"unequal batches, {recipe} recipe: result differs from the single-GPU forward")
         ret[rank] = "ok" if not msgs else "; ".join(msgs)
     except Exception as e:  # noqa: BLE001
         import traceback
