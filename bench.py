@@ -148,7 +148,7 @@ class Block:
 
         def step():     # the DeepSeek layer: shared experts, then routed experts with the add fused into the combine
             sh = bw.fp8_dense_mlp(x, *shared)
-            return bw.fp8_moe_forward(x, *wargs, top_k=K, routed_scale=1.0, residual=sh)
+            return bw.fp8_moe_forward(x, *wargs, top_k=K, routed_scale=1.0, residual=sh, **self.kw)
         return step
 
     def flops(self, T):

@@ -42,6 +42,7 @@ SIGNATURES = {
     "bwmoe_router_scratch_bytes": (_sz, [_i] * 4),
     "bwmoe_router": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _ip, _fp, _vp, _sz, _vp]),
     "bwmoe_moe_forward": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
+    "bwmoe_moe_forward_flags": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp, C.c_uint]),
     "bwmoe_moe_forward_ex": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [C.c_float, _vp, _vp, _vp, _sz, _vp]),
     "bwmoe_dense_mlp": (_i, [_vp] * 4 + [_fp] * 3 + [_i] * 3 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed": (_i, [_vp, _fp, _ip] + [_vp] * 3 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),

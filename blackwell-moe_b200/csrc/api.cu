@@ -55,7 +55,7 @@ inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 // Workspace layout.  The first block (status .. amax_h) is cleared by one memset per call.
 struct Layout {
   size_t status, amax_x, amax_h, zero_end;
-  size_t offsets, scale_x, scale_h, topk_idx, topk_w, row_amax, pos, row_slot, row_expert;
+  size_t offsets, scale_x, scale_h, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, row_w;
   size_t plan_scratch, gemm_scratch, router_scratch, router_scratch_bytes, xq, h, hq, y, total;
 };
 
@@ -82,6 +82,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   L->pos = take(sizeof(int32_t) * M);
   L->row_slot = take(sizeof(int32_t) * M);
   L->row_expert = take(sizeof(int32_t) * M);
+  L->row_w = take(sizeof(float) * M);
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
   L->gemm_scratch = take(gemm_scratch_bytes((int)M, D, H, E));
   L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
@@ -160,7 +161,7 @@ int check_forward_args(const char* who, const void* x, const void* wg, const voi
 int run_pipeline(const void* x, const float* weights, const int32_t* indices, const float* row_amax,
                  const void* wg, const void* wu, const void* wd, const float* sg, const float* su,
                  const float* sd, int T, int D, int H, int E, int K, void* out, void* ws, const Layout& L,
-                 cudaStream_t st, float out_scale = 1.0f, const void* residual = nullptr) {
+                 cudaStream_t st, float out_scale = 1.0f, const void* residual = nullptr, unsigned flags = 0) {
   const int M = T * K;
   int32_t* status = at<int32_t>(ws, L.status);
   int32_t* offsets = at<int32_t>(ws, L.offsets);
@@ -175,19 +176,25 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   if ((rc = launch_plan(indices, row_amax, T, E, K, offsets, pos, row_slot, row_expert, amax_x, status,
                         at<void>(ws, L.plan_scratch), st, scale_x)))
     return rc;
-  if ((rc = launch_scatter_quant(x, pos, indices, scale_x, T, D, K, at<void>(ws, L.xq), st))) return rc;
+  float* row_w = at<float>(ws, L.row_w);
+  if ((rc = launch_scatter_quant(x, pos, indices, scale_x, T, D, K, at<void>(ws, L.xq), st, weights, row_w))) return rc;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
                           amax_h, status, at<void>(ws, L.gemm_scratch), st)))
     return rc;
   // scale_h is derived from amax_h inside the requantisation kernel
   if ((rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h))) return rc;
-  const CombineArgs ca{pos, weights, T, K, out, out_scale, residual};
-  bool combined = false;
+  CombineArgs ca{pos, weights, T, K, out, out_scale, residual};
+  ca.row_w = row_w;
+  ca.row_slot = row_slot;
+  ca.reduce = (flags & BWMOE_FLAG_REDUCE_COMBINE) != 0 && out_scale == 1.0f && residual == nullptr && M > 64;
+  if (ca.reduce) BWMOE_CUDA_OK(cudaMemsetAsync(out, 0, (size_t)T * D * 2, st));   // the epilogue adds into it
+  int state = kCombinePlain;
   if ((rc = launch_down(at<void>(ws, L.hq), offsets, scale_h, wd, sd, M, D, H, E, at<void>(ws, L.y), status,
-                        at<void>(ws, L.gemm_scratch), st, &ca, &combined)))
+                        at<void>(ws, L.gemm_scratch), st, &ca, &state)))
     return rc;
-  if (combined) return BWMOE_OK;
-  return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st, out_scale, residual);
+  if (state == kCombineDone) return BWMOE_OK;
+  return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st, out_scale, residual,
+                        state == kCombinePreweighted);
 }
 
 // max|x| per row, for callers that bring their own routing
@@ -353,6 +360,26 @@ int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const v
                              L.router_scratch_bytes, at<int32_t>(ws, L.status)))
     return rc;
   return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st);
+}
+
+int bwmoe_moe_forward_flags(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                            const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                            void* out, void* ws, size_t ws_bytes, void* stream, unsigned flags) {
+  Layout L;
+  if (int rc = check_forward_args("moe_forward_flags", x, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, ws_bytes, &L, 0))
+    return rc;
+  BWMOE_REQUIRE(w_gate != nullptr, BWMOE_ERR_NULL, "moe_forward_flags: w_gate is null");
+  BWMOE_REQUIRE((flags & ~BWMOE_FLAG_REDUCE_COMBINE) == 0, BWMOE_ERR_UNSUPPORTED, "moe_forward_flags: unknown flag bits %#x", flags);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  float* weights = at<float>(ws, L.topk_w);
+  int32_t* indices = at<int32_t>(ws, L.topk_idx);
+  float* row_amax = at<float>(ws, L.row_amax);
+  if (int rc = launch_router(x, w_gate, T, D, E, K, weights, indices, row_amax, st, at<void>(ws, L.router_scratch),
+                             L.router_scratch_bytes, at<int32_t>(ws, L.status)))
+    return rc;
+  return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st, 1.0f, nullptr,
+                      flags);
 }
 
 int bwmoe_moe_forward_ex(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,

@@ -103,7 +103,8 @@ int launch_plan_static(const int32_t* indices, const float* row_amax, int T, int
 int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, float* scales,
                           cudaStream_t st);
 int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indices, const float* scales, int T,
-                         int D, int K, void* xq, cudaStream_t st);
+                         int D, int K, void* xq, cudaStream_t st, const float* weights = nullptr,
+                         float* row_w = nullptr);
 int launch_ep_maps(const int32_t* counts, const int32_t* offsets, int n_ranks, int E, int rank, int32_t* delta,
                    int32_t* offsets_local, int32_t* home_counts, int32_t* home_first, cudaStream_t st);
 int launch_scatter_quant_peers(const void* x, const int32_t* pos, const int32_t* indices, const float* scales,
@@ -117,7 +118,8 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
                    void* hq, cudaStream_t st, float* scales_from_amax_out = nullptr);
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
-                   void* out, cudaStream_t st, float scale = 1.0f, const void* residual = nullptr);
+                   void* out, cudaStream_t st, float scale = 1.0f, const void* residual = nullptr,
+                   bool preweighted = false);
 int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* seg_amax, cudaStream_t st);
 int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
                                 void* xq, float* scales_out, cudaStream_t st);
@@ -134,6 +136,17 @@ struct CombineArgs {
   void* out;
   float scale;
   const void* residual;
+  // for a combine that starts in the down projection's epilogue: the routing weight and the slot of every
+  // permuted row; reduce = add the weighted rows straight into `out` (zeroed by the caller) from the epilogue
+  const float* row_w = nullptr;
+  const int32_t* row_slot = nullptr;
+  bool reduce = false;
+};
+// What launch_down left for the caller to do about the combine.
+enum CombineState {
+  kCombinePlain = 0,        // y holds unweighted rows: run the weighted combine
+  kCombinePreweighted = 1,  // y holds rows already multiplied by their routing weight: run the sum-only combine
+  kCombineDone = 2          // out is complete
 };
 // One device pointer per rank of an expert-parallel group, passed to kernels by value.
 constexpr int kMaxPeers = 8;
@@ -151,7 +164,7 @@ struct HomeRoute {
 };
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
                 int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
-                const CombineArgs* combine = nullptr, bool* fused = nullptr, const HomeRoute* route = nullptr);
+                const CombineArgs* combine = nullptr, int* combine_state = nullptr, const HomeRoute* route = nullptr);
 
 // 128x128 block-scale recipe
 int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,

@@ -50,6 +50,14 @@ struct GemmParams {
   const int32_t* home_counts = nullptr;
   const int32_t* home_first = nullptr;
   void* home[8] = {};
+  // Weighted combine in the DOWN epilogue (row_w != nullptr): every finished row is multiplied by the routing
+  // weight of its slot, bf16(bf16(y) * bf16(w)) - the product the combine would form.  With tok_out set as
+  // well, the weighted row is added straight into out[token] with vector bf16 reductions (token =
+  // row_slot[row] / top_k; out zeroed beforehand) and no result row is written at all.
+  const float* row_w = nullptr;
+  const int32_t* row_slot = nullptr;
+  void* tok_out = nullptr;
+  int top_k = 1;
 };
 
 
@@ -295,8 +303,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float sa = p.scale_a[e];
         const float inv = 1.0f / (sa * p.scale_b0[e]);
         const int n0 = n_idx * BN;
-        // where this lane's row goes: the local result buffer, or the row's place on its home rank
+        // where this lane's row goes: the local result buffer, the row's place on its home rank, or (combine
+        // by reduction) the output row of the row's token
         __nv_bfloat16* out_row = out + (size_t)row * p.N_out;
+        const bool weighted = p.row_w != nullptr;
+        const bool reduce = p.tok_out != nullptr;
+        const float w_row = (weighted && row_ok) ? bf16_round(p.row_w[row]) : 1.0f;
+        if (reduce && row_ok)
+          out_row = static_cast<__nv_bfloat16*>(p.tok_out) + (size_t)(p.row_slot[row] / p.top_k) * p.N_out;
         if (p.n_home > 0 && row_ok) {
           int j = row - p.offsets[e], s = 0;
           for (; s < p.n_home - 1; ++s) {
@@ -329,13 +343,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const int i = (pc & 3) * 8 + 2 * j;
               __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(a[pc >> 2][i]) * inv,
                                                         __uint_as_float(a[pc >> 2][i + 1]) * inv);
+              if (weighted) {                          // bf16(y) * bf16(w), rounded to bf16: the combine's product
+                const float2 f = __bfloat1622float2(b2);
+                b2 = __floats2bfloat162_rn(f.x * w_row, f.y * w_row);
+              }
               w[j] = *reinterpret_cast<uint32_t*>(&b2);
             }
             v[pc] = make_uint4(w[0], w[1], w[2], w[3]);
           }
           group8_transpose(v, lane);
           const int col = n0 + c2 * 64 + piece * 8;
-          if (col < p.N_out) group8_store(v, row_ptr, ok_rows, lane, col);
+          if (col < p.N_out) {
+            if (reduce) group8_reduce(v, row_ptr, ok_rows, lane, col);
+            else        group8_store(v, row_ptr, ok_rows, lane, col);
+          }
         }
       }
       // hand the accumulator buffer back to the MMA warp
@@ -572,8 +593,8 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
 
 int launch_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd,
                 int M, int D, int H, int E, void* y, int32_t* status, void* scratch, cudaStream_t st,
-                const CombineArgs* combine, bool* fused, const HomeRoute* route) {
-  if (fused) *fused = false;
+                const CombineArgs* combine, int* combine_state, const HomeRoute* route) {
+  if (combine_state) *combine_state = kCombinePlain;
   BWMOE_REQUIRE(hq && offsets && sh && wd && sd && y && status, BWMOE_ERR_NULL, "down: null pointer");
   if (int rc = check_common("down", hq, y, M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(wd), BWMOE_ERR_BAD_ALIGN, "down: weights must be 16-byte aligned");
@@ -596,18 +617,31 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
       p.home[r] = route->home[r];
     }
   }
-  if (sp.split_k == 1) return launch_gemm<false, false>(ma, mb, mb, p, M, st);
+  if (sp.split_k == 1) {
+    // the combine starts in the epilogue when the caller handed over the rows' routing weights
+    if (combine != nullptr && combine_state != nullptr && route == nullptr && combine->row_w != nullptr) {
+      p.row_w = combine->row_w;
+      *combine_state = kCombinePreweighted;
+      if (combine->reduce && combine->row_slot != nullptr && combine->scale == 1.0f && combine->residual == nullptr) {
+        p.row_slot = combine->row_slot;
+        p.tok_out = combine->out;
+        p.top_k = combine->K;
+        *combine_state = kCombineDone;
+      }
+    }
+    return launch_gemm<false, false>(ma, mb, mb, p, M, st);
+  }
   BWMOE_REQUIRE(scratch != nullptr && aligned16(scratch), BWMOE_ERR_WORKSPACE, "down: scratch buffer required");
   p.partial = static_cast<float*>(scratch);
   if (int rc = launch_gemm<false, true>(ma, mb, mb, p, M, st)) return rc;
-  if (combine != nullptr && fused != nullptr && combine->T * combine->K == M) {
+  if (combine != nullptr && combine_state != nullptr && combine->T * combine->K == M) {
     const size_t nt = (size_t)combine->T * (D / 4);
     down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, counted(st)>>>(
         p.partial, sp.split_k, M, D, offsets, E, sh, sd, static_cast<__nv_bfloat16*>(y), combine->pos,
         combine->weights, combine->T, combine->K, static_cast<__nv_bfloat16*>(combine->out), combine->scale,
         static_cast<const __nv_bfloat16*>(combine->residual));
     BWMOE_CUDA_OK(cudaGetLastError());
-    *fused = true;
+    *combine_state = kCombineDone;
     return BWMOE_OK;
   }
   const size_t n = (size_t)M * (D / 4);

@@ -262,7 +262,8 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
 __global__ void __launch_bounds__(256)
 scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos,
                      const int32_t* __restrict__ indices, const float* __restrict__ scales, unsigned T,
-                     unsigned W, int K, uint8_t* __restrict__ dst) {
+                     unsigned W, int K, uint8_t* __restrict__ dst, const float* __restrict__ weights,
+                     float* __restrict__ row_w) {
   const unsigned per_row = W / 16;
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= T * per_row) return;
@@ -273,6 +274,7 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restr
   for (int k = 0; k < K; ++k) {
     const int row = pos[(size_t)t * K + k];
     if (row < 0) continue;                       // slot with an out-of-range expert: no row
+    if (row_w != nullptr && c == 0) row_w[row] = weights[(size_t)t * K + k];   // routing weight in row order
     const unsigned long long s2 = splat2(scales[indices[(size_t)t * K + k]]);
     reinterpret_cast<uint4*>(dst + (size_t)row * W)[c] =
         make_uint4(e4m3x4_scaled(r0.x, r0.y, s2), e4m3x4_scaled(r0.z, r0.w, s2), e4m3x4_scaled(r1.x, r1.y, s2),
@@ -394,6 +396,9 @@ combine_peers_kernel(const PeerPtrs src, const int32_t* __restrict__ pos, const 
 // ---- out[t,:] = bf16( sum_k float( bf16( y[pos[t*K+k],:] * bf16(w[t,k]) ) ) ) ----
 // Optional tail (the block glue of FP8MoELayer.forward, src/blackwell_moe/runtime/deepseek_patch.py:51-53):
 //   out = bf16( bf16(routed * scale) + residual ) with routed = the bf16 sum above.
+// PREWEIGHTED: the rows already carry bf16(y * bf16(w)) (the down projection's epilogue multiplied them), so
+// only the sum over k remains; the result is bit-identical either way.
+template <bool PREWEIGHTED>
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ pos,
                const float* __restrict__ weights, int T, int D, int K, __nv_bfloat16* __restrict__ out,
@@ -416,7 +421,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
     for (int j = 0; j < kRows; ++j) {
       const bool in_k = k0 + j < K;
       p[j] = in_k ? pos[(size_t)t * K + k0 + j] : -1;
-      w[j] = in_k ? weights[(size_t)t * K + k0 + j] : 0.f;
+      w[j] = (in_k && !PREWEIGHTED) ? weights[(size_t)t * K + k0 + j] : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < kRows; ++j)
@@ -429,8 +434,8 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = __bfloat1622float2(q[i]);
-        acc[2 * i] += bf16_round(f.x * wk);
-        acc[2 * i + 1] += bf16_round(f.y * wk);
+        acc[2 * i] += PREWEIGHTED ? f.x : bf16_round(f.x * wk);
+        acc[2 * i + 1] += PREWEIGHTED ? f.y : bf16_round(f.y * wk);
       }
     }
   }
@@ -554,12 +559,13 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
 }
 
 int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indices, const float* scales, int T,
-                         int D, int K, void* xq, cudaStream_t st) {
+                         int D, int K, void* xq, cudaStream_t st, const float* weights, float* row_w) {
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "scatter_quant: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(x && pos && indices && scales && xq, BWMOE_ERR_NULL, "scatter_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "scatter_quant: pointers must be 16-byte aligned");
+  BWMOE_REQUIRE(row_w == nullptr || weights != nullptr, BWMOE_ERR_NULL, "scatter_quant: row weights without weights");
   scatter_quant_kernel<<<quant_grid(T, D), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), pos, indices, scales,
-                                                         T, D, K, static_cast<uint8_t*>(xq));
+                                                         T, D, K, static_cast<uint8_t*>(xq), weights, row_w);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -616,15 +622,19 @@ int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const 
 }
 
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
-                   void* out, cudaStream_t st, float scale, const void* residual) {
+                   void* out, cudaStream_t st, float scale, const void* residual, bool preweighted) {
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 8 == 0, BWMOE_ERR_BAD_SHAPE, "combine: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(y && pos && weights && out, BWMOE_ERR_NULL, "combine: null pointer");
   BWMOE_REQUIRE(aligned16(y) && aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine: pointers must be 16-byte aligned");
   const size_t n = (size_t)T * (D / 8);
-  combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(y), pos,
-                                                              weights, T, D, K,
-                                                              static_cast<__nv_bfloat16*>(out), scale,
-                                                              static_cast<const __nv_bfloat16*>(residual));
+  if (preweighted)
+    combine_kernel<true><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
+        static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
+        static_cast<const __nv_bfloat16*>(residual));
+  else
+    combine_kernel<false><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
+        static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
+        static_cast<const __nv_bfloat16*>(residual));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

@@ -207,6 +207,21 @@ __device__ __forceinline__ void group8_store(const uint4 (&v)[8], const unsigned
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(row_ptr[k])) + col) = v[k];
   }
 }
+// The same addressing, but v[k] (eight bf16) is ADDED to the destination with one 16-byte vector reduction
+// (red.global.add.noftz.v4.bf16x2: rounds to bf16 after every addition, order of arrival).
+__device__ __forceinline__ void group8_reduce(const uint4 (&v)[8], const unsigned long long (&row_ptr)[8],
+                                              unsigned ok_rows, int lane, int col) {
+  const int g0 = lane & ~7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if ((ok_rows >> (g0 + k)) & 1u) {
+      const unsigned long long addr = row_ptr[k] + (unsigned long long)col * 2ull;
+      asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v[k].x), "r"(v[k].y),
+                   "r"(v[k].z), "r"(v[k].w)
+                   : "memory");
+    }
+  }
+}
 __device__ __forceinline__ void group8_row_pointers(const void* my_row, int lane, unsigned long long (&row_ptr)[8]) {
   const int g0 = lane & ~7;
 #pragma unroll

@@ -99,7 +99,7 @@ def _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate,
 
 def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
                     scales_gate, scales_up, scales_down, top_k: int = 8, *,
-                    routed_scale: float = 1.0, residual=None) -> torch.Tensor:
+                    routed_scale: float = 1.0, residual=None, combine: str = "deterministic") -> torch.Tensor:
     """FP8 MoE-block forward: ``x[T,D] bf16 -> out[T,D] bf16``.
 
     ``scales_*`` of shape ``[E]`` select the reference's per-tensor recipe (forward
@@ -114,7 +114,12 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
     Keyword-only extras (per-tensor recipe, device activations): ``routed_scale`` and
     ``residual[T,D] bf16`` fuse the tail of the reference's DeepSeek layer into the combine,
     ``out = bf16(bf16(routed * routed_scale) + residual)``
-    (src/blackwell_moe/runtime/deepseek_patch.py:51-53)."""
+    (src/blackwell_moe/runtime/deepseek_patch.py:51-53).  ``combine="atomic"`` lets the down projection's
+    epilogue add the weighted rows straight into the output (bf16 reductions in arrival order, as the
+    reference's scatter_add does, src/blackwell_moe/kernels/scatter.py:25-72): faster, within the same
+    1e-2 bound, but not bit-reproducible; the default sums a token's K rows in a fixed order."""
+    if combine not in ("deterministic", "atomic"):
+        raise ValueError(f"combine={combine!r}: expected 'deterministic' or 'atomic'")
     T, D, H, E = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down,
                                 scales_gate, scales_up, scales_down)
     assert w_gate.shape == (D, E) and w_gate.dtype == torch.bfloat16, (w_gate.shape, w_gate.dtype)
@@ -162,6 +167,10 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
                 _lib.check(lib.bwmoe_moe_forward_ex(x.data_ptr(), *ptrs, T, D, H, E, top_k, float(routed_scale),
                                                     residual.data_ptr() if residual is not None else None,
                                                     out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)))
+                return out
+            if combine == "atomic":
+                _lib.check(lib.bwmoe_moe_forward_flags(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
+                                                       ws.data_ptr(), ws.numel(), _stream(dev), 1))
                 return out
             _lib.check(lib.bwmoe_moe_forward(x.data_ptr(), *ptrs, T, D, H, E, top_k, out.data_ptr(),
                                              ws.data_ptr(), ws.numel(), _stream(dev)))

@@ -68,7 +68,7 @@ enum {
   BWMOE_WS_XQ = 8,         /* e4m3[M*D]   quantised permuted activations */
   BWMOE_WS_HQ = 9,         /* e4m3[M*H]   quantised SwiGLU output        */
   BWMOE_WS_H = 10,         /* bf16[M*H]   SwiGLU output before requant   */
-  BWMOE_WS_Y = 11,         /* bf16[M*D]   down-projection rows           */
+  BWMOE_WS_Y = 11,         /* bf16[M*D]   down-projection rows (per-tensor recipe, M > 64: already times the routing weight) */
   BWMOE_WS_ROW_EXPERT = 12, /* int32[M]   permuted row -> expert         */
   BWMOE_WS_X_INV = 13,     /* float[M*ceil(D/128)] block recipe: inverse scales of xq */
   BWMOE_WS_H_INV = 14      /* float[M*ceil(H/128)] block recipe: inverse scales of hq */
@@ -135,6 +135,25 @@ int bwmoe_moe_forward(const void* d_x, const void* d_w_gate,
                       const float* d_scales_gate, const float* d_scales_up, const float* d_scales_down,
                       int T, int D, int H, int E, int K,
                       void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * bwmoe_moe_forward with options (flags = 0 is bwmoe_moe_forward).
+ *   BWMOE_FLAG_REDUCE_COMBINE: the down projection's epilogue multiplies every finished row by its routing
+ *   weight and ADDS it straight into out[token] with vector bf16 reductions - no result rows are written
+ *   and no combine kernel runs.  This is how the reference combines (bf16 atomic adds in arrival order,
+ *   src/blackwell_moe/kernels/scatter.py:25-72): the sum is rounded to bf16 after every addition and its
+ *   order is not fixed, so two calls may differ in the last bit; within the 1e-2 bound, but not the
+ *   bit-reproducible default (which multiplies in the epilogue too and sums the K rows of a token in a
+ *   fixed order in a separate pass).  Batches of at most 64 rows ignore the flag.
+ */
+#define BWMOE_FLAG_REDUCE_COMBINE 1u
+int bwmoe_moe_forward_flags(const void* d_x, const void* d_w_gate,
+                            const void* d_experts_w_gate, const void* d_experts_w_up,
+                            const void* d_experts_w_down,
+                            const float* d_scales_gate, const float* d_scales_up, const float* d_scales_down,
+                            int T, int D, int H, int E, int K,
+                            void* d_out, void* d_workspace, size_t workspace_bytes, void* stream,
+                            unsigned flags);
 
 /*
  * bwmoe_moe_forward with the glue of the DeepSeek drop-in fused into the combine:

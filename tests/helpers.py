@@ -120,9 +120,10 @@ def expert_subset(W, experts):
     return sub
 
 
-def combine_on_cpu(y, weights, sort_perm, inverse_idx, T):
-    """The combine of fp8_moe_v3.py:70-73 applied to given result rows (bf16 products, bf16 index_add_)."""
+def combine_on_cpu(y, weights, sort_perm, inverse_idx, T, preweighted=False):
+    """The combine of fp8_moe_v3.py:70-73 applied to given result rows (bf16 products, bf16 index_add_);
+    preweighted: the rows already are the bf16 products."""
     flat_w = weights.reshape(-1)[sort_perm].to(BF16).unsqueeze(-1)
     out = torch.zeros(T, y.shape[1], dtype=BF16)
-    out.index_add_(0, inverse_idx, (y * flat_w).to(BF16))
+    out.index_add_(0, inverse_idx, y if preweighted else (y * flat_w).to(BF16))
     return out

@@ -82,6 +82,10 @@ def test_per_tensor_recipe_at_benchmark_dimensions(name, T, D, H, E, K, n_check)
                                         sub["s_up"], sub["s_down"], top_k=K, intermediates=inter, experts=experts)
     _check_integer_stages(v, inter, T, K)
     off = inter["offsets"]
+    # Above 64 rows the down projection's epilogue multiplies each row by its routing weight (the product the
+    # reference forms before its scatter_add, fp8_moe_v3.py:70-71); smaller batches keep plain rows.
+    preweighted = T * K > 64
+    want_rows = inter["weighted"] if preweighted else inter["y_perm"]
     for e in experts:
         s, t = int(off[e]), int(off[e + 1])
         if t <= s:
@@ -90,10 +94,11 @@ def test_per_tensor_recipe_at_benchmark_dimensions(name, T, D, H, E, K, n_check)
         assert torch.equal(v["xq"][s:t].view(torch.uint8), inter["xq"][s:t].view(torch.uint8)), f"x codes, expert {e}"
         assert oracle.rel_l1(v["h"][s:t], inter["h"][s:t]) < 5e-3, f"h, expert {e}"
         torch.testing.assert_close(v["scale_h"][e], inter["sh"][e], rtol=1.6e-2, atol=0)
-        assert oracle.rel_l1(v["y"][s:t], inter["y_perm"][s:t]) < 1e-2, f"y, expert {e}"
+        assert oracle.rel_l1(v["y"][s:t], want_rows[s:t]) < 1e-2, f"y, expert {e}"
     # the combine on every row: the reference's combine applied to the GPU's own result rows
     n_rows = int(off[-1])
-    comb = combine_on_cpu(v["y"][:n_rows], inter["weights"], inter["sort_perm"], inter["inverse_idx"], T)
+    comb = combine_on_cpu(v["y"][:n_rows], inter["weights"], inter["sort_perm"], inter["inverse_idx"], T,
+                          preweighted=preweighted)
     assert oracle.rel_l1(out, comb) < 3e-3
     if n_check is None:
         assert oracle.rel_l1(out, ref) < 1e-2

@@ -171,3 +171,21 @@ def test_full_size_mixtral_block_via_duplicated_tokens():
     assert torch.all(rexp[1:] >= rexp[:-1])
     same = rexp[1:] == rexp[:-1]
     assert torch.all(row_slot[1:][same] > row_slot[:-1][same]), "rows inside a segment must ascend by slot"
+
+
+@pytest.mark.parametrize("T,D,E,K,H", [(256, 1024, 16, 2, 2048), (700, 256, 4, 2, 384), (300, 2048, 64, 6, 1408)])
+def test_combine_by_reduction_in_the_down_epilogue(T, D, E, K, H):
+    """combine="atomic": the down projection's epilogue adds the weighted rows into the output with bf16
+    reductions (the reference's own way of combining, scatter.py:25-72).  Not bit-reproducible by design, so
+    the bars are the recipe's: 1e-2 of the oracle, and a small distance from the deterministic default."""
+    import blackwell_moe_b200 as bw
+    inp = make_inputs(T, D, E, K, H, seed=T + 1)
+    c = to_cuda(inp)
+    args = (c["x"], c["w_gate"], c["q_gate"], c["q_up"], c["q_down"], c["s_gate"], c["s_up"], c["s_down"])
+    det = bw.fp8_moe_forward(*args, top_k=K)
+    red = bw.fp8_moe_forward(*args, top_k=K, combine="atomic")
+    assert int(bw.moe_stage_views("cuda:0", T, D, H, E, K)["status"][0]) == 0
+    ref, _ = run_oracle_forward(inp)
+    assert oracle.rel_l1(red.cpu(), ref) < 1e-2
+    assert oracle.rel_l1(red.cpu(), det.cpu()) < 5e-3
+    assert torch.equal(bw.fp8_moe_forward(*args, top_k=K), det)        # the default stays bit-reproducible
