@@ -98,7 +98,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
 // Workspace of the block-scale recipe: no bf16 h, no segment statistics; per-row group scales instead.
 struct BlockLayout {
   size_t status, zero_end, offsets, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, plan_scratch;
-  size_t router_scratch, router_scratch_bytes, xq_tok, inv_tok, xq, x_inv, hq, h_inv, y, total;
+  size_t router_scratch, router_scratch_bytes, xq, x_inv, hq, h_inv, y, total;
 };
 
 bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
@@ -123,8 +123,6 @@ bool make_block_layout(int T, int D, int H, int E, int K, BlockLayout* L) {
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
   L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
   L->router_scratch = take(L->router_scratch_bytes);
-  L->xq_tok = take((size_t)T * D);
-  L->inv_tok = take(sizeof(float) * (size_t)T * ((D + 127) / 128));
   L->xq = take(M * D);
   L->x_inv = take(sizeof(float) * M * ((D + 127) / 128));
   L->hq = take(M * H);
@@ -230,8 +228,8 @@ int run_block_pipeline(const void* x, const float* weights, const int32_t* indic
   if ((rc = launch_plan(indices, nullptr, T, E, K, offsets, at<int32_t>(ws, L.pos), at<int32_t>(ws, L.row_slot),
                         at<int32_t>(ws, L.row_expert), nullptr, status, at<void>(ws, L.plan_scratch), st)))
     return rc;
-  if ((rc = launch_quant_then_gather_group(x, at<int32_t>(ws, L.row_slot), T, D, K, at<void>(ws, L.xq_tok),
-                                           at<float>(ws, L.inv_tok), at<void>(ws, L.xq), at<float>(ws, L.x_inv), st)))
+  // token-major: a row is read and quantised once, its codes and group scales written to its K rows
+  if ((rc = launch_quant_scatter_group(x, at<int32_t>(ws, L.pos), T, D, K, at<void>(ws, L.xq), at<float>(ws, L.x_inv), st)))
     return rc;
   if ((rc = launch_gateup_block(at<void>(ws, L.xq), at<float>(ws, L.x_inv), offsets, wg, wu, inv_g, inv_u, M, D, H, E,
                                 at<void>(ws, L.hq), at<float>(ws, L.h_inv), status, st)))

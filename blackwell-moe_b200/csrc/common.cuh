@@ -169,8 +169,8 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
 // 128x128 block-scale recipe
 int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int D, int K, void* xq, float* x_inv,
                               cudaStream_t st);
-int launch_quant_then_gather_group(const void* x, const int32_t* row_slot, int T, int D, int K, void* xq_tok,
-                                   float* inv_tok, void* xq, float* x_inv, cudaStream_t st);
+int launch_quant_scatter_group(const void* x, const int32_t* pos, int T, int D, int K, void* xq, float* x_inv,
+                               cudaStream_t st);
 int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
                         const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
                         int32_t* status, cudaStream_t st);

@@ -509,15 +509,19 @@ int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUten
 // inv = max(amax, 1e-4) / 448.  A thread owns 8 elements of kGroupVecs different groups (all loaded
 // before the first is used); the 16 threads of a group reduce the maximum with shuffles.
 constexpr int kGroupVecs = 4;
+// SCATTER: `m` is a token; its codes and scales go to each of its K permuted rows pos[m*K + k] (token-major:
+// the row is read and quantised once and written K times - the codes of a row do not depend on the expert).
+template <bool SCATTER>
 __global__ void __launch_bounds__(256)
 quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot, int M, int W,
-                        int K, uint8_t* __restrict__ dst, float* __restrict__ inv_out) {
+                        int K, uint8_t* __restrict__ dst, float* __restrict__ inv_out,
+                        const int32_t* __restrict__ pos) {
   const int groups = (W + 127) / 128;
   const unsigned per_block = blockDim.x * kGroupVecs;
   const unsigned chunks_per_row = (groups * 16 + per_block - 1) / per_block;
   const int m = (int)(blockIdx.x / chunks_per_row);
   const int v0 = (int)(blockIdx.x % chunks_per_row) * per_block + threadIdx.x;     // 8-element vector index
-  const size_t srow = row_slot != nullptr ? (size_t)(row_slot[m] / K) : (size_t)m;
+  const size_t srow = (!SCATTER && row_slot != nullptr) ? (size_t)(row_slot[m] / K) : (size_t)m;
   const uint4* in = reinterpret_cast<const uint4*>(src + srow * W);
   uint4 raw[kGroupVecs];
 #pragma unroll
@@ -543,26 +547,20 @@ quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __
     if (v * 8 < W) {
       const uint32_t lo = (uint32_t)to_e4m3x2(f[0] * s, f[1] * s) | ((uint32_t)to_e4m3x2(f[2] * s, f[3] * s) << 16);
       const uint32_t hi = (uint32_t)to_e4m3x2(f[4] * s, f[5] * s) | ((uint32_t)to_e4m3x2(f[6] * s, f[7] * s) << 16);
-      reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
-      if ((v & 15) == 0) inv_out[(size_t)m * groups + (v >> 4)] = __fdiv_rn(amax, kFp8Max);
+      const float inv = __fdiv_rn(amax, kFp8Max);
+      if constexpr (SCATTER) {
+        for (int k = 0; k < K; ++k) {
+          const int row = pos[(size_t)m * K + k];
+          if (row < 0) continue;                       // slot with an out-of-range expert: no row
+          reinterpret_cast<uint2*>(dst + (size_t)row * W)[v] = make_uint2(lo, hi);
+          if ((v & 15) == 0) inv_out[(size_t)row * groups + (v >> 4)] = inv;
+        }
+      } else {
+        reinterpret_cast<uint2*>(dst + (size_t)m * W)[v] = make_uint2(lo, hi);
+        if ((v & 15) == 0) inv_out[(size_t)m * groups + (v >> 4)] = inv;
+      }
     }
   }
-}
-
-// ---- copy quantised token rows (codes + group scales) into expert-contiguous order ----
-// One thread per 16 bytes of codes; the first threads of a row also move its scales.
-__global__ void __launch_bounds__(256)
-gather_quantised_rows_kernel(const uint8_t* __restrict__ xq_tok, const float* __restrict__ inv_tok,
-                             const int32_t* __restrict__ row_slot, int M, int D, int K, int groups,
-                             uint8_t* __restrict__ xq, float* __restrict__ x_inv) {
-  const int vec_per_row = D / 16;
-  const unsigned chunks_per_row = (vec_per_row + blockDim.x - 1) / blockDim.x;
-  const int m = (int)(blockIdx.x / chunks_per_row);
-  const int v = (int)(blockIdx.x % chunks_per_row) * blockDim.x + threadIdx.x;
-  const size_t t = (size_t)(row_slot[m] / K);
-  if (v < vec_per_row)
-    reinterpret_cast<uint4*>(xq + (size_t)m * D)[v] = reinterpret_cast<const uint4*>(xq_tok + t * D)[v];
-  if (v < groups) x_inv[(size_t)m * groups + v] = inv_tok[t * groups + v];
 }
 
 // Token-major form for expert parallelism: the codes and group scales of token t go to the place of
@@ -615,24 +613,25 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
   int threads = 32;
   while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
   const unsigned grid = (unsigned)((size_t)M * ceil_div(vecs_per_row, threads * kGroupVecs));
-  quant_group_rows_kernel<<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
-                                                    static_cast<uint8_t*>(xq), x_inv);
+  quant_group_rows_kernel<false><<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
+                                                           static_cast<uint8_t*>(xq), x_inv, nullptr);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
 
-// Block recipe: scales are per token, so tokens are quantised once in token order and the FP8 rows
-// are then copied into expert order (the codes are half the bytes and fit in L2 when re-read K times).
-int launch_quant_then_gather_group(const void* x, const int32_t* row_slot, int T, int D, int K, void* xq_tok,
-                                   float* inv_tok, void* xq, float* x_inv, cudaStream_t st) {
-  if (int rc = launch_gather_quant_group(x, nullptr, T, D, 1, xq_tok, inv_tok, st)) return rc;
-  BWMOE_REQUIRE(row_slot && xq && x_inv, BWMOE_ERR_NULL, "quant_then_gather_group: null pointer");
-  const int M = T * K, groups = ceil_div(D, 128), vec_per_row = D / 16;
+// Token-major quantise + scatter: every token row is read and quantised once and its codes and group scales
+// are written to each of its K permuted rows.
+int launch_quant_scatter_group(const void* x, const int32_t* pos, int T, int D, int K, void* xq, float* x_inv,
+                               cudaStream_t st) {
+  BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "quant_scatter_group: T=%d D=%d K=%d", T, D, K);
+  BWMOE_REQUIRE(x && pos && xq && x_inv, BWMOE_ERR_NULL, "quant_scatter_group: null pointer");
+  BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "quant_scatter_group: pointers must be 16-byte aligned");
+  const int vecs_per_row = ceil_div(D, 128) * 16;
   int threads = 32;
-  while (threads < 256 && threads < vec_per_row) threads <<= 1;
-  const unsigned grid = (unsigned)((size_t)M * ceil_div(vec_per_row, threads));
-  gather_quantised_rows_kernel<<<grid, threads, 0, counted(st)>>>(static_cast<const uint8_t*>(xq_tok), inv_tok, row_slot, M, D,
-                                                        K, groups, static_cast<uint8_t*>(xq), x_inv);
+  while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
+  const unsigned grid = (unsigned)((size_t)T * ceil_div(vecs_per_row, threads * kGroupVecs));
+  quant_group_rows_kernel<true><<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), nullptr, T, D, K,
+                                                          static_cast<uint8_t*>(xq), x_inv, pos);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
