@@ -65,6 +65,7 @@ SIGNATURES = {
     "bwmoe_gemm_scratch_bytes": (_sz, [_i] * 4),
     "bwmoe_gateup_swiglu": (_i, [_vp, _ip, _fp, _vp, _vp, _fp, _fp, _i, _i, _i, _i, _vp, _fp, _ip, _vp, _vp]),
     "bwmoe_requant": (_i, [_vp, _ip, _fp, _i, _i, _vp, _vp]),
+    "bwmoe_requant_segments": (_i, [_vp, _ip, _fp, _i, _i, _vp, _vp]),
     "bwmoe_down": (_i, [_vp, _ip, _fp, _vp, _fp, _i, _i, _i, _i, _vp, _ip, _vp, _vp]),
     "bwmoe_combine": (_i, [_vp, _ip, _fp, _i, _i, _i, _vp, _vp]),
     "bwmoe_ep_maps": (_i, [_ip, _ip, _i, _i, _i, _ip, _ip, _ip, _ip, _vp]),

@@ -54,7 +54,7 @@ inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // Workspace layout.  The first block (status .. amax_h) is cleared by one memset per call.
 struct Layout {
-  size_t status, amax_x, amax_h, zero_end;
+  size_t status, amax_x, amax_h, arrivals, zero_end;
   size_t offsets, scale_x, scale_h, topk_idx, topk_w, row_amax, pos, row_slot, row_expert, row_w;
   size_t plan_scratch, gemm_scratch, router_scratch, router_scratch_bytes, xq, h, hq, y, total;
 };
@@ -72,6 +72,7 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   L->status = take(16);
   L->amax_x = take(sizeof(float) * E);
   L->amax_h = take(sizeof(float) * E);
+  L->arrivals = take(16);
   L->zero_end = o;
   L->offsets = take(sizeof(int32_t) * (E + 1));
   L->scale_x = take(sizeof(float) * E);
@@ -176,11 +177,15 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
     return rc;
   float* row_w = at<float>(ws, L.row_w);
   if ((rc = launch_scatter_quant(x, pos, indices, scale_x, T, D, K, at<void>(ws, L.xq), st, weights, row_w))) return rc;
+  const FusedRequant fr{at<void>(ws, L.hq), scale_h, at<unsigned int>(ws, L.arrivals)};
+  bool requant_done = false;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
-                          amax_h, status, at<void>(ws, L.gemm_scratch), st)))
+                          amax_h, status, at<void>(ws, L.gemm_scratch), st, &fr, &requant_done)))
     return rc;
   // scale_h is derived from amax_h inside the requantisation kernel
-  if ((rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h))) return rc;
+  if (!requant_done &&
+      (rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h)))
+    return rc;
   CombineArgs ca{pos, weights, T, K, out, out_scale, residual};
   ca.row_w = row_w;
   ca.row_slot = row_slot;
@@ -420,10 +425,14 @@ int bwmoe_dense_mlp(const void* x, const void* wg, const void* wu, const void* w
   if ((rc = launch_quant_rows_from_amax(x, at<int32_t>(ws, L.row_expert), at<float>(ws, L.amax_x), T, D,
                                         at<void>(ws, L.xq), at<float>(ws, L.scale_x), st)))
     return rc;
+  const FusedRequant fr{at<void>(ws, L.hq), at<float>(ws, L.scale_h), at<unsigned int>(ws, L.arrivals)};
+  bool requant_done = false;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, at<float>(ws, L.scale_x), wg, wu, sg, su, T, D, H, 1,
-                          at<void>(ws, L.h), at<float>(ws, L.amax_h), status, at<void>(ws, L.gemm_scratch), st)))
+                          at<void>(ws, L.h), at<float>(ws, L.amax_h), status, at<void>(ws, L.gemm_scratch), st, &fr,
+                          &requant_done)))
     return rc;
-  if ((rc = launch_requant(at<void>(ws, L.h), at<int32_t>(ws, L.row_expert), at<float>(ws, L.amax_h), T, H,
+  if (!requant_done &&
+      (rc = launch_requant(at<void>(ws, L.h), at<int32_t>(ws, L.row_expert), at<float>(ws, L.amax_h), T, H,
                            at<void>(ws, L.hq), st, at<float>(ws, L.scale_h))))
     return rc;
   return launch_down(at<void>(ws, L.hq), offsets, at<float>(ws, L.scale_h), wd, sd, T, D, H, 1, out, status,
@@ -636,6 +645,11 @@ int bwmoe_gateup_swiglu(const void* xq, const int32_t* offsets, const float* sx,
 int bwmoe_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H, void* hq,
                   void* stream) {
   return launch_requant(h, row_expert, scales_h, M, H, hq, static_cast<cudaStream_t>(stream));
+}
+
+int bwmoe_requant_segments(const void* h, const int32_t* offsets, const float* scales_h, int E, int H, void* hq,
+                           void* stream) {
+  return launch_requant_segments(h, offsets, scales_h, E, H, hq, static_cast<cudaStream_t>(stream));
 }
 
 int bwmoe_down(const void* hq, const int32_t* offsets, const float* sh, const void* wd, const float* sd, int M,

@@ -117,6 +117,8 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
                         const float* scales, int M, int D, int K, void* xq, cudaStream_t st);
 int launch_requant(const void* h, const int32_t* row_expert, const float* scales_h, int M, int H,
                    void* hq, cudaStream_t st, float* scales_from_amax_out = nullptr);
+int launch_requant_segments(const void* h, const int32_t* offsets, const float* scales_h, int E, int H, void* hq,
+                            cudaStream_t st);
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
                    void* out, cudaStream_t st, float scale = 1.0f, const void* residual = nullptr,
                    bool preweighted = false);
@@ -124,9 +126,18 @@ int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* 
 int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
                                 void* xq, float* scales_out, cudaStream_t st);
 size_t gemm_scratch_bytes(int M, int D, int H, int E);
+// Handed to launch_gateup by the whole-forward entry points: where the requantised h, its scales and the
+// zero-initialised arrival counter of the fused small-batch kernel live.  *requant_done tells the caller
+// whether hq and scale_h were produced (then no 16-bit h exists and no requantisation pass is needed).
+struct FusedRequant {
+  void* hq;
+  float* scale_h;
+  unsigned int* arrivals;
+};
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
-                  int32_t* status, void* scratch, cudaStream_t st);
+                  int32_t* status, void* scratch, cudaStream_t st, const FusedRequant* fr = nullptr,
+                  bool* requant_done = nullptr);
 // What the weighted combine needs; handed to launch_down so that a split-K down projection can sum its
 // slabs and combine in one kernel (*fused reports whether it did; otherwise the caller combines).
 struct CombineArgs {

@@ -442,6 +442,91 @@ swiglu_from_partials_kernel(const float* __restrict__ partial, int S, int M, int
   }
 }
 
+// The same SwiGLU from the slabs, followed in the same kernel by the requantisation of h with its segment
+// scale: no 16-bit h is written at all.  The scale needs the maximum over the whole segment, so the kernel
+// has two phases separated by a grid-wide counter: every thread keeps its h values (at most kFusedItems x 4)
+// in registers, publishes their maxima, the blocks meet (bounded wait; all blocks are resident, the grid is at
+// most one block per SM), and then every thread quantises what it holds.  Same arithmetic as
+// swiglu_from_partials_kernel + quant_rows_kernel.
+constexpr int kFusedItems = 8;
+__global__ void __launch_bounds__(256)
+swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, int M, int H,
+                                    const int32_t* __restrict__ offsets, int E, const float* __restrict__ sx,
+                                    const float* __restrict__ sg, const float* __restrict__ su,
+                                    uint8_t* __restrict__ hq, float* __restrict__ seg_amax,
+                                    float* __restrict__ scale_h, unsigned int* __restrict__ arrivals,
+                                    int32_t* __restrict__ status) {
+  __shared__ int s_ok;
+  const int vec_per_row = H / 4;
+  const int n_rows = min(M, offsets[E]);
+  const long long total = (long long)n_rows * vec_per_row;
+  float hv[kFusedItems][4];
+  int ex[kFusedItems];
+#pragma unroll
+  for (int i = 0; i < kFusedItems; ++i) {
+    const long long item = ((long long)blockIdx.x * kFusedItems + i) * blockDim.x + threadIdx.x;
+    ex[i] = -1;
+    hv[i][0] = hv[i][1] = hv[i][2] = hv[i][3] = 0.f;
+    if (item >= total) continue;
+    const int m = (int)(item / vec_per_row), v = (int)(item % vec_per_row);
+    const int e = expert_of_row(offsets, E, m);
+    ex[i] = e;
+    float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+    float4 a[kSplitMax], b[kSplitMax];
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s) {
+      const float* row = partial + ((size_t)s * M + m) * (2 * H);
+      a[s] = s < S ? reinterpret_cast<const float4*>(row)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+      b[s] = s < S ? reinterpret_cast<const float4*>(row + H)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int s = 0; s < kSplitMax; ++s) {    // fixed order: deterministic (absent slabs add +0)
+      g[0] += a[s].x, g[1] += a[s].y, g[2] += a[s].z, g[3] += a[s].w;
+      u[0] += b[s].x, u[1] += b[s].y, u[2] += b[s].z, u[3] += b[s].w;
+    }
+    const float inv_g = 1.0f / (sx[e] * sg[e]), inv_u = 1.0f / (sx[e] * su[e]);
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float gate = bf16_round(g[q] * inv_g);
+      const float up = bf16_round(u[q] * inv_u);
+      hv[i][q] = bf16_round(bf16_round(silu_f(gate)) * up);
+      amax = fmaxf(amax, fabsf(hv[i][q]));
+    }
+    if (amax > 0.f) atomic_max_nonneg(seg_amax + e, amax);
+  }
+  // ---- all blocks meet: every maximum is published before any scale is read ----
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(arrivals, 1u);
+    bool ok = true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spin = 1; atomicAdd(arrivals, 0u) < gridDim.x; ++spin) {
+      if ((spin & 63u) == 0u && global_ns() - t0 > WAIT_LIMIT_NS) {
+        atomicOr(status, BWMOE_STATUS_WAIT_TIMEOUT);
+        ok = false;
+        break;
+      }
+    }
+    __threadfence();
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+#pragma unroll
+  for (int i = 0; i < kFusedItems; ++i) {
+    if (ex[i] < 0) continue;
+    const long long item = ((long long)blockIdx.x * kFusedItems + i) * blockDim.x + threadIdx.x;
+    const int m = (int)(item / vec_per_row), v = (int)(item % vec_per_row);
+    const float scale = scale_from_amax(__ldcg(seg_amax + ex[i]));
+    if (v == 0) scale_h[ex[i]] = scale;            // every row of the segment writes the same value
+    reinterpret_cast<uint32_t*>(hq + (size_t)m * H)[v] =
+        (uint32_t)to_e4m3x2(hv[i][0] * scale, hv[i][1] * scale) |
+        ((uint32_t)to_e4m3x2(hv[i][2] * scale, hv[i][3] * scale) << 16);
+  }
+}
+
 // y = bf16(sum of slabs * 1/(s_h * s_d)); one thread per (row, 4 columns)
 __global__ void __launch_bounds__(256)
 down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D, const int32_t* __restrict__ offsets,
@@ -568,7 +653,8 @@ size_t gemm_scratch_bytes(int M, int D, int H, int /*E*/) {
 
 int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const void* wg, const void* wu,
                   const float* sg, const float* su, int M, int D, int H, int E, void* h, float* amax_h,
-                  int32_t* status, void* scratch, cudaStream_t st) {
+                  int32_t* status, void* scratch, cudaStream_t st, const FusedRequant* fr, bool* requant_done) {
+  if (requant_done) *requant_done = false;
   BWMOE_REQUIRE(xq && offsets && sx && wg && wu && sg && su && h && amax_h && status, BWMOE_ERR_NULL,
                 "gateup: null pointer");
   if (int rc = check_common("gateup", xq, h, M, D, H, E)) return rc;
@@ -585,6 +671,16 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
   p.partial = static_cast<float*>(scratch);
   if (int rc = launch_gemm<true, true>(ma, mg, mu, p, M, st)) return rc;
   const size_t n = (size_t)M * (H / 4);
+  // small batches inside the whole forward: SwiGLU and the requantisation of h in one kernel (no 16-bit h)
+  const size_t fused_blocks = (n + 256 * kFusedItems - 1) / (256 * kFusedItems);
+  if (fr != nullptr && requant_done != nullptr && fused_blocks <= (size_t)sm_count()) {
+    swiglu_requant_from_partials_kernel<<<(unsigned)fused_blocks, 256, 0, counted(st)>>>(
+        p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<uint8_t*>(fr->hq), amax_h, fr->scale_h,
+        fr->arrivals, status);
+    BWMOE_CUDA_OK(cudaGetLastError());
+    *requant_done = true;
+    return BWMOE_OK;
+  }
   swiglu_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
       p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<__nv_bfloat16*>(h), amax_h);
   BWMOE_CUDA_OK(cudaGetLastError());

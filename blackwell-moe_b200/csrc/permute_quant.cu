@@ -256,6 +256,32 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
                  e4m3x4_scaled(r1.z, r1.w, s2));
 }
 
+// Rows of expert-contiguous segments -> E4M3 with the segment's scale, the number of rows known only on
+// the device (offsets[E]): a fixed grid strides over rows x 16-element pieces, the expert of a row is
+// found by bisection of the offsets.  For callers that must not wait for row counts on the host (expert
+// parallelism: the rows a rank receives are counted on the device).
+__global__ void __launch_bounds__(256)
+quant_segments_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ offsets, int E,
+                      const float* __restrict__ scales, unsigned W, uint8_t* __restrict__ dst) {
+  const unsigned per_row = W / 16;
+  const unsigned long long total = (unsigned long long)offsets[E] * per_row;
+  for (unsigned long long p = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; p < total;
+       p += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned m = (unsigned)(p / per_row), c = (unsigned)(p - (unsigned long long)m * per_row);
+    int lo = 0, hi = E;                          // largest e with offsets[e] <= m
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if ((unsigned)offsets[mid] <= m) lo = mid; else hi = mid;
+    }
+    const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)m * W) + 2 * c;
+    const uint4 r0 = in[0], r1 = in[1];
+    const unsigned long long s2 = splat2(scales[lo]);
+    reinterpret_cast<uint4*>(dst + (size_t)m * W)[c] =
+        make_uint4(e4m3x4_scaled(r0.x, r0.y, s2), e4m3x4_scaled(r0.z, r0.w, s2), e4m3x4_scaled(r1.x, r1.y, s2),
+                   e4m3x4_scaled(r1.z, r1.w, s2));
+  }
+}
+
 // Token-major form of the gather + quantisation: a token's row is read once and written to each of
 // its K destination rows with that row's expert scale (K x fewer reads than walking the permuted rows).
 // One thread per 16 consecutive elements of x[T, W].
@@ -583,6 +609,17 @@ int launch_requant(const void* h, const int32_t* row_expert, const float* scales
     quant_rows_kernel<false, false><<<quant_grid(M, H), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
                                                                       row_expert, scales_h, nullptr, M, H, 1,
                                                                       static_cast<uint8_t*>(hq));
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_requant_segments(const void* h, const int32_t* offsets, const float* scales_h, int E, int H, void* hq,
+                            cudaStream_t st) {
+  BWMOE_REQUIRE(E > 0 && E <= kMaxE && H > 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "requant_segments: E=%d H=%d", E, H);
+  BWMOE_REQUIRE(h && offsets && scales_h && hq, BWMOE_ERR_NULL, "requant_segments: null pointer");
+  BWMOE_REQUIRE(aligned16(h) && aligned16(hq), BWMOE_ERR_BAD_ALIGN, "requant_segments: pointers must be 16-byte aligned");
+  quant_segments_kernel<<<sm_count() * 16, 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), offsets, E, scales_h,
+                                                                  (unsigned)H, static_cast<uint8_t*>(hq));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

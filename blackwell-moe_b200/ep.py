@@ -362,46 +362,46 @@ class ExpertParallelMoE:
         gathered = gathered.view(G, 2 * E)
         amax = gathered[:, :E].amax(0).contiguous()
         counts = gathered[:, E:].contiguous().view(i32)                 # [G, E] rows rank s has for expert e
-        counts_host = counts.cpu()                                      # the step's one host synchronisation
         scale_x = new(E, dtype=f32)
         _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
         sx_local = scale_x[rank * el:(rank + 1) * el].contiguous()
         delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
-        seg = offsets_l[1:] - offsets_l[:-1]
-        R = min(int(counts_host[:, rank * el:(rank + 1) * el].sum()), peer["cap"])
+        # No host synchronisation: the number of rows this rank receives stays on the device.  The GEMMs and the
+        # requantisation take their rows from the device-side segment offsets; the buffers are sized for the
+        # agreed worst case, and a row beyond it is dropped by the store kernel (status bit).
+        cap = peer["cap"]
         self._mark("counts+maps")
 
         peer["hx"].barrier()             # every rank is done with the previous step's buffers
         self._mark("barrier A")
         _lib.check(lib.bwmoe_scatter_quant_peers(x.data_ptr(), pos.data_ptr(), indices.data_ptr(), scale_x.data_ptr(),
-                                                 delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, peer["cap"],
+                                                 delta.data_ptr(), T, D, K, el, peer["xq_ptrs"], G, cap,
                                                  status.data_ptr(), st))
         self._mark("quantise+store")
         peer["hx"].barrier()             # every row of this step has landed
         self._mark("barrier B")
-        if R > 0:
-            row_expert_l = torch.repeat_interleave(torch.arange(el, device=dev, dtype=i32), seg.to(torch.int64),
-                                                   output_size=R)
-            amax_h = torch.zeros(el, dtype=f32, device=dev)
-            h, hq = new(R, H, dtype=torch.bfloat16), new(R, H, dtype=u8)
-            gs = new(max(256, lib.bwmoe_gemm_scratch_bytes(R, D, H, el)), dtype=u8)
-            _lib.check(lib.bwmoe_gateup_swiglu(peer["xq"].data_ptr(), offsets_l.data_ptr(), sx_local.data_ptr(),
-                                               self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
-                                               self.su.data_ptr(), R, D, H, el, h.data_ptr(), amax_h.data_ptr(),
-                                               status.data_ptr(), gs.data_ptr(), st))
-            scale_h = new(el, dtype=f32)
-            _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
-            _lib.check(lib.bwmoe_requant(h.data_ptr(), row_expert_l.data_ptr(), scale_h.data_ptr(), R, H,
-                                         hq.data_ptr(), st))
-            if self._push():
-                _lib.check(lib.bwmoe_down_peers(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(),
-                                                self.wd.data_ptr(), self.sd.data_ptr(), R, D, H, el,
-                                                home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"], G,
-                                                status.data_ptr(), st))
-            else:
-                _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
-                                          self.sd.data_ptr(), R, D, H, el, peer["y"].data_ptr(), status.data_ptr(),
-                                          gs.data_ptr(), st))
+        if "h" not in peer:
+            peer["h"], peer["hq"] = new(cap, H, dtype=torch.bfloat16), new(cap, H, dtype=u8)
+            peer["gs"] = new(max(256, lib.bwmoe_gemm_scratch_bytes(cap, D, H, el)), dtype=u8)
+        h, hq, gs = peer["h"], peer["hq"], peer["gs"]
+        amax_h = torch.zeros(el, dtype=f32, device=dev)
+        _lib.check(lib.bwmoe_gateup_swiglu(peer["xq"].data_ptr(), offsets_l.data_ptr(), sx_local.data_ptr(),
+                                           self.wg.data_ptr(), self.wu.data_ptr(), self.sg.data_ptr(),
+                                           self.su.data_ptr(), cap, D, H, el, h.data_ptr(), amax_h.data_ptr(),
+                                           status.data_ptr(), gs.data_ptr(), st))
+        scale_h = new(el, dtype=f32)
+        _lib.check(lib.bwmoe_segment_scales(amax_h.data_ptr(), None, el, scale_h.data_ptr(), st))
+        _lib.check(lib.bwmoe_requant_segments(h.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), el, H,
+                                              hq.data_ptr(), st))
+        if self._push():
+            _lib.check(lib.bwmoe_down_peers(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(),
+                                            self.wd.data_ptr(), self.sd.data_ptr(), cap, D, H, el,
+                                            home_counts.data_ptr(), home_first.data_ptr(), peer["y_ptrs"], G,
+                                            status.data_ptr(), st))
+        else:
+            _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets_l.data_ptr(), scale_h.data_ptr(), self.wd.data_ptr(),
+                                      self.sd.data_ptr(), cap, D, H, el, peer["y"].data_ptr(), status.data_ptr(),
+                                      gs.data_ptr(), st))
         self._mark("gate/up+requant+down")
         peer["hy"].barrier()             # every rank's result rows are complete (and, pushed, at home)
         self._mark("barrier C")

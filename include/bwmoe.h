@@ -359,6 +359,17 @@ int bwmoe_requant(const void* d_h, const int32_t* d_row_expert, const float* d_s
                   void* d_hq, void* stream);
 
 /*
+ * bwmoe_requant for callers that do not know the number of rows on the host: the rows are those of the
+ * segments d_offsets[0 .. E] (row count d_offsets[E], read on the device), each quantised with its
+ * segment's scale.  Used by the expert-parallel path, where the rows a rank receives are counted on the
+ * device and the host never waits for the count.
+ * replaces: segment_quant_fp8 on h, src/blackwell_moe/kernels/segment_ops.py:68-120 (whose launch grid
+ *           needs the largest segment on the host, segment_ops.py:107).
+ */
+int bwmoe_requant_segments(const void* d_h, const int32_t* d_offsets, const float* d_scales_h, int E, int H,
+                           void* d_hq, void* stream);
+
+/*
  * Grouped down FP8 GEMM: y[m,:] = bf16(acc / (scale_h[e] * scale_down[e])).
  * replaces: grouped_fp8_gemm, src/blackwell_moe/kernels/grouped_fp8.py:36-128.
  */

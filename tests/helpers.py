@@ -68,7 +68,12 @@ def check_against_oracle(inp, out, views, ref_out, inter, tol=1e-2):
     live = counts > 0
     assert torch.equal(views["scale_x"][live], inter["sx"][live]), "x segment scales differ"
     assert torch.equal(views["xq"].view(torch.uint8), inter["xq"].view(torch.uint8)), "x FP8 codes differ"
-    assert oracle.rel_l1(views["h"], inter["h"]) < 5e-3, "SwiGLU output off"
+    if M > 64:
+        assert oracle.rel_l1(views["h"], inter["h"]) < 5e-3, "SwiGLU output off"
+    else:   # small batches requantise h inside the SwiGLU kernel: no 16-bit h exists, the codes are what can be checked
+        n = int(inter["offsets"][-1])
+        mism = (views["hq"][:n].view(torch.uint8) != inter["hq"][:n].view(torch.uint8)).float().mean().item()
+        assert mism < 0.02, f"{mism:.4f} of the h codes differ"
     torch.testing.assert_close(views["scale_h"][live], inter["sh"][live], rtol=1.6e-2, atol=0)
     err = oracle.rel_l1(out, ref_out)
     assert err < tol, f"rel-L1 vs FP8 recipe oracle {err:.4f} >= {tol}"

@@ -92,7 +92,11 @@ def test_per_tensor_recipe_at_benchmark_dimensions(name, T, D, H, E, K, n_check)
             continue
         assert float(v["scale_x"][e]) == float(inter["sx"][e]), f"x scale of expert {e}"
         assert torch.equal(v["xq"][s:t].view(torch.uint8), inter["xq"][s:t].view(torch.uint8)), f"x codes, expert {e}"
-        assert oracle.rel_l1(v["h"][s:t], inter["h"][s:t]) < 5e-3, f"h, expert {e}"
+        if preweighted:
+            assert oracle.rel_l1(v["h"][s:t], inter["h"][s:t]) < 5e-3, f"h, expert {e}"
+        else:       # at most 64 rows: h is requantised inside the SwiGLU kernel, no 16-bit h is written
+            mism = (v["hq"][s:t].view(torch.uint8) != inter["hq"][s:t].view(torch.uint8)).float().mean().item()
+            assert mism < 0.02, f"{mism:.4f} of the h codes of expert {e} differ"
         torch.testing.assert_close(v["scale_h"][e], inter["sh"][e], rtol=1.6e-2, atol=0)
         assert oracle.rel_l1(v["y"][s:t], want_rows[s:t]) < 1e-2, f"y, expert {e}"
     # the combine on every row: the reference's combine applied to the GPU's own result rows
