@@ -33,6 +33,7 @@ _vp, _i, _sz, _fp, _ip = C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_void_p
 SIGNATURES = {
     "bwmoe_version": (_i, []),
     "bwmoe_set_sm_reserve": (_i, [_i]),
+    "bwmoe_invalidate": (_i, []),
     "bwmoe_launch_count": (C.c_longlong, []),
     "bwmoe_last_error": (_i, [C.c_char_p, _sz]),
     "bwmoe_workspace_bytes": (_sz, [_i] * 5),

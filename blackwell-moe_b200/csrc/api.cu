@@ -6,9 +6,50 @@
 #include <cstdio>
 #include <cstring>
 
-#include "common.cuh"
+#include <mutex>
+
+#include "sm100_gemm.cuh"
 
 namespace bwmoe {
+namespace sm100 {
+namespace {
+struct MapEntry {
+  int kind = -1, dev = -1, d0 = 0, d1 = 0, d2 = 0;
+  const void* base = nullptr;
+  CUtensorMap map;
+};
+constexpr int kMapCache = 64;
+MapEntry g_maps[kMapCache];
+int g_map_next = 0;
+std::mutex g_map_mu;
+int current_device() {
+  int dev = -1;
+  return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+}  // namespace
+
+bool tensor_map_lookup(int kind, const void* base, int d0, int d1, int d2, CUtensorMap* out) {
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  for (const MapEntry& m : g_maps)
+    if (m.kind == kind && m.base == base && m.dev == dev && m.d0 == d0 && m.d1 == d1 && m.d2 == d2) {
+      *out = m.map;
+      return true;
+    }
+  return false;
+}
+void tensor_map_store(int kind, const void* base, int d0, int d1, int d2, const CUtensorMap& map) {
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  MapEntry& m = g_maps[g_map_next];
+  g_map_next = (g_map_next + 1) % kMapCache;
+  m.kind = kind, m.dev = dev, m.base = base, m.d0 = d0, m.d1 = d1, m.d2 = d2, m.map = map;
+}
+void tensor_map_clear() {
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  for (MapEntry& m : g_maps) m.kind = -1;
+}
+}  // namespace sm100
 
 namespace {
 thread_local char g_error[512] = "";
@@ -275,6 +316,11 @@ int bwmoe_version(void) { return BWMOE_VERSION; }
 int bwmoe_set_sm_reserve(int n) {
   BWMOE_REQUIRE(n >= 0 && n < 128, BWMOE_ERR_BAD_SHAPE, "set_sm_reserve: %d out of range", n);
   g_sm_reserve = n;
+  return BWMOE_OK;
+}
+
+int bwmoe_invalidate(void) {
+  sm100::tensor_map_clear();
   return BWMOE_OK;
 }
 

@@ -8,13 +8,17 @@
 // (src/blackwell_moe/kernels/grouped_fp8.py:36-89), and of F.silu(gate)*up
 // (src/blackwell_moe/kernels/fp8_moe_v3.py:60).
 //
-// Structure per CTA (192 threads, one CTA per SM):
+// Structure per CTA (320 threads, one CTA per SM):
 //   warp 0      : TMA producer - activations (K-major) and weights (N-major, as the
 //                 caller's [E,K,N] layout dictates) into a 4-stage 128B-swizzled ring
 //   warp 1      : tcgen05.mma issuer, kind::f8f6f4, M=128 N=256 K=32, fp32 accumulators
 //                 in tensor memory, two 256-column buffers so that the epilogue of tile i
 //                 overlaps the main loop of tile i+1
-//   warps 2..5  : epilogue - tcgen05.ld, dequantise, SwiGLU / bf16 rounding, global store
+//   warps 2..9  : epilogue, two warps per tensor-memory lane quarter with half of the tile's
+//                 columns each - tcgen05.ld, dequantise, SwiGLU / bf16 rounding (DOWN: times the
+//                 row's routing weight), stores transposed across lane groups so that every
+//                 store instruction writes whole 128-byte lines (or, for the combine by
+//                 reduction, 16-byte vector bf16 reductions into the token's output row)
 // A tile is 128 permuted rows of ONE expert x 256 accumulator columns (GATE_UP: 128 gate +
 // 128 up columns -> 128 h columns; DOWN: 256 output columns).  Tiles are ordered expert-major,
 // then column block, then row block, so that concurrently running CTAs share weight tiles
@@ -464,10 +468,11 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
   int ex[kFusedItems];
 #pragma unroll
   for (int i = 0; i < kFusedItems; ++i) {
-    const long long item = ((long long)blockIdx.x * kFusedItems + i) * blockDim.x + threadIdx.x;
+    const long long item = ((long long)i * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;   // spread over all blocks
     ex[i] = -1;
     hv[i][0] = hv[i][1] = hv[i][2] = hv[i][3] = 0.f;
-    if (item >= total) continue;
+    float amax = 0.f;
+    if (item < total) {
     const int m = (int)(item / vec_per_row), v = (int)(item % vec_per_row);
     const int e = expert_of_row(offsets, E, m);
     ex[i] = e;
@@ -485,7 +490,6 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
       u[0] += b[s].x, u[1] += b[s].y, u[2] += b[s].z, u[3] += b[s].w;
     }
     const float inv_g = 1.0f / (sx[e] * sg[e]), inv_u = 1.0f / (sx[e] * su[e]);
-    float amax = 0.f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const float gate = bf16_round(g[q] * inv_g);
@@ -493,7 +497,18 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
       hv[i][q] = bf16_round(bf16_round(silu_f(gate)) * up);
       amax = fmaxf(amax, fabsf(hv[i][q]));
     }
-    if (amax > 0.f) atomic_max_nonneg(seg_amax + e, amax);
+    }
+    // one atomic per warp when the whole warp works on one expert (the common case), else per thread: tens of
+    // thousands of atomics on one address would serialise for longer than the rest of the kernel takes
+    const int key = ex[i];
+    const int key0 = __shfl_sync(0xffffffffu, key, 0);
+    if (__all_sync(0xffffffffu, key == key0)) {
+      float mx = amax;
+      for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      if ((threadIdx.x & 31) == 0 && key0 >= 0 && mx > 0.f) atomic_max_nonneg(seg_amax + key0, mx);
+    } else if (key >= 0 && amax > 0.f) {
+      atomic_max_nonneg(seg_amax + key, amax);
+    }
   }
   // ---- all blocks meet: every maximum is published before any scale is read ----
   __syncthreads();
@@ -502,7 +517,15 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
     atomicAdd(arrivals, 1u);
     bool ok = true;
     const unsigned long long t0 = global_ns();
-    for (uint32_t spin = 1; atomicAdd(arrivals, 0u) < gridDim.x; ++spin) {
+    // polled with plain acquire loads and a pause: pollers that hammer the counter with atomics delay the
+    // arrivals they are waiting for
+    auto arrived = [&]() {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(arrivals) : "memory");
+      return v;
+    };
+    for (uint32_t spin = 1; arrived() < gridDim.x; ++spin) {
+      __nanosleep(64);
       if ((spin & 63u) == 0u && global_ns() - t0 > WAIT_LIMIT_NS) {
         atomicOr(status, BWMOE_STATUS_WAIT_TIMEOUT);
         ok = false;
@@ -517,7 +540,7 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
 #pragma unroll
   for (int i = 0; i < kFusedItems; ++i) {
     if (ex[i] < 0) continue;
-    const long long item = ((long long)blockIdx.x * kFusedItems + i) * blockDim.x + threadIdx.x;
+    const long long item = ((long long)i * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
     const int m = (int)(item / vec_per_row), v = (int)(item % vec_per_row);
     const float scale = scale_from_amax(__ldcg(seg_amax + ex[i]));
     if (v == 0) scale_h[ex[i]] = scale;            // every row of the segment writes the same value
@@ -672,8 +695,10 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
   if (int rc = launch_gemm<true, true>(ma, mg, mu, p, M, st)) return rc;
   const size_t n = (size_t)M * (H / 4);
   // small batches inside the whole forward: SwiGLU and the requantisation of h in one kernel (no 16-bit h)
-  const size_t fused_blocks = (n + 256 * kFusedItems - 1) / (256 * kFusedItems);
-  if (fr != nullptr && requant_done != nullptr && fused_blocks <= (size_t)sm_count()) {
+  // as many blocks as there are SMs (all resident at once: they meet inside the kernel), at most kFusedItems items
+  // per thread
+  const size_t fused_blocks = std::min<size_t>((size_t)sm_count(), (n + 255) / 256);
+  if (fr != nullptr && requant_done != nullptr && n <= fused_blocks * 256 * kFusedItems) {
     swiglu_requant_from_partials_kernel<<<(unsigned)fused_blocks, 256, 0, counted(st)>>>(
         p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<uint8_t*>(fr->hq), amax_h, fr->scale_h,
         fr->arrivals, status);

@@ -240,11 +240,22 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= M * per_row) return;
   const unsigned m = p / per_row, c = p - m * per_row;
-  const int expert = row_expert[m];
-  if (expert < 0) return;                        // a row no slot owns (expert id out of range)
-  const size_t srow = SRC_BY_SLOT ? (size_t)(row_slot[m] / K) : (size_t)m;
-  const uint4* in = reinterpret_cast<const uint4*>(src + srow * W) + 2 * c;
-  const uint4 r0 = in[0], r1 = in[1];
+  // The row's data and its expert are fetched side by side (two dependent round trips would halve the rate
+  // of this bandwidth-bound kernel); only the gather form must know that the row exists before it can tell
+  // where the data is.
+  int expert;
+  uint4 r0, r1;
+  if constexpr (SRC_BY_SLOT) {
+    expert = row_expert[m];
+    if (expert < 0) return;                      // a row no slot owns (expert id out of range)
+    const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)(row_slot[m] / K) * W) + 2 * c;
+    r0 = in[0], r1 = in[1];
+  } else {
+    const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)m * W) + 2 * c;
+    r0 = in[0], r1 = in[1];
+    expert = row_expert[m];
+    if (expert < 0) return;
+  }
   float scale = scales[expert];
   if (FROM_AMAX) {
     scale = scale_from_amax(scale);

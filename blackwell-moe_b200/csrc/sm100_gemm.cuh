@@ -243,8 +243,17 @@ inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are a pure function of (base pointer, shape): a small cache keyed by them takes the
+// driver calls off the host path of repeated forwards (five encodes per forward otherwise).  The entries
+// hold no data pointers of their own and never go stale by a change of the CONTENTS behind a pointer (an
+// expert cache swapping a slot's weights); bwmoe_invalidate() empties the cache for callers that want that
+// after freeing memory.  Implemented in api.cu.
+bool tensor_map_lookup(int kind, const void* base, int d0, int d1, int d2, CUtensorMap* out);
+void tensor_map_store(int kind, const void* base, int d0, int d1, int d2, const CUtensorMap& map);
+
 // activations [rows, kdim] e4m3 row-major: box 128 (K) x 128 (rows), 128-byte swizzle
 inline int make_map_a(CUtensorMap* map, const void* base, int rows, int kdim) {
+  if (tensor_map_lookup(0, base, rows, kdim, 0, map)) return BWMOE_OK;
   auto fn = encode_fn();
   BWMOE_REQUIRE(fn != nullptr, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)kdim, (cuuint64_t)rows};
@@ -256,10 +265,12 @@ inline int make_map_a(CUtensorMap* map, const void* base, int rows, int kdim) {
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   BWMOE_REQUIRE(r == CUDA_SUCCESS, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled(A: rows=%d k=%d) failed: %d", rows,
                 kdim, (int)r);
+  tensor_map_store(0, base, rows, kdim, 0, *map);
   return BWMOE_OK;
 }
 // weights [E, kdim, n] e4m3, n contiguous: box 128 (N) x 128 (K) x 1, 128-byte swizzle
 inline int make_map_b(CUtensorMap* map, const void* base, int E, int kdim, int n) {
+  if (tensor_map_lookup(1, base, E, kdim, n, map)) return BWMOE_OK;
   auto fn = encode_fn();
   BWMOE_REQUIRE(fn != nullptr, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
   cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)kdim, (cuuint64_t)E};
@@ -271,6 +282,7 @@ inline int make_map_b(CUtensorMap* map, const void* base, int E, int kdim, int n
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   BWMOE_REQUIRE(r == CUDA_SUCCESS, BWMOE_ERR_CUDA, "cuTensorMapEncodeTiled(B: E=%d k=%d n=%d) failed: %d", E,
                 kdim, n, (int)r);
+  tensor_map_store(1, base, E, kdim, n, *map);
   return BWMOE_OK;
 }
 

@@ -82,6 +82,12 @@ int bwmoe_version(void);
  * No counterpart in the reference (it is single-GPU). */
 int bwmoe_set_sm_reserve(int n);
 
+/* Empties the library's cache of encoded TMA descriptors (keyed by base pointer and shape; at most 64, on the
+ * host).  Never needed for correctness - a descriptor does not depend on the contents behind its pointer, so
+ * an expert cache may swap a slot's weights freely - only to drop entries of memory that has been freed.
+ * The one piece of state the library keeps between calls.  No counterpart in the reference. */
+int bwmoe_invalidate(void);
+
 /* Number of kernels the library has launched in this process so far (all threads, all devices).
  * For benchmarks that report how many of the library's kernels ran inside a timed region.
  * No counterpart in the reference. */
