@@ -126,11 +126,14 @@ class Block:
         self.D, self.H, self.E, self.K, self.T_default, self.Hs = WORKLOADS[workload]
         self.block, self.zipf = workload in BLOCK_SCALE, workload in ZIPF
         self.W = synth_weights(self.D, self.H, self.E, dev, seed=7, block=self.block)
-        self.shared = None
-        if self.Hs:
+        self.n_shared = 0
+        if self.Hs:     # the shared MLP (intermediate n_shared x H) appended as always-on groups of the same pipeline
             S = synth_weights(self.D, self.Hs, 1, dev, seed=11)
-            self.shared = tuple(S[k][0].contiguous() for k in ("q_gate", "q_up", "q_down")) + \
-                tuple(S[k][0:1].contiguous() for k in ("s_gate", "s_up", "s_down"))
+            W = self.W
+            g, u, d, sg, su, sd, self.n_shared = bw.stack_shared_experts(
+                W["q_gate"], W["q_up"], W["q_down"], W["s_gate"], W["s_up"], W["s_down"],
+                S["q_gate"][0], S["q_up"][0], S["q_down"][0], S["s_gate"][0], S["s_up"][0], S["s_down"][0])
+            self.W = {"q_gate": g, "q_up": u, "q_down": d, "s_gate": sg, "s_up": su, "s_down": sd}
         self.kw = {} if combine is None else {"combine": combine}
 
     def wargs(self, w_gate):
@@ -142,14 +145,10 @@ class Block:
 
     def step_fn(self, x, w_gate):
         bw, K, wargs = self.bw, self.K, self.wargs(w_gate)
-        if self.shared is None:
+        if not self.n_shared:
             return lambda: bw.fp8_moe_forward(x, *wargs, top_k=K, **self.kw)
-        shared = self.shared
-
-        def step():     # the DeepSeek layer: shared experts, then routed experts with the add fused into the combine
-            sh = bw.fp8_dense_mlp(x, *shared)
-            return bw.fp8_moe_forward(x, *wargs, top_k=K, routed_scale=1.0, residual=sh, **self.kw)
-        return step
+        S = self.n_shared          # the DeepSeek layer: routed and shared experts in one pipeline
+        return lambda: bw.fp8_moe_forward_shared(x, *wargs, top_k=K, n_shared=S, routed_scale=1.0)
 
     def flops(self, T):
         return float(T) * (6.0 * self.K * self.D * self.H + 2.0 * self.D * self.E + 6.0 * self.D * self.Hs)
@@ -362,8 +361,9 @@ def sweep_rows(dev, stream, pk, flush, have=None):
         g = graph_of(step, dev, stream)
         gms = median(time_region(g.replay, 10, stream, flush, each=True)) * 1e3
         del g
-        off = blk.bw.moe_stage_views(dev, T, blk.D, blk.H, blk.E, blk.K, block=blk.block)["offsets"]
-        used = int(((off[1:] - off[:-1]) > 0).sum())
+        off = blk.bw.moe_stage_views(dev, T, blk.D, blk.H, blk.E + blk.n_shared, blk.K + blk.n_shared,
+                                     block=blk.block)["offsets"]
+        used = int(((off[1:blk.E + 1] - off[:blk.E]) > 0).sum())          # routed experts that were selected
         best = min(ms, gms)
         flops, nbytes = blk.flops(T), blk.decode_bytes(T, used)
         t_tensor, t_hbm = flops / (fp8_peak * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)
@@ -485,7 +485,7 @@ def run_ours(args):
     # (a) synchronous call per step: copy in, compute, copy out, wait
     x_host = x.cpu().pin_memory()
     if world == 1:
-        if blk.shared is None:
+        if not blk.n_shared:
             wargs = blk.wargs(w_gate)
             e2e_step = lambda: bw.fp8_moe_forward(x_host, *wargs, top_k=K)   # noqa: E731
         else:
@@ -507,7 +507,7 @@ def run_ours(args):
     e2e_api = "fp8_moe_forward(x_host) per step" if world == 1 else "ExpertParallelMoE.forward(x_host) per step"
     # (b) the streaming API: the same per-step copies, overlapped with the neighbouring steps' compute
     pipe = None
-    if world == 1 and blk.shared is None:
+    if world == 1 and not blk.n_shared:
         pipe = bw.HostPipeline(*blk.wargs(w_gate), top_k=K, max_tokens=T, depth=2)
         e2e_api = "HostPipeline.submit/result, depth 2 (H2D, compute, D2H of neighbouring steps overlap)"
     elif world > 1 and hasattr(ep, "pipeline"):
@@ -592,6 +592,7 @@ def run_ours(args):
     if world == 1:
         fp8 = measure_fp8_peak(dev, stream)
         step()
+        E, K = E + blk.n_shared, K + blk.n_shared        # the pipeline's own dimensions (always-on groups included)
         M = T * K
         ws = bw.moe._workspaces[(dev.index, stream.cuda_stream)]
         view_fn = lib.bwmoe_workspace_view_block if block else lib.bwmoe_workspace_view
@@ -651,6 +652,8 @@ def run_ours(args):
                         "kernel": kernel_name, "kernel_ms": k_secs * 1e3, "bytes_per_launch": wbytes,
                         "peak_basis": f"hbm_gbs = {hbm:.0f} GB/s {pk['of']}"}
 
+    if world == 1:
+        E, K = E - blk.n_shared, K - blk.n_shared
     graph_ms = None
     if world == 1 and args.graph:
         g = graph_of(step, dev, stream)

@@ -15,7 +15,9 @@ from .moe import (
     fp8_moe_forward,
     fp8_moe_forward_fastcache,
     fp8_moe_forward_routed,
+    fp8_moe_forward_shared,
     moe_stage_views,
+    stack_shared_experts,
     streaming_moe_forward,
     top_k_router,
 )
@@ -34,7 +36,7 @@ __version__ = "0.1.0"
 __all__ = [
     "FP8_MAX_E4M3", "BwmoeError", "HostPipeline", "FP8MixtralSparseMoeBlock", "FP8MoELayer", "FP8SharedExpert", "fp8_dense_mlp",
     "patch_deepseek_moe_with_store", "patch_shared_experts", "dequant_fp8_e4m3", "fp8_moe_forward", "fp8_moe_forward_fastcache",
-    "fp8_moe_forward_routed", "streaming_moe_forward",
+    "fp8_moe_forward_routed", "fp8_moe_forward_shared", "stack_shared_experts", "streaming_moe_forward",
     "fp8_moe_forward_small_e", "fp8_moe_forward_v3", "fp8_moe_forward_v4", "lib", "library_path",
     "moe_stage_views", "quant_fp8_block_128", "quant_fp8_e4m3", "quantize_expert_weights",
     "quantize_expert_weights_block", "top_k_router",

@@ -45,6 +45,8 @@ SIGNATURES = {
     "bwmoe_moe_forward": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_flags": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp, C.c_uint]),
     "bwmoe_moe_forward_ex": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [C.c_float, _vp, _vp, _vp, _sz, _vp]),
+    "bwmoe_workspace_bytes_shared": (_sz, [_i] * 6),
+    "bwmoe_moe_forward_shared": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 6 + [C.c_float, _vp, _vp, _sz, _vp]),
     "bwmoe_dense_mlp": (_i, [_vp] * 4 + [_fp] * 3 + [_i] * 3 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed": (_i, [_vp, _fp, _ip] + [_vp] * 3 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_routed_remap": (_i, [_vp, _fp, _ip, _ip, _i] + [_vp] * 3 + [_fp] * 3 + [_i] * 5

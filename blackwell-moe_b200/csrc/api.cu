@@ -100,7 +100,8 @@ struct Layout {
   size_t plan_scratch, gemm_scratch, router_scratch, router_scratch_bytes, xq, h, hq, y, total;
 };
 
-bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
+// n_shared: the last n_shared experts / slots are always-on groups; the router works on the others only
+bool make_layout(int T, int D, int H, int E, int K, Layout* L, int n_shared = 0) {
   if (T <= 0 || D <= 0 || H <= 0 || E <= 0 || K <= 0 || E > 256 || K > E || K > 32) return false;
   if ((long long)T * K >= (1ll << 31)) return false;
   const size_t M = (size_t)T * K;
@@ -127,12 +128,13 @@ bool make_layout(int T, int D, int H, int E, int K, Layout* L) {
   L->row_w = take(sizeof(float) * M);
   L->plan_scratch = take(plan_scratch_bytes(T, E, K));
   L->gemm_scratch = take(gemm_scratch_bytes((int)M, D, H, E));
-  L->router_scratch_bytes = router_scratch_bytes(T, D, E, K);
-  L->router_scratch = take(L->router_scratch_bytes);
   L->xq = take(M * D);
   L->h = take(M * H * 2);
   L->hq = take(M * H);
   L->y = take(M * D * 2);
+  // last, so that no other offset depends on how many of the experts the router sees
+  L->router_scratch_bytes = router_scratch_bytes(T, D, E - n_shared, K - n_shared);
+  L->router_scratch = take(L->router_scratch_bytes);
   L->total = o;
   return true;
 }
@@ -181,14 +183,14 @@ T* at(void* ws, size_t off) {
 
 int check_forward_args(const char* who, const void* x, const void* wg, const void* wu, const void* wd,
                        const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
-                       void* out, void* ws, size_t ws_bytes, Layout* L, size_t extra) {
+                       void* out, void* ws, size_t ws_bytes, Layout* L, size_t extra, int n_shared = 0) {
   BWMOE_REQUIRE(T > 0 && D > 0 && H > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "%s: T=%d D=%d H=%d E=%d K=%d",
                 who, T, D, H, E, K);
   BWMOE_REQUIRE(D % 16 == 0 && H % 16 == 0, BWMOE_ERR_BAD_SHAPE, "%s: D=%d and H=%d must be multiples of 16", who, D, H);
   BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "%s: E=%d > 256 experts", who, E);
   BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "%s: top_k=%d must be <= min(E,32)", who, K);
   BWMOE_REQUIRE(x && wg && wu && wd && sg && su && sd && out, BWMOE_ERR_NULL, "%s: null pointer", who);
-  BWMOE_REQUIRE(make_layout(T, D, H, E, K, L), BWMOE_ERR_BAD_SHAPE, "%s: shape not representable", who);
+  BWMOE_REQUIRE(make_layout(T, D, H, E, K, L, n_shared), BWMOE_ERR_BAD_SHAPE, "%s: shape not representable", who);
   BWMOE_REQUIRE(ws != nullptr && ws_bytes >= L->total + extra, BWMOE_ERR_WORKSPACE,
                 "%s: workspace of %zu bytes given, %zu needed", who, ws_bytes, L->total + extra);
   BWMOE_REQUIRE(aligned16(x) && aligned16(out) && aligned16(wg) && aligned16(wu) && aligned16(wd) &&
@@ -201,7 +203,8 @@ int check_forward_args(const char* who, const void* x, const void* wg, const voi
 int run_pipeline(const void* x, const float* weights, const int32_t* indices, const float* row_amax,
                  const void* wg, const void* wu, const void* wd, const float* sg, const float* su,
                  const float* sd, int T, int D, int H, int E, int K, void* out, void* ws, const Layout& L,
-                 cudaStream_t st, float out_scale = 1.0f, const void* residual = nullptr, unsigned flags = 0) {
+                 cudaStream_t st, float out_scale = 1.0f, const void* residual = nullptr, unsigned flags = 0,
+                 int n_shared = 0) {
   const int M = T * K;
   int32_t* status = at<int32_t>(ws, L.status);
   int32_t* offsets = at<int32_t>(ws, L.offsets);
@@ -220,9 +223,15 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   if ((rc = launch_scatter_quant(x, pos, indices, scale_x, T, D, K, at<void>(ws, L.xq), st, weights, row_w))) return rc;
   const FusedRequant fr{at<void>(ws, L.hq), scale_h, at<unsigned int>(ws, L.arrivals)};
   bool requant_done = false;
+  // The always-on groups E-n_shared .. E-1 are column pieces of ONE shared MLP whose h is quantised with one
+  // scale (FP8SharedExpert, shared_expert_fp8.py:64): their maxima are merged before the requantisation,
+  // which therefore cannot be fused into the small-batch SwiGLU kernel.
+  const bool merge = n_shared > 1;
   if ((rc = launch_gateup(at<void>(ws, L.xq), offsets, scale_x, wg, wu, sg, su, M, D, H, E, at<void>(ws, L.h),
-                          amax_h, status, at<void>(ws, L.gemm_scratch), st, &fr, &requant_done)))
+                          amax_h, status, at<void>(ws, L.gemm_scratch), st, merge ? nullptr : &fr,
+                          merge ? nullptr : &requant_done)))
     return rc;
+  if (merge && (rc = launch_merge_amax(amax_h, E - n_shared, n_shared, st))) return rc;
   // scale_h is derived from amax_h inside the requantisation kernel
   if (!requant_done &&
       (rc = launch_requant(at<void>(ws, L.h), row_expert, amax_h, M, H, at<void>(ws, L.hq), st, scale_h)))
@@ -230,6 +239,7 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
   CombineArgs ca{pos, weights, T, K, out, out_scale, residual};
   ca.row_w = row_w;
   ca.row_slot = row_slot;
+  ca.n_tail = n_shared;
   ca.reduce = (flags & BWMOE_FLAG_REDUCE_COMBINE) != 0 && out_scale == 1.0f && residual == nullptr && M > 64;
   if (ca.reduce) BWMOE_CUDA_OK(cudaMemsetAsync(out, 0, (size_t)T * D * 2, st));   // the epilogue adds into it
   int state = kCombinePlain;
@@ -238,7 +248,7 @@ int run_pipeline(const void* x, const float* weights, const int32_t* indices, co
     return rc;
   if (state == kCombineDone) return BWMOE_OK;
   return launch_combine(at<void>(ws, L.y), pos, weights, T, D, K, out, st, out_scale, residual,
-                        state == kCombinePreweighted);
+                        state == kCombinePreweighted, n_shared);
 }
 
 // max|x| per row, for callers that bring their own routing
@@ -342,6 +352,12 @@ size_t bwmoe_workspace_bytes(int T, int D, int H, int E, int K) {
   return L.total;
 }
 
+size_t bwmoe_workspace_bytes_shared(int T, int D, int H, int E, int K, int S) {
+  Layout L;
+  if (S < 1 || D % 16 != 0 || H % 16 != 0 || !make_layout(T, D, H, E + S, K + S, &L, S)) return 0;
+  return L.total;
+}
+
 size_t bwmoe_workspace_bytes_host(int T, int D, int H, int E, int K) {
   const size_t base = bwmoe_workspace_bytes(T, D, H, E, K);
   return base == 0 ? 0 : base + 2 * align_up((size_t)T * D * 2);
@@ -429,6 +445,33 @@ int bwmoe_moe_forward_flags(const void* x, const void* w_gate, const void* wg, c
     return rc;
   return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E, K, out, ws, L, st, 1.0f, nullptr,
                       flags);
+}
+
+int bwmoe_moe_forward_shared(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
+                             const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
+                             int S, float routed_scale, void* out, void* ws, size_t ws_bytes, void* stream) {
+  Layout L;
+  BWMOE_REQUIRE(S >= 1 && E >= 1 && K >= 1, BWMOE_ERR_BAD_SHAPE, "moe_forward_shared: E=%d K=%d S=%d", E, K, S);
+  BWMOE_REQUIRE(K <= E, BWMOE_ERR_UNSUPPORTED, "moe_forward_shared: top_k=%d > %d routed experts", K, E);
+  if (int rc = check_forward_args("moe_forward_shared", x, wg, wu, wd, sg, su, sd, T, D, H, E + S, K + S, out, ws,
+                                  ws_bytes, &L, 0, S))
+    return rc;
+  BWMOE_REQUIRE(w_gate != nullptr, BWMOE_ERR_NULL, "moe_forward_shared: w_gate is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BWMOE_CUDA_OK(cudaMemsetAsync(ws, 0, L.zero_end, st));
+  // routing of the E routed experts into scratch that later stages overwrite (pos, row_w), then the S always-on
+  // slots are appended: indices / weights [T, K+S]
+  int32_t* idx_r = at<int32_t>(ws, L.pos);
+  float* w_r = at<float>(ws, L.row_w);
+  float* weights = at<float>(ws, L.topk_w);
+  int32_t* indices = at<int32_t>(ws, L.topk_idx);
+  float* row_amax = at<float>(ws, L.row_amax);
+  if (int rc = launch_router(x, w_gate, T, D, E, K, w_r, idx_r, row_amax, st, at<void>(ws, L.router_scratch),
+                             L.router_scratch_bytes, at<int32_t>(ws, L.status)))
+    return rc;
+  if (int rc = launch_append_shared_slots(idx_r, w_r, T, K, E, S, indices, weights, st)) return rc;
+  return run_pipeline(x, weights, indices, row_amax, wg, wu, wd, sg, su, sd, T, D, H, E + S, K + S, out, ws, L, st,
+                      routed_scale, nullptr, 0, S);
 }
 
 int bwmoe_moe_forward_ex(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,

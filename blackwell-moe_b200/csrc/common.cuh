@@ -121,7 +121,10 @@ int launch_requant_segments(const void* h, const int32_t* offsets, const float* 
                             cudaStream_t st);
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
                    void* out, cudaStream_t st, float scale = 1.0f, const void* residual = nullptr,
-                   bool preweighted = false);
+                   bool preweighted = false, int n_tail = 0);
+int launch_append_shared_slots(const int32_t* idx_r, const float* w_r, int T, int K, int E, int S, int32_t* idx,
+                               float* w, cudaStream_t st);
+int launch_merge_amax(float* amax, int first, int count, cudaStream_t st);
 int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* seg_amax, cudaStream_t st);
 int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
                                 void* xq, float* scales_out, cudaStream_t st);
@@ -152,6 +155,7 @@ struct CombineArgs {
   const float* row_w = nullptr;
   const int32_t* row_slot = nullptr;
   bool reduce = false;
+  int n_tail = 0;      // always-on slots at the end of every token's K: added after the scale (see combine_kernel)
 };
 // What launch_down left for the caller to do about the combine.
 enum CombineState {

@@ -584,12 +584,12 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
                                   const float* __restrict__ sd, __nv_bfloat16* __restrict__ y,
                                   const int32_t* __restrict__ pos, const float* __restrict__ weights, int T, int K,
                                   __nv_bfloat16* __restrict__ out, float scale,
-                                  const __nv_bfloat16* __restrict__ residual) {
+                                  const __nv_bfloat16* __restrict__ residual, int n_tail) {
   const int vec_per_row = D / 4;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)T * vec_per_row) return;
   const int t = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, tail[4] = {0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < K; ++k) {
     const int m = pos[(size_t)t * K + k];
     if (m < 0) continue;
@@ -607,10 +607,11 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
         make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     const float w = bf16_round(weights[(size_t)t * K + k]);
     const float2 f0 = __bfloat1622float2(lo), f1 = __bfloat1622float2(hi);
-    acc[0] += bf16_round(f0.x * w);
-    acc[1] += bf16_round(f0.y * w);
-    acc[2] += bf16_round(f1.x * w);
-    acc[3] += bf16_round(f1.y * w);
+    float* dst = k < K - n_tail ? acc : tail;          // always-on slots are summed apart (see combine_kernel)
+    dst[0] += bf16_round(f0.x * w);
+    dst[1] += bf16_round(f0.y * w);
+    dst[2] += bf16_round(f1.x * w);
+    dst[3] += bf16_round(f1.y * w);
   }
   if (scale != 1.0f) {     // bf16 tensor times a Python scalar: fp32 product with the unrounded scalar
 #pragma unroll
@@ -625,6 +626,10 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
       acc[2 * i] = bf16_round(acc[2 * i]) + f.x;
       acc[2 * i + 1] = bf16_round(acc[2 * i + 1]) + f.y;
     }
+  }
+  if (n_tail > 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = bf16_round(acc[i]) + bf16_round(tail[i]);
   }
   const __nv_bfloat162 o0 = __floats2bfloat162_rn(acc[0], acc[1]), o1 = __floats2bfloat162_rn(acc[2], acc[3]);
   reinterpret_cast<uint2*>(out + (size_t)t * D)[v] =
@@ -743,7 +748,8 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
     if (combine != nullptr && combine_state != nullptr && route == nullptr && combine->row_w != nullptr) {
       p.row_w = combine->row_w;
       *combine_state = kCombinePreweighted;
-      if (combine->reduce && combine->row_slot != nullptr && combine->scale == 1.0f && combine->residual == nullptr) {
+      if (combine->reduce && combine->row_slot != nullptr && combine->scale == 1.0f && combine->residual == nullptr &&
+          combine->n_tail == 0) {
         p.row_slot = combine->row_slot;
         p.tok_out = combine->out;
         p.top_k = combine->K;
@@ -760,7 +766,7 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
     down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, counted(st)>>>(
         p.partial, sp.split_k, M, D, offsets, E, sh, sd, static_cast<__nv_bfloat16*>(y), combine->pos,
         combine->weights, combine->T, combine->K, static_cast<__nv_bfloat16*>(combine->out), combine->scale,
-        static_cast<const __nv_bfloat16*>(combine->residual));
+        static_cast<const __nv_bfloat16*>(combine->residual), combine->n_tail);
     BWMOE_CUDA_OK(cudaGetLastError());
     *combine_state = kCombineDone;
     return BWMOE_OK;

@@ -240,24 +240,15 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= M * per_row) return;
   const unsigned m = p / per_row, c = p - m * per_row;
-  // The row's data and its expert are fetched side by side (two dependent round trips would halve the rate
-  // of this bandwidth-bound kernel); only the gather form must know that the row exists before it can tell
-  // where the data is.
-  int expert;
-  uint4 r0, r1;
-  if constexpr (SRC_BY_SLOT) {
-    expert = row_expert[m];
-    if (expert < 0) return;                      // a row no slot owns (expert id out of range)
-    const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)(row_slot[m] / K) * W) + 2 * c;
-    r0 = in[0], r1 = in[1];
-  } else {
-    const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)m * W) + 2 * c;
-    r0 = in[0], r1 = in[1];
-    expert = row_expert[m];
-    if (expert < 0) return;
-  }
-  float scale = scales[expert];
-  if (FROM_AMAX) {
+  // A row that no slot owns (expert id out of range: row_expert = -1) is not skipped by a branch, which would
+  // put a dependent round trip in front of the data loads of this bandwidth-bound kernel: it is quantised with
+  // scale 0 (its place in dst exists), and only its index uses are guarded.
+  const int expert = row_expert[m];
+  const size_t srow = SRC_BY_SLOT ? (size_t)(max(row_slot[m], 0) / K) : (size_t)m;
+  const uint4* in = reinterpret_cast<const uint4*>(src + srow * W) + 2 * c;
+  const uint4 r0 = in[0], r1 = in[1];
+  float scale = expert >= 0 ? scales[expert] : 0.f;
+  if (FROM_AMAX && expert >= 0) {
     scale = scale_from_amax(scale);
     if (c == 0) scales_out[expert] = scale;      // every row of the segment writes the same value
   }
@@ -435,18 +426,22 @@ combine_peers_kernel(const PeerPtrs src, const int32_t* __restrict__ pos, const 
 //   out = bf16( bf16(routed * scale) + residual ) with routed = the bf16 sum above.
 // PREWEIGHTED: the rows already carry bf16(y * bf16(w)) (the down projection's epilogue multiplied them), so
 // only the sum over k remains; the result is bit-identical either way.
+// n_tail: the last n_tail slots of every token are always-on (shared) experts run as extra groups of the same
+// pipeline; their rows are the `shared` term of the glue above: out = bf16( bf16(routed * scale) + bf16(sum of
+// the tail rows) ).
 template <bool PREWEIGHTED>
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ pos,
                const float* __restrict__ weights, int T, int D, int K, __nv_bfloat16* __restrict__ out,
-               float scale, const __nv_bfloat16* __restrict__ residual) {
+               float scale, const __nv_bfloat16* __restrict__ residual, int n_tail) {
   const int vec_per_row = D / 8;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)T * vec_per_row) return;
   const int t = (int)(gid / vec_per_row), v = (int)(gid % vec_per_row);
-  float acc[8];
+  const int k_routed = K - n_tail;
+  float acc[8], tail[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f, tail[i] = 0.f;
   // three rows at a time: their vectors are all requested before the first is used (one load in flight
   // per thread left the gather at 5.2 TB/s; eight cost too many registers)
   constexpr int kRows = 3;
@@ -471,8 +466,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = __bfloat1622float2(q[i]);
-        acc[2 * i] += PREWEIGHTED ? f.x : bf16_round(f.x * wk);
-        acc[2 * i + 1] += PREWEIGHTED ? f.y : bf16_round(f.y * wk);
+        const float a = PREWEIGHTED ? f.x : bf16_round(f.x * wk), b = PREWEIGHTED ? f.y : bf16_round(f.y * wk);
+        if (k0 + j < k_routed) acc[2 * i] += a, acc[2 * i + 1] += b;
+        else                   tail[2 * i] += a, tail[2 * i + 1] += b;
       }
     }
   }
@@ -490,6 +486,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
       acc[2 * i + 1] = bf16_round(acc[2 * i + 1]) + f.y;
     }
   }
+  if (n_tail > 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = bf16_round(acc[i]) + bf16_round(tail[i]);
+  }
   uint4 o;
   __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -497,7 +497,40 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
   reinterpret_cast<uint4*>(out + (size_t)t * D)[v] = o;
 }
 
+// Routing of a block with S always-on experts appended as groups E .. E+S-1: every token keeps its K routed
+// slots and gets S more with weight 1.
+__global__ void append_shared_slots_kernel(const int32_t* __restrict__ idx_r, const float* __restrict__ w_r, int T,
+                                           int K, int E, int S, int32_t* __restrict__ idx, float* __restrict__ w) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int KS = K + S;
+  if (i >= T * KS) return;
+  const int t = i / KS, k = i - t * KS;
+  idx[i] = k < K ? idx_r[t * K + k] : E + (k - K);
+  w[i] = k < K ? w_r[t * K + k] : 1.0f;
+}
+
+// amax[first .. first+count) <- their common maximum: groups that are pieces of one tensor share its scale
+__global__ void merge_amax_kernel(float* __restrict__ amax, int first, int count) {
+  float m = 0.f;
+  for (int i = 0; i < count; ++i) m = fmaxf(m, amax[first + i]);
+  for (int i = 0; i < count; ++i) amax[first + i] = m;
+}
+
 }  // namespace
+
+int launch_append_shared_slots(const int32_t* idx_r, const float* w_r, int T, int K, int E, int S, int32_t* idx,
+                               float* w, cudaStream_t st) {
+  const int n = T * (K + S);
+  append_shared_slots_kernel<<<ceil_div(n, 256), 256, 0, counted(st)>>>(idx_r, w_r, T, K, E, S, idx, w);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
+
+int launch_merge_amax(float* amax, int first, int count, cudaStream_t st) {
+  merge_amax_kernel<<<1, 1, 0, counted(st)>>>(amax, first, count);
+  BWMOE_CUDA_OK(cudaGetLastError());
+  return BWMOE_OK;
+}
 
 inline unsigned quant_grid(int M, int W) { return (unsigned)(((size_t)M * (W / 16) + 255) / 256); }
 
@@ -670,7 +703,8 @@ int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const 
 }
 
 int launch_combine(const void* y, const int32_t* pos, const float* weights, int T, int D, int K,
-                   void* out, cudaStream_t st, float scale, const void* residual, bool preweighted) {
+                   void* out, cudaStream_t st, float scale, const void* residual, bool preweighted, int n_tail) {
+  BWMOE_REQUIRE(n_tail >= 0 && n_tail < K, BWMOE_ERR_BAD_SHAPE, "combine: %d always-on slots of %d", n_tail, K);
   BWMOE_REQUIRE(T > 0 && D > 0 && K > 0 && D % 8 == 0, BWMOE_ERR_BAD_SHAPE, "combine: T=%d D=%d K=%d", T, D, K);
   BWMOE_REQUIRE(y && pos && weights && out, BWMOE_ERR_NULL, "combine: null pointer");
   BWMOE_REQUIRE(aligned16(y) && aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine: pointers must be 16-byte aligned");
@@ -678,11 +712,11 @@ int launch_combine(const void* y, const int32_t* pos, const float* weights, int 
   if (preweighted)
     combine_kernel<true><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
         static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
-        static_cast<const __nv_bfloat16*>(residual));
+        static_cast<const __nv_bfloat16*>(residual), n_tail);
   else
     combine_kernel<false><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
         static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
-        static_cast<const __nv_bfloat16*>(residual));
+        static_cast<const __nv_bfloat16*>(residual), n_tail);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

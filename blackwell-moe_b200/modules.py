@@ -16,7 +16,8 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .moe import _contig, _require_cuda, _stream, _workspace, fp8_moe_forward
+from .moe import (_contig, _require_cuda, _stream, _workspace, fp8_moe_forward, fp8_moe_forward_shared,
+                  stack_shared_experts)
 from .quant import quant_fp8_e4m3
 
 _FP8 = torch.float8_e4m3fn
@@ -106,9 +107,42 @@ class FP8MoELayer(nn.Module):
         self.shared_experts = deepseek_moe.shared_experts
         self.gate = deepseek_moe.gate
 
+    #: run the shared experts as always-on groups of the routed pipeline (one set of launches for the whole
+    #: block) when they are an :class:`FP8SharedExpert` whose intermediate size is a multiple of the routed
+    #: experts'; set to False to keep the two separate calls of the reference's forward
+    fold_shared = True
+    _folded = None
+
+    def _fold(self):
+        """Stack the shared MLP behind the routed experts once (the routed buffers are replaced by the
+        stacked ones, so nothing is held twice)."""
+        sh = self.shared_experts
+        E, D, H = self.experts_w_gate_fp8.shape
+        ok = (self.fold_shared and isinstance(sh, FP8SharedExpert) and sh.w_gate.shape[0] == D
+              and sh.w_gate.shape[1] % H == 0 and sh.w_gate.device == self.experts_w_gate_fp8.device)
+        if ok:
+            S = sh.w_gate.shape[1] // H
+            ok = E + S <= 256 and self.top_k + S <= 32
+        if not ok:
+            self._folded = False
+            return
+        g, u, d, sg, su, sd, S = stack_shared_experts(
+            self.experts_w_gate_fp8, self.experts_w_up_fp8, self.experts_w_down_fp8, self.scales_gate, self.scales_up,
+            self.scales_down, sh.w_gate, sh.w_up, sh.w_down, sh.s_gate, sh.s_up, sh.s_down)
+        self.experts_w_gate_fp8, self.experts_w_up_fp8, self.experts_w_down_fp8 = g, u, d
+        self.scales_gate, self.scales_up, self.scales_down = sg, su, sd
+        self._folded = S
+
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         shape = hidden_states.shape
         x = hidden_states.reshape(-1, self.hidden_dim).to(torch.bfloat16).contiguous()
+        if self._folded is None:
+            self._fold()
+        if self._folded:
+            out = fp8_moe_forward_shared(x, self.w_router, self.experts_w_gate_fp8, self.experts_w_up_fp8,
+                                         self.experts_w_down_fp8, self.scales_gate, self.scales_up, self.scales_down,
+                                         top_k=self.top_k, n_shared=self._folded, routed_scale=float(self.routed_scale))
+            return out.reshape(shape)
         shared_out = self.shared_experts(hidden_states).reshape(-1, self.hidden_dim).to(torch.bfloat16).contiguous()
         out = fp8_moe_forward(x, self.w_router, self.experts_w_gate_fp8, self.experts_w_up_fp8,
                               self.experts_w_down_fp8, self.scales_gate, self.scales_up, self.scales_down,

@@ -185,6 +185,57 @@ def fp8_moe_forward(x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
         return out
 
 
+def fp8_moe_forward_shared(x, w_gate, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down,
+                           top_k: int, n_shared: int, routed_scale: float = 1.0) -> torch.Tensor:
+    """The DeepSeek block in one pipeline: ``E`` routed experts (top-k of the router ``w_gate[D,E]``) plus
+    ``n_shared`` always-on experts that are the last ``n_shared`` entries of the stacked weight tensors
+    (``[E + n_shared, ...]``); ``out = bf16(bf16(routed * routed_scale) + shared)``.  Takes over
+    ``FP8MoELayer.forward`` (src/blackwell_moe/runtime/deepseek_patch.py:39-53) including its shared-expert call
+    (src/blackwell_moe/runtime/shared_expert_fp8.py:57-68); :func:`stack_shared_experts` prepares the tensors."""
+    T, D, H, EA = _check_experts(x, experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down)
+    E = EA - n_shared
+    assert n_shared >= 1 and E >= top_k >= 1, (EA, n_shared, top_k)
+    assert scales_gate.dim() == 1, "the shared-expert pipeline exists for the per-tensor recipe"
+    assert w_gate.shape == (D, E) and w_gate.dtype == torch.bfloat16, (w_gate.shape, w_gate.dtype)
+    tensors = [_contig(t, "tensor") for t in (x, w_gate, experts_w_gate, experts_w_up, experts_w_down,
+                                              scales_gate, scales_up, scales_down)]
+    dev = _require_cuda(*tensors)
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        need = lib.bwmoe_workspace_bytes_shared(T, D, H, E, top_k, n_shared)
+        if need == 0:
+            raise ValueError(f"unsupported shape T={T} D={D} H={H} E={E}+{n_shared} top_k={top_k}+{n_shared}")
+        ws = _workspace(dev, need)
+        out = torch.empty_like(x)
+        _lib.check(lib.bwmoe_moe_forward_shared(*[t.data_ptr() for t in tensors], T, D, H, E, top_k, n_shared,
+                                                float(routed_scale), out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                _stream(dev)))
+    return out
+
+
+def stack_shared_experts(experts_w_gate, experts_w_up, experts_w_down, scales_gate, scales_up, scales_down,
+                         shared_w_gate, shared_w_up, shared_w_down, shared_s_gate, shared_s_up, shared_s_down):
+    """Append a shared MLP (``[D, S*H]`` gate/up, ``[S*H, D]`` down, per-tensor scales) to stacked routed experts
+    as ``S`` more experts of intermediate ``H``: column pieces of gate/up, row pieces of down, each with the
+    MLP's scale.  Returns the six ``[E+S, ...]`` tensors and ``S`` (load time, plain torch)."""
+    E, D, H = experts_w_gate.shape
+    Hs = shared_w_gate.shape[1]
+    assert tuple(shared_w_gate.shape) == (D, Hs) and tuple(shared_w_down.shape) == (Hs, D) and Hs % H == 0, \
+        (shared_w_gate.shape, shared_w_down.shape, H)
+    S = Hs // H
+    u8 = torch.uint8
+
+    def cat(a, b):                      # float8 tensors are concatenated through their byte view
+        return torch.cat([a.contiguous().view(u8), b.contiguous().view(u8)]).view(_FP8).contiguous()
+    gate = cat(experts_w_gate, shared_w_gate.view(u8).view(D, S, H).permute(1, 0, 2))
+    up = cat(experts_w_up, shared_w_up.view(u8).view(D, S, H).permute(1, 0, 2))
+    down = cat(experts_w_down, shared_w_down.view(u8).view(S, H, D))
+    f32 = torch.float32
+    scales = [torch.cat([r.to(f32).reshape(-1), s.to(f32).reshape(1).expand(S)]).contiguous()
+              for r, s in ((scales_gate, shared_s_gate), (scales_up, shared_s_up), (scales_down, shared_s_down))]
+    return gate, up, down, scales[0], scales[1], scales[2], S
+
+
 def fp8_moe_forward_routed(x, router_weights, expert_indices, experts_w_gate, experts_w_up, experts_w_down,
                            scales_gate, scales_up, scales_down, remap=None) -> torch.Tensor:
     """Same block with caller-supplied routing (``router_weights[T,K] fp32``,

@@ -174,6 +174,29 @@ int bwmoe_moe_forward_ex(const void* d_x, const void* d_w_gate,
                          void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The DeepSeek block in ONE pipeline: E routed experts (top-K) plus S always-on shared experts run as groups
+ * E .. E+S-1 of the same permute / grouped-GEMM / combine kernels, every token being routed to them with
+ * weight 1:   out = bf16( bf16(routed * routed_scale) + shared ).
+ * The weight tensors hold E+S experts: d_experts_w_gate/up[E+S, D, H], d_experts_w_down[E+S, H, D],
+ * d_scales_*[E+S].  A shared MLP of intermediate S*H (HF DeepseekV2MLP with n_shared_experts * H) is passed as
+ * S column pieces of its gate/up matrices and S row pieces of its down matrix, each with the MLP's per-tensor
+ * scale; the pieces then share one activation scale for x (all rows) and one for h (their maxima are merged),
+ * as FP8SharedExpert quantises them.  d_w_gate is the router's [D, E].
+ * Workspace: bwmoe_workspace_bytes_shared(T, D, H, E, K, S) (the layout of E+S experts and K+S slots per
+ * token, with the router's scratch sized for the E routed experts); bwmoe_workspace_view with (E+S, K+S)
+ * addresses its intermediates.
+ * replaces: FP8MoELayer.forward, src/blackwell_moe/runtime/deepseek_patch.py:39-53, including the
+ *           shared-expert call FP8SharedExpert.forward, src/blackwell_moe/runtime/shared_expert_fp8.py:57-68.
+ */
+size_t bwmoe_workspace_bytes_shared(int T, int D, int H, int E, int K, int S);
+int bwmoe_moe_forward_shared(const void* d_x, const void* d_w_gate,
+                             const void* d_experts_w_gate, const void* d_experts_w_up,
+                             const void* d_experts_w_down,
+                             const float* d_scales_gate, const float* d_scales_up, const float* d_scales_down,
+                             int T, int D, int H, int E, int K, int S, float routed_scale,
+                             void* d_out, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Dense (always-on) FP8 SwiGLU MLP over all T rows with whole-tensor scales for x and h:
  * the shared experts of a DeepSeek block.  Weights [D,H] / [H,D] e4m3, scales [1] fp32.
  * Workspace: bwmoe_workspace_bytes(T, D, H, 1, 1).

@@ -70,6 +70,15 @@ def test_shared_expert_module_and_deepseek_layer():
     ref = (routed * 2.5) + sh_ref
     assert oracle.rel_l1(out, ref) < 1e-2
 
+    assert layer._folded == 3        # Hs = 3 x H: the shared MLP runs as three always-on groups of the routed pipeline
+    # the reference's two separate calls (shared MLP, then routed experts with the add fused into the combine)
+    layer2 = bw.FP8MoELayer(DeepseekV2MoE().cuda(), store).cuda()
+    layer2.fold_shared = False
+    out2 = layer2(x3.cuda()).cpu().view(T, D)
+    assert layer2._folded is False
+    assert oracle.rel_l1(out2, ref) < 1e-2
+    assert oracle.rel_l1(out, out2) < 5e-3
+
     # the patch helper finds the module by class name
     model = nn.Module()
     model.model = nn.Module()
