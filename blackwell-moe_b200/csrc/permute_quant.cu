@@ -250,7 +250,9 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restri
   float scale = expert >= 0 ? scales[expert] : 0.f;
   if (FROM_AMAX && expert >= 0) {
     scale = scale_from_amax(scale);
-    if (c == 0) scales_out[expert] = scale;      // every row of the segment writes the same value
+    // published once per segment, by its first row (a store per row piled a hundred thousand stores onto a few
+    // dozen addresses)
+    if (c == 0 && (m == 0 || row_expert[m - 1] != expert)) scales_out[expert] = scale;
   }
   const unsigned long long s2 = splat2(scale);
   reinterpret_cast<uint4*>(dst + (size_t)m * W)[c] =
