@@ -5,8 +5,8 @@
  * Conventions
  *   - every pointer named d_* is a DEVICE pointer owned by the caller; h_* is a
  *     HOST pointer.  The library allocates no device memory, frees nothing and
- *     keeps no pointer after a call returns (bwmoe_moe_forward_host is the one
- *     documented exception: it uses a caller-provided device workspace too).
+ *     dereferences no pointer after a call returns (it remembers base addresses only as
+ *     keys of its host-side cache of encoded TMA descriptors, see bwmoe_invalidate).
  *   - all work is enqueued on `stream` (a cudaStream_t passed as void*); no call
  *     synchronises the device except bwmoe_moe_forward_host and bwmoe_read_status.
  *   - every function returns 0 on success or a negative BWMOE_ERR_* code;
