@@ -346,33 +346,65 @@ block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-        {
-          uint32_t r0[32], r1[32];
-          tmem_ld32(t_row + colA, r0);
-          tmem_ld32(t_row + colA + 32, r1);
-          tmem_ld_wait();
-          const unsigned long long s2 = splat2(sA);
+        if constexpr (GATE_UP) {
+          // Four 32-column chunks, software-pipelined: the load of chunk i+1 is in flight while chunk i is folded
+          // (tcgen05.wait::ld waits for every load issued so far, so each wait is followed by the next load and
+          // only then by the FMAs of the chunk that just landed).  The buffer is handed back to the tensor pipe
+          // as soon as its last chunk is in registers - before the last chunk's FMAs, which need it no more.
+          {
+            uint32_t ra[32], rb[32];
+            const unsigned long long sA2 = splat2(sA), sB2 = splat2(sB);
+            tmem_ld32(t_row + colA, ra);
+            tmem_ld_wait();
+            tmem_ld32(t_row + colA + 32, rb);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            fma2(accA2[j], r0[2 * j], r0[2 * j + 1], s2);
-            fma2(accA2[16 + j], r1[2 * j], r1[2 * j + 1], s2);
-          }
-        }
-        {
-          uint32_t r0[32], r1[32];
-          tmem_ld32(t_row + colB, r0);
-          tmem_ld32(t_row + colB + 32, r1);
-          tmem_ld_wait();
-          const unsigned long long s2 = splat2(sB);
+            for (int j = 0; j < 16; ++j) fma2(accA2[j], ra[2 * j], ra[2 * j + 1], sA2);
+            tmem_ld_wait();
+            tmem_ld32(t_row + colB, ra);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            fma2(accB2[j], r0[2 * j], r0[2 * j + 1], s2);
-            fma2(accB2[16 + j], r1[2 * j], r1[2 * j + 1], s2);
+            for (int j = 0; j < 16; ++j) fma2(accA2[16 + j], rb[2 * j], rb[2 * j + 1], sA2);
+            tmem_ld_wait();
+            tmem_ld32(t_row + colB + 32, rb);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(accB2[j], ra[2 * j], ra[2 * j + 1], sB2);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * hbA);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(accB2[16 + j], rb[2 * j], rb[2 * j + 1], sB2);
           }
+        } else {
+          // Down tiles (a K loop of 4-11 blocks, then 64 KiB of output per tile: the stores set the pace) measured
+          // 4 % faster with the plain order: two rounds of two loads, the buffer released after the FMAs.
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld32(t_row + colA, r0);
+            tmem_ld32(t_row + colA + 32, r1);
+            tmem_ld_wait();
+            const unsigned long long s2 = splat2(sA);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              fma2(accA2[j], r0[2 * j], r0[2 * j + 1], s2);
+              fma2(accA2[16 + j], r1[2 * j], r1[2 * j + 1], s2);
+            }
+          }
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld32(t_row + colB, r0);
+            tmem_ld32(t_row + colB + 32, r1);
+            tmem_ld_wait();
+            const unsigned long long s2 = splat2(sB);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              fma2(accB2[j], r0[2 * j], r0[2 * j + 1], s2);
+              fma2(accB2[16 + j], r1[2 * j], r1[2 * j + 1], s2);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * hbA);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * hbA);
       }
       if (!ok) break;
       float accA[64], accB[64];
