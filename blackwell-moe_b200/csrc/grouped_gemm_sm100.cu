@@ -24,6 +24,9 @@
 // then column block, then row block, so that concurrently running CTAs share weight tiles
 // and an expert's activations stay in L2 while its weights stream through once.
 //
+// Large batches run the DOWN projection on CTA pairs (two-CTA clusters, cta_group::2, 256-row tiles; see the
+// kernel's PAIR parameter); everything else runs one CTA per tile.
+//
 // Every barrier wait is bounded: when a wait runs out the kernel sets
 // BWMOE_STATUS_WAIT_TIMEOUT in the status word, tells the other warps to stop, waits for
 // copies in flight, frees its tensor memory and returns.
@@ -71,16 +74,17 @@ struct TileCursor {
   const int* cum;       // smem [E+1]: tiles before expert e
   const int32_t* offsets;
   int E, n_tiles, e;
+  int bm = BM;          // rows per tile: 128, or 256 when a CTA pair shares the tile
   __device__ bool locate(int tile, int& expert, int& row0, int& row_end, int& n_idx, int& split) {
     while (e < E && tile >= cum[e + 1]) ++e;
     if (e >= E) return false;
     const int seg0 = offsets[e], seg1 = offsets[e + 1];
-    const int m_tiles = (seg1 - seg0 + BM - 1) / BM;
+    const int m_tiles = (seg1 - seg0 + bm - 1) / bm;
     const int within = tile - cum[e];
     const int rest = within / m_tiles;
     n_idx = rest % n_tiles;
     split = rest / n_tiles;
-    row0 = seg0 + (within % m_tiles) * BM;
+    row0 = seg0 + (within % m_tiles) * bm;
     row_end = seg1;
     expert = e;
     return true;
@@ -93,7 +97,19 @@ struct TileCursor {
 constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 
-template <bool GATE_UP, bool RAW>
+// PAIR: the CTAs of a two-CTA cluster share 256-row tiles (cta_group::2).  CTA `rank` of the pair loads rows
+// rank*128.. of the tile and one 128-column half of the weight tile (GATE_UP: rank 0 the gate box, rank 1 the
+// up box), so every weight byte enters one of the two shared memories only; the even CTA issues M=256 MMAs
+// that read both shared memories and write each CTA's 128 rows into that CTA's tensor memory.  Stages are
+// 32 KiB per CTA, so the ring is six deep.  Barriers: loads of both CTAs report to the even CTA's full
+// barrier; the issuer commits to the stage's empty barrier and to the accumulator's full barrier of each CTA
+// in turn; the odd CTA's epilogue warps hand accumulator buffers back on the even CTA's barrier.
+// Measured inside whole forwards on one B200 (same process order, both builds twice): the down projection
+// gains 2 % (Mixtral shape, 16384 tokens: 1531 -> 1498 us; DeepSeek shape: 373 -> 365 us), the gate/up
+// projection loses 2-5 % (2863 -> 2910 us; 1476 -> 1548 us at 8192 tokens), so the launcher pairs the down
+// projection only.  Both forms run with the SM clock already lowered by the power limit (1.55 GHz of 1.97
+// at 71-77 % tensor-pipe activity), which is why halving the weight traffic into shared memory buys so little.
+template <bool GATE_UP, bool RAW, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
@@ -104,9 +120,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
-  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  static_assert(!(PAIR && RAW), "split-K tiles are not paired");
+  constexpr int NSTAGE = PAIR ? PAIR_STAGES : STAGES;
+  constexpr int STAGE_SZ = PAIR ? PAIR_STAGE_BYTES : STAGE_BYTES;
+  constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;
+  const uint32_t bars = tiles_base + NSTAGE * STAGE_SZ;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * NSTAGE;
+  const uint32_t bar_tfull = bars + 16 * NSTAGE, bar_tempty = bar_tfull + 16;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;            // place in the pair
+  const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &s_abort;
 
@@ -116,19 +139,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int t = 0;
     if (e < p.E) {
       const int rows = p.offsets[e + 1] - p.offsets[e];
-      t = ((rows + BM - 1) / BM) * p.n_tiles * p.split_k;
+      t = ((rows + TILE_ROWS - 1) / TILE_ROWS) * p.n_tiles * p.split_k;
     }
     s_cum[e + 1] = t;
   }
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
+      mbar_init(bar_tempty + 8 * b, PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -151,9 +174,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int j = 0; j < 8; ++j) s_cum[1 + lane * 8 + j] = base + v[j];
     if (lane == 0) s_cum[0] = 0;
   }
-  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(smem_u32(&s_tmem_base), TMEM_COLS);
+    else                tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();       // the peer's barriers and tensor memory exist from here on
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   const int total_tiles = s_cum[p.E];
@@ -162,34 +189,51 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0, TILE_ROWS};
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         int e, row0, row_end, n_idx, split;
         if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
         const int n0 = GATE_UP ? n_idx * BN_HALF : n_idx * BN;
         const int kb0 = split * p.k_per_split, kb1 = min(k_blocks, kb0 + p.k_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status))) break;
-          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sa = tiles_base + stage * STAGE_SZ;
           const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, STAGE_BYTES);
-          tma_load_2d(sa, &map_a, full, kb * BK, row0);
-          tma_load_3d(sa + A_BYTES, &map_b0, full, n0, kb * BK, e);
-          if (GATE_UP) tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b1, full, n0, kb * BK, e);
-          else         tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b0, full, n0 + BN_HALF, kb * BK, e);
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted by the even CTA's barrier, which alone announces them
+            const uint32_t full_even = map_to_cta(full, 0);
+            if (rank == 0) mbar_expect_tx(full, 2 * PAIR_STAGE_BYTES);
+            tma_load_2d_pair(sa, &map_a, full_even, kb * BK, row0 + (int)rank * BM);
+            if (GATE_UP) tma_load_3d_pair(sa + A_BYTES, rank ? &map_b1 : &map_b0, full_even, n0, kb * BK, e);
+            else         tma_load_3d_pair(sa + A_BYTES, &map_b0, full_even, n0 + (int)rank * BN_HALF, kb * BK, e);
+          } else {
+            mbar_expect_tx(full, STAGE_BYTES);
+            tma_load_2d(sa, &map_a, full, kb * BK, row0);
+            tma_load_3d(sa + A_BYTES, &map_b0, full, n0, kb * BK, e);
+            if (GATE_UP) tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b1, full, n0, kb * BK, e);
+            else         tma_load_3d(sa + A_BYTES + B_HALF_BYTES, &map_b0, full, n0 + BN_HALF, kb * BK, e);
+          }
+          if (++stage == NSTAGE) stage = 0, phase ^= 1u;
+        }
+      }
+      if constexpr (PAIR) {
+        // the issuer's last commits arrive on this CTA's empty barriers from the other CTA: let them land
+        // before this CTA can leave
+        for (int i = 0; ok && i < NSTAGE; ++i) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
+          if (++stage == NSTAGE) stage = 0, phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
-      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0, TILE_ROWS};
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++local) {
         int e, row0, row_end, n_idx, split;
         if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
         const int kb0 = split * p.k_per_split, kb1 = min(k_blocks, kb0 + p.k_per_split);
@@ -201,17 +245,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
           tc_fence_after();
-          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sa = tiles_base + stage * STAGE_SZ;
           const uint64_t da = desc_kmajor(sa), db = desc_nmajor(sa + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // A: +32 bytes along K inside the swizzle atom; B: +32 K rows = 4096 bytes
-            mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+            if constexpr (PAIR) mma_f8_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC_PAIR, acc);
+            else                mma_f8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 256), IDESC, acc);
           }
-          mma_commit(bar_empty + 8 * stage);          // frees the stage when these MMAs retire
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
+          // frees the stage (in both CTAs of a pair) when these MMAs retire
+          if constexpr (PAIR) {
+            mma_commit_pair(bar_empty + 8 * stage);
+            mma_commit_pair(map_to_cta(bar_empty + 8 * stage, 1));
+          } else {
+            mma_commit(bar_empty + 8 * stage);
+          }
+          if (++stage == NSTAGE) stage = 0, phase ^= 1u;
         }
-        if (ok) mma_commit(bar_tfull + 8 * buf);       // accumulator complete
+        if (ok) {                                      // accumulator complete
+          if constexpr (PAIR) {
+            mma_commit_pair(bar_tfull + 8 * buf);
+            mma_commit_pair(map_to_cta(bar_tfull + 8 * buf, 1));
+          } else {
+            mma_commit(bar_tfull + 8 * buf);
+          }
+        }
       }
     }
   } else {
@@ -219,13 +278,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;                      // TMEM lane group this warp may read
     const int half = (warp - 2) >> 2;                  // which half of the tile's columns
     const int r_in_tile = quarter * 32 + lane;
-    TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0};
+    TileCursor cur{s_cum, p.offsets, p.E, p.n_tiles, 0, TILE_ROWS};
     uint32_t local = 0;
     bool ok = true;
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++local) {
       int e, row0, row_end, n_idx, split;
       if (!cur.locate(tile, e, row0, row_end, n_idx, split)) break;
+      row0 += (int)rank * BM;                          // this CTA's half of a pair's tile
       const uint32_t buf = local & 1u, use = local >> 1;
       ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
@@ -366,7 +426,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * buf, 0));
+        else                   mbar_arrive(bar_tempty + 8 * buf);
+      }
     }
   }
 
@@ -377,8 +440,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();       // neither CTA leaves while the other may still signal it
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else                tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 
@@ -652,14 +719,58 @@ SplitPlan choose_split(int M, int E, int k_blocks, int n_tiles) {
   return sp;
 }
 
+// Pairs pay when an expert's segment fills several 256-row tiles: below that the rows a pair computes past the
+// end of a segment outweigh what the halved weight traffic into shared memory saves.
+constexpr int kPairMinRowsPerExpert = 1024;
+bool pair_tiles_pay(bool gate_up, int M, int E) {
+  return !gate_up && M / E >= kPairMinRowsPerExpert && gemm_sm_budget() >= 2;
+}
+
 template <bool GATE_UP, bool RAW>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const GemmParams& p,
                 int M, cudaStream_t st) {
+  if constexpr (!RAW && !GATE_UP) {
+    if (pair_tiles_pay(GATE_UP, M, p.E)) {
+      static unsigned char smem_set[64] = {0};
+      BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, false, true>, PAIR_SMEM_BYTES, smem_set));
+      const long long max_tiles = (long long)(ceil_div(M, 2 * BM) + p.E) * p.n_tiles;
+      const int pairs = (int)std::min<long long>(gemm_sm_budget() / 2, max_tiles);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * pairs);
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      // pairs that can be resident at once (per device, asked once): the persistent loop needs no more
+      static int resident_pairs[64] = {0};
+      int dev = 0;
+      BWMOE_CUDA_OK(cudaGetDevice(&dev));
+      if (dev >= 0 && dev < 64) {
+        if (resident_pairs[dev] == 0) {
+          int n = 0;
+          cfg.gridDim = dim3(2 * (sm_count() / 2));
+          BWMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<GATE_UP, false, true>, &cfg));
+          BWMOE_REQUIRE(n >= 1, BWMOE_ERR_CUDA, "no CTA pair of the grouped GEMM fits on this device");
+          resident_pairs[dev] = n;
+        }
+        cfg.gridDim = dim3(2 * std::min(pairs, resident_pairs[dev]));
+      }
+      note_launch();
+      BWMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<GATE_UP, false, true>, ma, mb0, mb1, p));
+      return BWMOE_OK;
+    }
+  }
   static unsigned char smem_set[64] = {0};
-  BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, RAW>, SMEM_BYTES, smem_set));
+  BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, RAW, false>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  grouped_gemm_kernel<GATE_UP, RAW><<<grid, GEMM_THREADS, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
+  grouped_gemm_kernel<GATE_UP, RAW, false><<<grid, GEMM_THREADS, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

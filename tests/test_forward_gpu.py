@@ -189,3 +189,38 @@ def test_combine_by_reduction_in_the_down_epilogue(T, D, E, K, H):
     assert oracle.rel_l1(red.cpu(), ref) < 1e-2
     assert oracle.rel_l1(red.cpu(), det.cpu()) < 5e-3
     assert torch.equal(bw.fp8_moe_forward(*args, top_k=K), det)        # the default stays bit-reproducible
+
+
+def test_down_projection_on_cta_pairs_equals_single_cta_tiles():
+    """Segments of 1024 rows and more per expert run the down GEMM on two-CTA clusters with 256-row tiles.  The
+    same rows pushed below that mean by appending empty experts take the one-CTA path; K order and rounding are
+    the same, so the two results must agree bit for bit (ragged segment ends, a column count that is not a
+    multiple of the tile), and both must match an fp32 matmul of the decoded operands."""
+    from blackwell_moe_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(5)
+    M, H, D = 4133, 512, 640
+    seg = [0, 2100, M]
+    hq = (torch.randn(M, H, generator=g) * 40).clamp(-448, 448).to(FP8).to(dev)
+    wd = (torch.randn(8, H, D, generator=g) * 40).clamp(-448, 448).to(FP8).to(dev)
+    sh = (torch.rand(8, generator=g) * 50 + 10).to(dev)
+    sd = (torch.rand(8, generator=g) * 50 + 10).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    outs = []
+    for E in (2, 8):
+        offsets = torch.tensor(seg + [M] * (E - 2), dtype=torch.int32, device=dev)
+        y = torch.full((M, D), float("nan"), dtype=BF16, device=dev)
+        scratch = torch.empty(lib.bwmoe_gemm_scratch_bytes(M, D, H, E), dtype=torch.uint8, device=dev)
+        _lib.check(lib.bwmoe_down(hq.data_ptr(), offsets.data_ptr(), sh.data_ptr(), wd.data_ptr(), sd.data_ptr(),
+                                  M, D, H, E, y.data_ptr(), status.data_ptr(), scratch.data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        outs.append(y)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    ref = torch.empty(M, D, device=dev)
+    for e in range(2):
+        rows = slice(seg[e], seg[e + 1])
+        ref[rows] = (hq[rows].float() @ wd[e].float()) / (sh[e] * sd[e])
+    assert oracle.rel_l1(outs[0].float().cpu(), ref.cpu()) < 5e-3
