@@ -3,9 +3,12 @@
 PARITY UNPINNED for the FP8 arithmetic: the reference never multiplies
 block-scaled FP8 operands.  Its Qwen path dequantises the weights to bf16
 (src/blackwell_moe/runtime/qwen_patch.py:30-40) and runs ``F.linear`` per
-expert (qwen_patch.py:108-129).  What *is* pinned by a fixture is the
-weight-scale semantics: ``dequant_block_128`` must reproduce the reference's
-``_dequant_block_fp8`` bit for bit.  The rest of this file is our own
+expert (qwen_patch.py:108-129).  What *is* pinned by fixtures: the
+weight-scale semantics (``dequant_block_128`` must reproduce the reference's
+``_dequant_block_fp8`` bit for bit) and the block's output
+(``streaming_qwen_forward`` restates the reference's StreamingQwenMoE.forward
+and is checked against an output of that very method; the FP8 recipe must stay
+within the reference's stated ~7 % of it).  The rest of this file is our own
 definition of the recipe: weights carry one multiplicative inverse scale per
 128x128 block, activations one per token per 128 consecutive K elements, and
 the bf16 rounding points are those of the per-tensor recipe
@@ -132,4 +135,22 @@ def moe_forward_block_recipe(x, w_gate, wq_gate, wq_up, wq_down, inv_gate, inv_u
         intermediates.update(weights=weights, indices=indices, sort_perm=sort_perm,
                              inverse_idx=inverse_idx, offsets=offsets, xq=xq, x_inv=x_inv,
                              hq=hq_all, y_perm=y_perm)
+    return out
+
+
+def streaming_qwen_forward(x, weights, indices, hf_gate, hf_up, hf_down):
+    """The routed part of StreamingQwenMoE.forward (src/blackwell_moe/runtime/qwen_patch.py:98-134):
+    experts in ascending id, weights dequantised to bf16, ``F.linear`` in bf16, the weighted rows added
+    into a bf16 output one expert after the other.  ``hf_*[e]`` = ``(codes[out, in], scale_inv[out/128, in/128])``."""
+    out = torch.zeros_like(x)
+    for eid in torch.unique(indices).tolist():
+        pos = (indices == eid).nonzero(as_tuple=False)
+        token_idx, k_idx = pos[:, 0], pos[:, 1]
+        cur = x[token_idx]
+        deq = lambda pair: dequant_block_128(pair[0], pair[1])      # noqa: E731  ([out, in] orientation here)
+        gate = F.linear(cur, deq(hf_gate[eid]))
+        up = F.linear(cur, deq(hf_up[eid]))
+        y = F.linear(F.silu(gate) * up, deq(hf_down[eid]))
+        w = weights[token_idx, k_idx].unsqueeze(-1).to(y.dtype)
+        out.index_add_(0, token_idx, (y * w).to(out.dtype))
     return out

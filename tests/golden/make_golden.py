@@ -160,6 +160,73 @@ def expert_file_cases():
                         layer=np.int32(layer))
 
 
+def streaming_qwen_case():
+    """The reference's block-FP8 MoE block itself: StreamingQwenMoE.forward
+    (src/blackwell_moe/runtime/qwen_patch.py:98-134) run unmodified on CPU.  The module asks its reader
+    for an expert's raw FP8 weights and 128x128 inverse scales, dequantises them to bf16 and applies
+    F.linear per expert; here the reader serves seeded tensors from memory, the gate is the reference's
+    own top_k_router_ref, and the shared expert contributes zero.  Stored: inputs, HF-layout weights
+    ([out, in] codes, [out/128, in/128] scales), routing, and the block output."""
+    from blackwell_moe.kernels.routing import top_k_router_ref
+    from blackwell_moe.runtime.qwen_patch import StreamingQwenMoE
+    T, D, E, K, H = 96, 256, 16, 4, 384
+    g = gen(600)
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    w_gate = (torch.randn(D, E, generator=g) * 0.05).to(torch.bfloat16)
+
+    def block_quant(w):                        # [out, in] bf16 -> HF block FP8 (codes, weight_scale_inv)
+        o, i = w.shape
+        wf = w.float().view(o // 128, 128, i // 128, 128)
+        inv = (wf.abs().amax(dim=(1, 3)).clamp(min=1e-4) / 448.0).to(torch.float32)
+        q = (wf / inv[:, None, :, None]).clamp(-448, 448).view(o, i).to(torch.float8_e4m3fn)
+        return q, inv
+
+    store = {}
+    for e in range(E):
+        store[e] = {
+            "gate_proj": block_quant((torch.randn(H, D, generator=g) * 0.02).to(torch.bfloat16)),
+            "up_proj": block_quant((torch.randn(H, D, generator=g) * 0.02).to(torch.bfloat16)),
+            "down_proj": block_quant((torch.randn(D, H, generator=g) * 0.02).to(torch.bfloat16)),
+        }
+
+    class Reader:
+        def load_expert_fp8(self, expert_id, device="cuda"):
+            return store[int(expert_id)]
+
+    class Gate(torch.nn.Module):
+        def forward(self, h):
+            weights, indices = top_k_router_ref(h, w_gate, K)
+            return None, weights, indices.long()
+
+    class Zero(torch.nn.Module):
+        def __init__(self, width):
+            super().__init__()
+            self.width = width
+
+        def forward(self, h):
+            return torch.zeros(h.shape[0], self.width, dtype=h.dtype)
+
+    class Experts:
+        num_experts, hidden_dim = E, D
+
+    class Original(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate, self.shared_expert, self.shared_expert_gate = Gate(), Zero(D), Zero(1)
+            self.experts = Experts()
+
+    block = StreamingQwenMoE(Original(), layer_idx=0, reader=Reader(), cache_size=E)
+    with torch.no_grad():
+        y = block(x.view(1, T, D)).view(T, D)
+        weights, indices = top_k_router_ref(x, w_gate, K)
+    out = dict(x=bits(x), wg=bits(w_gate), y=bits(y), weights=weights.numpy(), indices=indices.numpy().astype(np.int32),
+               k=np.int32(K))
+    for name in ("gate_proj", "up_proj", "down_proj"):
+        out[name + "_q"] = np.stack([bits(store[e][name][0]) for e in range(E)])
+        out[name + "_inv"] = np.stack([store[e][name][1].numpy() for e in range(E)])
+    np.savez_compressed(OUT / "streaming_qwen.npz", **out)
+
+
 if __name__ == "__main__":
     import blackwell_moe
     print("reference version", blackwell_moe.__version__, "torch", torch.__version__)
@@ -168,5 +235,6 @@ if __name__ == "__main__":
     forward_cases()
     block_and_shared_cases()
     expert_file_cases()
+    streaming_qwen_case()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

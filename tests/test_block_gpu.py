@@ -1,8 +1,10 @@
 """128x128 block-scale recipe on the GPU against the CPU restatement (oracle.block).
 
 The reference has no FP8 kernel for this recipe (it dequantises to bf16), so the
-arithmetic itself is pinned only by our own oracle; what the reference does pin -
-the meaning of the weight scales - is covered by tests/test_oracle_golden.py.  Bars:
+FP8 arithmetic itself is pinned only by our own oracle; what the reference does pin -
+the meaning of the weight scales, and the bf16 output of its StreamingQwenMoE block on
+a block-FP8 checkpoint - is covered by tests/test_oracle_golden.py and by the last test
+here.  Bars:
 routing, permutation, activation codes and activation scales bit-exact; output
 within 1e-2 relative L1 of the block oracle and within ~7 % of the reference's bf16
 forward on the dequantised weights (what its Qwen path computes)."""
@@ -78,3 +80,26 @@ def test_block_weight_quantiser_matches_oracle():
         qo, so = oracle.quant_block_128(w[e])
         assert torch.equal(s[e].cpu(), so)
         assert torch.equal(q[e].cpu().view(torch.uint8), qo.view(torch.uint8))
+
+
+def test_block_forward_against_an_output_of_the_reference_module(golden):
+    """End to end on a block-FP8 checkpoint in the HF layout: weights through formats.from_hf_block_fp8, the
+    CUDA block path, and the result against the fixture written by the reference's own
+    StreamingQwenMoE.forward (src/blackwell_moe/runtime/qwen_patch.py:98-134), within the reference's stated
+    ~7 % FP8-versus-bf16 relative L1; routing must equal the reference's."""
+    import blackwell_moe_b200 as bw
+    from blackwell_moe_b200 import formats
+    from conftest import from_bits
+    g = golden("streaming_qwen")
+    E, K = g["gate_proj_q"].shape[0], int(g["k"])
+    x, w_gate = from_bits(g["x"], BF16).cuda(), from_bits(g["wg"], BF16).cuda()
+    packs = []
+    for n in ("gate_proj", "up_proj", "down_proj"):
+        q, inv = formats.from_hf_block_fp8([from_bits(g[n + "_q"][e], FP8) for e in range(E)],
+                                           [torch.from_numpy(g[n + "_inv"][e]) for e in range(E)])
+        packs += [q.cuda(), inv.cuda()]
+    qg, ig, qu, iu, qd, idn = packs
+    wt, idx = bw.top_k_router(x, w_gate, K)
+    assert torch.equal(idx.cpu().long(), torch.from_numpy(g["indices"]).long())
+    out = bw.fp8_moe_forward(x, w_gate, qg, qu, qd, ig, iu, idn, top_k=K)
+    assert oracle.rel_l1(out.cpu(), from_bits(g["y"], BF16)) < 7e-2

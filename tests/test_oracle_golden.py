@@ -137,3 +137,35 @@ def test_shared_expert_matches_reference(golden):
                                  from_bits(g["s_wd"], FP8), torch.from_numpy(g["s_sg"]), torch.from_numpy(g["s_su"]),
                                  torch.from_numpy(g["s_sd"]))
     assert oracle.rel_l1(y, from_bits(g["sy"], BF16)) < 2e-3
+
+
+def _streaming_qwen(g):
+    E = g["gate_proj_q"].shape[0]
+    hf = {name: [(from_bits(g[name + "_q"][e], FP8), torch.from_numpy(g[name + "_inv"][e])) for e in range(E)]
+          for name in ("gate_proj", "up_proj", "down_proj")}
+    return (from_bits(g["x"], BF16), from_bits(g["wg"], BF16), torch.from_numpy(g["weights"]),
+            torch.from_numpy(g["indices"]).long(), hf, from_bits(g["y"], BF16), int(g["k"]))
+
+
+def test_block_checkpoint_forward_matches_the_reference_module(golden):
+    """tests/golden/streaming_qwen.npz holds an output of the reference's StreamingQwenMoE.forward
+    (src/blackwell_moe/runtime/qwen_patch.py:98-134) on block-FP8 weights.  The restatement of that loop
+    must reproduce it (bf16 matmuls on CPU: equal up to the blocking of the host BLAS), routing included."""
+    x, w_gate, weights, indices, hf, y_ref, k = _streaming_qwen(golden("streaming_qwen"))
+    wt, idx = oracle.router_canonical(x, w_gate, k)
+    assert torch.equal(idx.long(), indices)
+    y = oracle.streaming_qwen_forward(x, weights, indices, hf["gate_proj"], hf["up_proj"], hf["down_proj"])
+    assert oracle.rel_l1(y, y_ref) < 2e-3
+
+
+def test_block_fp8_recipe_stays_within_the_stated_bound_of_the_reference_module(golden):
+    """The FP8 block recipe (128-wide activation groups, 128x128 weight blocks, FP8 products) against what
+    the reference computes for the same checkpoint in bf16: the reference's own FP8-versus-bf16 bound of
+    ~7 % relative L1 (docs/BENCH_v0.3.md:61-69)."""
+    from blackwell_moe_b200 import formats
+    x, w_gate, weights, indices, hf, y_ref, k = _streaming_qwen(golden("streaming_qwen"))
+    packs = [formats.from_hf_block_fp8([q for q, _ in hf[n]], [s for _, s in hf[n]])
+             for n in ("gate_proj", "up_proj", "down_proj")]
+    (qg, ig), (qu, iu), (qd, idn) = packs
+    y = oracle.moe_forward_block_recipe(x, w_gate, qg, qu, qd, ig, iu, idn, top_k=k)
+    assert oracle.rel_l1(y, y_ref) < 7e-2
