@@ -277,7 +277,10 @@ def time_region(fn, steps, stream, flush=None, each=False):
     `each`).  With `flush` (a buffer larger than L2) every call is timed on its own and the buffer is
     rewritten before it, so that nothing of the previous call is still L2-resident."""
     if flush is not None or each:
-        times = []
+        # Everything is queued first and read back after one synchronisation: the flush in front of a call
+        # gives the host the time to queue that call, so the events bracket device time even for forwards of
+        # a few launches (with a host synchronisation per call the device would wait for the host's launches).
+        marks = []
         for i in range(steps):
             if flush is not None:
                 flush.fill_(i & 0x7f)
@@ -285,8 +288,9 @@ def time_region(fn, steps, stream, flush=None, each=False):
             a.record(stream)
             fn()
             b.record(stream)
-            b.synchronize()
-            times.append(a.elapsed_time(b) / 1e3)
+            marks.append((a, b))
+        marks[-1][1].synchronize()
+        times = [a.elapsed_time(b) / 1e3 for a, b in marks]
         return times if each else sum(times)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)

@@ -197,7 +197,7 @@ def test_down_projection_on_cta_pairs_equals_single_cta_tiles():
     the same, so the two results must agree bit for bit (ragged segment ends, a column count that is not a
     multiple of the tile), and both must match an fp32 matmul of the decoded operands."""
     from blackwell_moe_b200 import _lib
-    lib = _lib.load()
+    lib = _lib.lib()
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(5)
     M, H, D = 4133, 512, 640
