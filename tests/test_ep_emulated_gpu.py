@@ -111,6 +111,7 @@ def _run(world, T, D, E, K, H, push):
 
 @pytest.mark.parametrize("push", [True, False], ids=["push", "pull"])
 @pytest.mark.parametrize("world,T,D,E,K,H", [(2, 96, 256, 8, 2, 256), (4, 150, 512, 16, 4, 384), (2, 700, 256, 4, 2, 128),
-                                             (8, 40, 256, 8, 2, 128)])
+                                             (8, 40, 256, 8, 2, 128),
+                                             (2, 2600, 256, 4, 2, 128)])      # 2600 rows per expert: paired down tiles
 def test_peer_kernels_with_ranks_played_on_one_gpu(world, T, D, E, K, H, push):
     _run(world, T, D, E, K, H, push)
