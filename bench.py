@@ -358,8 +358,14 @@ def sweep_rows(dev, stream, pk, flush, have=None):
             blk = have if (have is not None and have.name == workload) else Block(workload, dev)
         x, w_gate = blk.inputs(T)
         step = blk.step_fn(x, w_gate)
-        for _ in range(3):
+        # at least 3 forwards; rows of at most 1024 tokens (forwards of 0.1-0.5 ms) also at least 50 ms of them,
+        # or they would be timed while the clocks are still coming up from the idle the CPU arm leaves behind
+        t0, n_warm = time.perf_counter(), 0
+        while n_warm < 3 or (T <= 1024 and time.perf_counter() - t0 < 0.05):
             step()
+            n_warm += 1
+            if n_warm % 8 == 0:
+                torch.cuda.synchronize(dev)
         torch.cuda.synchronize(dev)
         ms = median(time_region(step, 10, stream, flush, each=True)) * 1e3
         g = graph_of(step, dev, stream)
