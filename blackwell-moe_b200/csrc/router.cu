@@ -11,25 +11,20 @@
 // summation, which bounds the error of a logit by about 20 * 2^-24 * sum|x_d * w_de|.
 // Tokens for which two neighbouring logits among ranks 1..K+1 are closer than twice that
 // bound are re-evaluated in fp64 by the whole block, so the chosen experts and their
-// order equal the exactly-rounded ones for every token.
+// order equal the exactly-rounded ones for every token.  The kernel for small batches
+// (router_token_kernel) accumulates in fp64 from the start and needs neither bound nor second pass.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace bwmoe {
 namespace {
+namespace cg = cooperative_groups;
 
 constexpr int kThreads = 256;
 constexpr int kChunk = 256;   // D elements staged per step
 constexpr int kInner = 16;    // products per plain-FMA block
 constexpr int kMaxEJ = 8;     // E <= 32 * kMaxEJ
-
-struct Cand {
-  float v;
-  int i;
-};
-// true when a ranks ahead of b: larger value, or equal value and lower id
-__device__ __forceinline__ bool ahead(const Cand& a, const Cand& b) {
-  return a.v > b.v || (a.v == b.v && a.i < b.i);
-}
 
 // Kahan step: (sum, comp) += y.  Kept out of reach of re-association by the intrinsics.
 __device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
@@ -39,54 +34,77 @@ __device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
   sum = t;
 }
 
+// Monotone map of a float onto unsigned integers (a < b  <=>  key(a) < key(b); -0 is folded onto +0 first).
+__device__ __forceinline__ unsigned order_key(float v) {
+  const unsigned u = __float_as_uint(v + 0.0f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float order_value(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
 // Top-K (+1) selection of one token by one warp.  Writes weights/indices; returns true when
 // two neighbouring selected logits (or the K-th and the best rejected one) are within thr.
-__device__ __forceinline__ bool select_token(const float* lg_row, int E, int K, float thr_rel, float thr_abs,
-                                             float* w_out, int32_t* i_out, int lane, float* cut_out = nullptr) {
-  float v[kMaxEJ];
+// Lane l holds the logits of experts l, l+32, ... (EJ of them); every round takes the best remaining
+// (value desc, id asc) with two warp-wide reductions: the largest key, then the lowest id that has it.
+template <int EJ>
+__device__ __forceinline__ bool select_token_regs(const float* lg_row, int E, int K, float thr_rel, float thr_abs,
+                                                  float* w_out, int32_t* i_out, int lane, float* cut_out) {
+  unsigned key[EJ];
   float lmax = 0.f;
 #pragma unroll
-  for (int j = 0; j < kMaxEJ; ++j) {
+  for (int j = 0; j < EJ; ++j) {
     const int ee = lane + 32 * j;
-    v[j] = ee < E ? lg_row[ee] : -INFINITY;
-    if (ee < E && fabsf(v[j]) < INFINITY) lmax = fmaxf(lmax, fabsf(v[j]));
+    const float v = ee < E ? lg_row[ee] : -INFINITY;
+    key[j] = ee < E ? order_key(v) : 0u;                 // 0 is below the key of every float
+    if (ee < E && fabsf(v) < INFINITY) lmax = fmaxf(lmax, fabsf(v));
   }
   for (int off = 16; off; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
   const float thr = thr_abs + lmax * thr_rel;
-  unsigned taken = 0;
   bool ambiguous = false;
   float prev = 0.f;
-  Cand chosen = {0.f, 0};   // lane i keeps the i-th selected (value, id)
+  float chosen_v = 0.f;                                   // lane i keeps the i-th selected (value, id)
+  int chosen_i = 0;
   const int rounds = K < E ? K + 1 : K;
   for (int it = 0; it < rounds; ++it) {
-    Cand best = {-INFINITY, 0x7fffffff};
+    unsigned bk = 0u;
+    int bj = 0;
 #pragma unroll
-    for (int j = 0; j < kMaxEJ; ++j) {
-      const Cand c = {v[j], lane + 32 * j};
-      if (!((taken >> j) & 1u) && lane + 32 * j < E && ahead(c, best)) best = c;
+    for (int j = 0; j < EJ; ++j)                          // ids ascend with j: the first maximum is the lowest id
+      if (key[j] > bk) bk = key[j], bj = j;
+    const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+    const unsigned mine = (bk == top && top != 0u) ? (unsigned)(lane + 32 * bj) : 0x7fffffffu;
+    const int bi = (int)__reduce_min_sync(0xffffffffu, mine);
+    const float bv = order_value(top);
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < EJ; ++j)
+        if (j == (bi >> 5)) key[j] = 0u;                  // taken
     }
-    for (int off = 16; off; off >>= 1) {
-      const Cand o = {__shfl_xor_sync(0xffffffffu, best.v, off), __shfl_xor_sync(0xffffffffu, best.i, off)};
-      if (ahead(o, best)) best = o;
-    }
-    if ((best.i & 31) == lane) taken |= 1u << (best.i >> 5);
-    if (it > 0 && prev - best.v <= thr) ambiguous = true;
-    prev = best.v;
-    if (it < K && lane == it) chosen = best;
+    if (it > 0 && prev - bv <= thr) ambiguous = true;
+    prev = bv;
+    if (it < K && lane == it) chosen_v = bv, chosen_i = bi;
   }
   // Experts whose approximate logit lies below this cannot reach the top K whatever the rounding did
   // (prev is the best rejected logit, or the K-th one when K == E).
   if (cut_out != nullptr && lane == 0) *cut_out = prev - thr;
   // weights: softmax over the selected logits == softmax over all experts, renormalised
-  const float top = __shfl_sync(0xffffffffu, chosen.v, 0);
-  const float p = lane < K ? expf(chosen.v - top) : 0.f;
+  const float top = __shfl_sync(0xffffffffu, chosen_v, 0);
+  const float p = lane < K ? expf(chosen_v - top) : 0.f;
   float z = p;
   for (int off = 16; off; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
   if (lane < K) {
     w_out[lane] = p / z;
-    i_out[lane] = chosen.i;
+    i_out[lane] = chosen_i;
   }
   return ambiguous;
+}
+__device__ __forceinline__ bool select_token(const float* lg_row, int E, int K, float thr_rel, float thr_abs,
+                                             float* w_out, int32_t* i_out, int lane, float* cut_out = nullptr) {
+  if (E <= 32) return select_token_regs<1>(lg_row, E, K, thr_rel, thr_abs, w_out, i_out, lane, cut_out);
+  if (E <= 64) return select_token_regs<2>(lg_row, E, K, thr_rel, thr_abs, w_out, i_out, lane, cut_out);
+  if (E <= 128) return select_token_regs<4>(lg_row, E, K, thr_rel, thr_abs, w_out, i_out, lane, cut_out);
+  return select_token_regs<kMaxEJ>(lg_row, E, K, thr_rel, thr_abs, w_out, i_out, lane, cut_out);
 }
 
 // Exact logits of one token in fp64 by the whole block, then rounded once to fp32.
@@ -153,174 +171,120 @@ __device__ void exact_logits_block(const __nv_bfloat16* __restrict__ xrow, const
   __syncthreads();
 }
 
-// Exact logits of at most 32 listed experts of one token (fp64, whole block), rounded once to fp32;
-// every other expert's logit becomes -inf.  Threads are laid out as (candidate, d-group); partial sums
-// meet in a fixed order (shuffle tree inside the warp, then warp by warp).
-__device__ void exact_candidates_block(const __nv_bfloat16* __restrict__ xrow, const __nv_bfloat16* __restrict__ wg,
-                                       int D, int E, const int* cand /* smem */, int n_cand, float* lg_row,
-                                       double* dpart /* smem [nwarps][32] */) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
-  int P = 1;
-  while (P < n_cand) P <<= 1;                  // lanes per d, a power of two <= 32
-  const int c = tid % P, dg = tid / P, NG = nthreads / P;
-  double a = 0.0;
-  if (c < n_cand) {
-    const int e = cand[c];
-#pragma unroll 4
-    for (int d = dg; d < D; d += NG)
-      a = fma((double)__bfloat162float(xrow[d]), (double)__bfloat162float(wg[(size_t)d * E + e]), a);
-  }
-  for (int off = P; off < 32; off <<= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-  if (lane < P) dpart[warp * 32 + lane] = a;
-  for (int e = tid; e < E; e += nthreads) lg_row[e] = -INFINITY;
-  __syncthreads();
-  if (tid < n_cand) {
-    double sum = 0.0;
-    for (int w = 0; w < nwarps; ++w) sum += dpart[w * 32 + tid];
-    lg_row[cand[tid]] = (float)sum;
-  }
-  __syncthreads();
-}
-
 // ---------------------------------------------------------------------------------------
-// One block per token: threads = (expert octet, d-group).  Used when the gate is narrow
-// (E <= 16: the whole w_gate stays in L1) or the batch is small (decode), where tiling
-// tokens buys nothing and what matters is many loads in flight.
+// One thread-block cluster per token, for small batches (decode): threads = (expert octet, d-group), the
+// d-groups spread over the 1-8 CTAs of the cluster so that a few tokens still pull the gate matrix through
+// many SMs at once.  The products (exact in fp32) are accumulated in fp64 - a few thousand DFMAs per SM
+// disappear behind the loads here - so the sums ARE the exact logits, rounded once to fp32: no error
+// bound, no tie detection, no second pass.  Every CTA reduces its own share in a fixed shuffle tree to
+// partial logits in its shared memory; after a cluster barrier CTA 0 adds the partials of its peers in
+// rank order (distributed shared memory) and selects.
 // ---------------------------------------------------------------------------------------
+constexpr int kTokenSmemBytes = 32 * 256 * (int)sizeof(double);     // per-warp partial logits
 __global__ void __launch_bounds__(1024)
 router_token_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int T, int D,
                     int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
                     float* __restrict__ row_amax) {
-  __shared__ __align__(16) float part[32][256];     // per-warp partial logits (reused for fp64 partials)
+  extern __shared__ __align__(16) double token_part[];          // [nwarps][256]
+  __shared__ double lgd[256];                                   // this CTA's partial logits
   __shared__ float lg[256];
-  __shared__ double dsum[256];
-  __shared__ float s_stat[3][32];
-  __shared__ float s_wsq[256];        // squared column norms of w_gate
-  __shared__ int s_amb, s_ncand, s_cand[32];
-  __shared__ float s_cut;
+  __shared__ float s_max[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const int tok = blockIdx.x;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  const int tok = blockIdx.x / C;
   const __nv_bfloat16* xrow = x + (size_t)tok * D;
   int V = 1;
   while (V < E / 8) V <<= 1;
-  const int ev = tid % V, dg = tid / V, NG = blockDim.x / V;
+  const int NG = blockDim.x / V;                          // d-groups of this CTA
+  const int ev = tid % V, dg = rank * NG + tid / V;       // d-group among those of the whole cluster
   const bool ev_ok = ev < E / 8;
 
-  float acc[8], comp[8], inner[8], wsq[8];
+  double acc[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f, comp[j] = 0.f, inner[j] = 0.f, wsq[j] = 0.f;
-  float xsq = 0.f, xmax = 0.f;
-  int inner_n = 0;
-  for (int e = tid; e < 256; e += blockDim.x) s_wsq[e] = 0.f;
-  __syncthreads();
-  // kLoads loads are issued before any of them is used: with one token per block the loop is a chain of
-  // memory round trips otherwise.  Padding steps multiply by zero and change nothing.
-  constexpr int kLoads = 8;
-  static_assert(kInner % kLoads == 0, "a Kahan step closes a whole number of load batches");
-  for (int d0 = dg; d0 < D; d0 += NG * kLoads) {
-    float xv[kLoads];
-    uint4 raw[kLoads];
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0;
+  float xmax = 0.f;
+  // A step of a thread: 8 consecutive d (one 16-byte load of x) against its expert octet in those 8 gate rows,
+  // so a warp reads whole runs of consecutive rows and all eight row loads are issued before the first is
+  // used.  Rows past D multiply by zero and change nothing.
+  const bool vec_x = (reinterpret_cast<uintptr_t>(xrow) & 15u) == 0 && D % 8 == 0;
+  for (int d = dg * 8; d < D; d += NG * C * 8) {
+    float xv[8];
+    uint4 raw[8];
+    if (vec_x) {
+      const uint4 xr = *reinterpret_cast<const uint4*>(xrow + d);
+      const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xr);
 #pragma unroll
-    for (int u = 0; u < kLoads; ++u) {
-      const int d = d0 + u * NG;
-      const bool ok = d < D;
-      xv[u] = ok ? __bfloat162float(xrow[d]) : 0.f;
-      raw[u] = (ok && ev_ok) ? *reinterpret_cast<const uint4*>(wg + (size_t)d * E + 8 * ev) : make_uint4(0u, 0u, 0u, 0u);
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(px[q]);
+        xv[2 * q] = f.x, xv[2 * q + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) xv[q] = d + q < D ? __bfloat162float(xrow[d + q]) : 0.f;
     }
 #pragma unroll
-    for (int u = 0; u < kLoads; ++u) {
-      if (ev == 0) {
-        xsq = fmaf(xv[u], xv[u], xsq);
-        xmax = fmaxf(xmax, fabsf(xv[u]));
-      }
-      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+    for (int q = 0; q < 8; ++q)
+      raw[q] = (d + q < D && ev_ok) ? *reinterpret_cast<const uint4*>(wg + (size_t)(d + q) * E + 8 * ev)
+                                    : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (ev == 0) xmax = fmaxf(xmax, fabsf(xv[q]));
+      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&raw[q]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(pw[j]);
-        wsq[2 * j] = fmaf(f.x, f.x, wsq[2 * j]);
-        wsq[2 * j + 1] = fmaf(f.y, f.y, wsq[2 * j + 1]);
-        inner[2 * j] = fmaf(xv[u], f.x, inner[2 * j]);
-        inner[2 * j + 1] = fmaf(xv[u], f.y, inner[2 * j + 1]);
+        // a bf16 x bf16 product has 16 significant bits: exact in fp32, and unchanged by the conversion
+        acc[2 * j] += (double)__fmul_rn(xv[q], f.x);
+        acc[2 * j + 1] += (double)__fmul_rn(xv[q], f.y);
       }
     }
-    inner_n += kLoads;
-    if (inner_n == kInner) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        kahan_add(acc[j], comp[j], inner[j]);
-        inner[j] = 0.f;
-      }
-      inner_n = 0;
-    }
   }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    kahan_add(acc[j], comp[j], inner[j]);
-    acc[j] = __fsub_rn(acc[j], comp[j]);
-  }
-  // d-groups inside the warp: plain shuffle tree (at most 5 roundings per logit)
+  // d-groups inside the warp, then the warps, then the CTAs: one fixed tree, so the result is reproducible
   for (int off = V; off < 32; off <<= 1) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
-      wsq[j] += __shfl_xor_sync(0xffffffffu, wsq[j], off);
-    }
+    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
   }
   if (lane < V && ev_ok) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      part[warp][8 * ev + j] = acc[j];
-      atomicAdd(&s_wsq[8 * ev + j], wsq[j]);     // only feeds the tie threshold: order does not matter
+    for (int j = 0; j < 8; ++j) token_part[warp * 256 + 8 * ev + j] = acc[j];
+  }
+  for (int off = 16; off; off >>= 1) xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
+  if (lane == 0) s_max[warp] = xmax;
+  __syncthreads();
+  // warp w sums experts w, w + nwarps, ...; lane l brings warp l's part
+  for (int e = warp; e < E; e += nwarps) {
+    double v = lane < nwarps ? token_part[lane * 256 + e] : 0.0;
+    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) lgd[e] = v;
+  }
+  if (C > 1) {
+    cluster.sync();
+    if (rank == 0) {
+      for (int e = tid; e < E; e += blockDim.x) {
+        double v = lgd[e];
+        for (int r = 1; r < C; ++r) v += cluster.map_shared_rank(lgd, r)[e];
+        lg[e] = (float)v;                                 // the one rounding to fp32
+      }
+      if (tid < nwarps) {
+        float m = s_max[tid];
+        for (int r = 1; r < C; ++r) m = fmaxf(m, cluster.map_shared_rank(s_max, r)[tid]);
+        s_max[tid] = m;
+      }
     }
+    cluster.sync();                     // the peers' shared memory has been read: they may leave
+    if (rank != 0) return;
+  } else {
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) lg[e] = (float)lgd[e];
+    __syncthreads();
   }
-  for (int off = 16; off; off >>= 1) {
-    xsq += __shfl_xor_sync(0xffffffffu, xsq, off);
-    xmax = fmaxf(xmax, __shfl_xor_sync(0xffffffffu, xmax, off));
-  }
-  if (lane == 0) s_stat[0][warp] = xsq, s_stat[1][warp] = xmax;
-  __syncthreads();
-  // warps: compensated sum in a fixed order
-  for (int e = tid; e < E; e += blockDim.x) {
-    float sm = 0.f, c = 0.f;
-    for (int w = 0; w < nwarps; ++w) kahan_add(sm, c, part[w][e]);
-    lg[e] = __fsub_rn(sm, c);
-  }
-  float x_sq = 0.f, m_tok = 0.f, w_sq = 0.f;
-  for (int w = 0; w < nwarps; ++w) {
-    x_sq += s_stat[0][w];
-    m_tok = fmaxf(m_tok, s_stat[1][w]);
-  }
-  for (int e = 0; e < E; ++e) w_sq = fmaxf(w_sq, s_wsq[e]);
-  // Cauchy-Schwarz: sum_d |x_d w_de| <= |x|_2 * |w_e|_2
-  const float xw_bound = sqrtf(x_sq) * sqrtf(w_sq) * 1.001f;
-  __syncthreads();
-  // blocks of kInner FMAs + compensated outer sum (2) + in-warp tree (<=5) + compensated warp sum (2)
-  const float gamma = (float)(kInner + 10) * 5.9604645e-8f * 1.05f;
   if (warp == 0) {
-    const bool amb = select_token(lg, E, K, 1.0e-6f, 2.f * gamma * xw_bound, weights + (size_t)tok * K,
-                                  indices + (size_t)tok * K, lane, &s_cut);
-    if (lane == 0) {
-      s_amb = amb ? 1 : 0;
-      s_ncand = 0;
-      if (row_amax != nullptr) row_amax[tok] = m_tok;
-    }
-  }
-  __syncthreads();
-  if (!s_amb) return;
-  // near tie: only the experts that can still reach the top K are evaluated exactly
-  for (int e = tid; e < E; e += blockDim.x) {
-    if (lg[e] >= s_cut) {
-      const int slot = atomicAdd(&s_ncand, 1);
-      if (slot < 32) s_cand[slot] = e;
-    }
-  }
-  __syncthreads();
-  if (s_ncand <= 32)
-    exact_candidates_block(xrow, wg, D, E, s_cand, s_ncand, lg, reinterpret_cast<double*>(&part[0][0]));
-  else
-    exact_logits_block(xrow, wg, D, E, lg, dsum);
-  if (warp == 0)
+    float m_tok = lane < nwarps ? s_max[lane] : 0.f;
+    for (int off = 16; off; off >>= 1) m_tok = fmaxf(m_tok, __shfl_xor_sync(0xffffffffu, m_tok, off));
     select_token(lg, E, K, 0.f, -1.f, weights + (size_t)tok * K, indices + (size_t)tok * K, lane);
+    if (lane == 0 && row_amax != nullptr) row_amax[tok] = m_tok;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -675,9 +639,32 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
   if (vec_gate && vec_x && E <= 16 && T >= 1024) {
     router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, counted(st)>>>(xp, wp, T, D, E, K, weights,
                                                                                  indices, row_amax);
-  } else if (vec_gate && T < 1024) {
-    const int threads = (E >= 128 || T <= 64) ? 1024 : 256;   // few tokens: spread each row over more threads
-    router_token_kernel<<<T, threads, 0, counted(st)>>>(xp, wp, T, D, E, K, weights, indices, row_amax);
+  } else if (vec_gate && T < 1024 && (long long)T * E * D <= (1ll << 26)) {      // fp64 sums: small batches only
+    // Few tokens: a cluster of up to 8 CTAs per token (as many as keep the grid within the SMs), and enough
+    // threads that every (expert octet, 8 consecutive d) pair has a thread of its own where that fits.
+    static unsigned char smem_set[64] = {0};
+    BWMOE_CUDA_OK(ensure_dynamic_smem(router_token_kernel, kTokenSmemBytes, smem_set));
+    int C = 1;
+    while (C < 8 && T * C * 2 <= sm_count()) C *= 2;
+    int V = 1;
+    while (V < E / 8) V <<= 1;
+    int threads = 256;
+    while (threads < 1024 && (long long)threads * C < (long long)V * ceil_div(D, 8)) threads *= 2;
+    if (T > 64 && E < 128) threads = 256;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(T * C));
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = kTokenSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    note_launch();
+    BWMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, router_token_kernel, xp, wp, T, D, E, K, weights, indices, row_amax));
   } else if (T >= 2048) {
     constexpr int TOK = 16;
     router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, counted(st)>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
