@@ -198,4 +198,13 @@ int launch_scatter_rows_group_peers(const void* xq_tok, const float* inv_tok, co
                                     int experts_per_rank, void* const* xq_of_rank, void* const* inv_of_rank,
                                     int n_ranks, int rows_cap, int32_t* status, cudaStream_t st);
 
+// Monotone map of a float onto unsigned integers (a < b  <=>  key(a) < key(b); -0 is folded onto +0 first).
+__device__ __forceinline__ unsigned order_key(float v) {
+  const unsigned u = __float_as_uint(v + 0.0f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float order_value(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
 }  // namespace bwmoe

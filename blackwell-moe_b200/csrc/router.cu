@@ -34,15 +34,6 @@ __device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
   sum = t;
 }
 
-// Monotone map of a float onto unsigned integers (a < b  <=>  key(a) < key(b); -0 is folded onto +0 first).
-__device__ __forceinline__ unsigned order_key(float v) {
-  const unsigned u = __float_as_uint(v + 0.0f);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float order_value(unsigned k) {
-  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
-}
-
 // Top-K (+1) selection of one token by one warp.  Writes weights/indices; returns true when
 // two neighbouring selected logits (or the K-th and the best rejected one) are within thr.
 // Lane l holds the logits of experts l, l+32, ... (EJ of them); every round takes the best remaining

@@ -245,32 +245,33 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   // ---- the best tensor-core logits, sorted by (value desc, id asc): lane j keeps entry j.  The list
   //      stops at 12 entries, or earlier once an entry past the K-th falls below kth - 2t: nothing
   //      after it can be a candidate. ----
-  float v[EJ];
+  // (two warp-wide reductions per entry: the largest order-preserving key, then the lowest id that has it)
+  unsigned key[EJ];
 #pragma unroll
   for (int j = 0; j < EJ; ++j) {
     const int e = lane + 32 * j;
-    v[j] = e < E ? logits[(size_t)tok * ld_logits + e] : -INFINITY;
+    key[j] = e < E ? order_key(logits[(size_t)tok * ld_logits + e]) : 0u;      // 0: below every float's key
   }
   float cv = -INFINITY;
   int ci = 0x7fffffff;
-  unsigned taken = 0;
   const int n_max = E < L_CAND ? E : L_CAND;
   int n_list = 0;
   float kth_tc = 0.f;
   for (int it = 0; it < n_max; ++it) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
+    unsigned bk = 0u;
+    int bj = 0;
 #pragma unroll
-    for (int j = 0; j < EJ; ++j) {
-      const int e = lane + 32 * j;
-      if (!((taken >> j) & 1u) && e < E && (v[j] > bv || (v[j] == bv && e < bi))) bv = v[j], bi = e;
+    for (int j = 0; j < EJ; ++j)                          // ids ascend with j: the first maximum is the lowest id
+      if (key[j] > bk) bk = key[j], bj = j;
+    const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+    const unsigned mine = (bk == top && top != 0u) ? (unsigned)(lane + 32 * bj) : 0x7fffffffu;
+    const int bi = (int)__reduce_min_sync(0xffffffffu, mine);
+    const float bv = order_value(top);
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < EJ; ++j)
+        if (j == (bi >> 5)) key[j] = 0u;                  // taken
     }
-    for (int off = 16; off; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
-    }
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
     if (lane == it) cv = bv, ci = bi;
     n_list = it + 1;
     if (it == K - 1) kth_tc = bv;
