@@ -419,7 +419,8 @@ int bwmoe_combine(const void* d_y, const int32_t* d_pos, const float* d_weights,
 /*
  * Expert-parallel transport over peer memory (one process per GPU, the buffers of every rank mapped
  * into each process; the host pointer arrays hold one device pointer per rank).  No counterpart in
- * the reference, which is single-GPU (its docs/DESIGN.md:24 names expert parallelism as future work).
+ * the reference, which is single-GPU (the design notes under its docs/ directory name expert parallelism as
+ * future work).
  *
  * bwmoe_scatter_quant_peers: quantise the token rows (as bwmoe_gather_quant does) and store the row of
  *   slot (t,k), routed to expert e, into row d_pos[t*K+k] + d_delta[e] of the receive buffer of rank
