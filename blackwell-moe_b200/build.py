@@ -20,7 +20,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libbwmoe.so"
-SOURCES = ["api.cu", "router.cu", "permute_quant.cu", "grouped_gemm_sm100.cu", "grouped_gemm_block_sm100.cu",
+SOURCES = ["api.cu", "router.cu", "permute_quant.cu", "grouped_gemm_sm100.cu", "grouped_gemm_block_sm100.cu", "grouped_gemm_block_small_sm100.cu",
            "router_tc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

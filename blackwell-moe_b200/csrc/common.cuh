@@ -186,6 +186,14 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
                               cudaStream_t st);
 int launch_quant_scatter_group(const void* x, const int32_t* pos, int T, int D, int K, void* xq, float* x_inv,
                                cudaStream_t st);
+// Small batches of the block-scale recipe (a handful of rows per expert): operand-swapped tiles, see
+// grouped_gemm_block_small_sm100.cu.  launch_gateup_block / launch_down_block pick them by themselves.
+bool block_small_applicable(int M, int Kdim, int E);
+int launch_gateup_block_small(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
+                              const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq,
+                              float* h_inv, int32_t* status, cudaStream_t st);
+int launch_down_block_small(const void* hq, const float* h_inv, const int32_t* offsets, const void* wd,
+                            const float* inv_d, int M, int D, int H, int E, void* y, int32_t* status, cudaStream_t st);
 int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offsets, const void* wg, const void* wu,
                         const float* inv_g, const float* inv_u, int M, int D, int H, int E, void* hq, float* h_inv,
                         int32_t* status, cudaStream_t st);

@@ -25,6 +25,8 @@
 // never lands in a buffer the partner warp of the same rows may still read), and the per-K-block
 // weight scales of a tile sit in registers, one K block per lane, broadcast by a shuffle.
 // Every barrier wait is bounded exactly as in the per-tensor kernel.
+// Batches with a handful of rows per expert go to the operand-swapped kernel of
+// grouped_gemm_block_small_sm100.cu instead (the launchers at the end of this file decide).
 #include "sm100_gemm.cuh"
 
 namespace bwmoe {
@@ -676,6 +678,8 @@ int launch_gateup_block(const void* xq, const float* x_inv, const int32_t* offse
   if (int rc = check_block("gateup_block", M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(xq) && aligned16(hq) && aligned16(wg) && aligned16(wu), BWMOE_ERR_BAD_ALIGN,
                 "gateup_block: pointers must be 16-byte aligned");
+  if (block_small_applicable(M, D, E))
+    return launch_gateup_block_small(xq, x_inv, offsets, wg, wu, inv_g, inv_u, M, D, H, E, hq, h_inv, status, st);
   CUtensorMap ma, mg, mu;
   if (int rc = make_map_a(&ma, xq, M, D)) return rc;
   if (int rc = make_map_b(&mg, wg, E, D, H)) return rc;
@@ -692,6 +696,8 @@ int launch_down_block(const void* hq, const float* h_inv, const int32_t* offsets
   if (int rc = check_block("down_block", M, D, H, E)) return rc;
   BWMOE_REQUIRE(aligned16(hq) && aligned16(y) && aligned16(wd), BWMOE_ERR_BAD_ALIGN,
                 "down_block: pointers must be 16-byte aligned");
+  if (route == nullptr && block_small_applicable(M, H, E))
+    return launch_down_block_small(hq, h_inv, offsets, wd, inv_d, M, D, H, E, y, status, st);
   CUtensorMap ma, mb;
   if (int rc = make_map_a(&ma, hq, M, H)) return rc;
   if (int rc = make_map_b(&mb, wd, E, H, D)) return rc;

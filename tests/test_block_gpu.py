@@ -103,3 +103,47 @@ def test_block_forward_against_an_output_of_the_reference_module(golden):
     assert torch.equal(idx.cpu().long(), torch.from_numpy(g["indices"]).long())
     out = bw.fp8_moe_forward(x, w_gate, qg, qu, qd, ig, iu, idn, top_k=K)
     assert oracle.rel_l1(out.cpu(), from_bits(g["y"], BF16)) < 7e-2
+
+
+def test_small_batch_tiles_equal_large_batch_tiles():
+    """A handful of rows per expert takes the operand-swapped kernel (weights on the M side, 32 tokens on the
+    N side); the same rows with fewer, fuller experts' worth of segments per expert count take the 128-row
+    tiles.  Products, K order, scale products and rounding points are the same, so codes, group scales and
+    result rows must agree bit for bit (ragged segments, an empty expert, H and D not multiples of the tile)."""
+    from blackwell_moe_b200 import _lib
+    lib = _lib.lib()
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(9)
+    D, H, E_small, E_big = 384, 320, 16, 4
+    seg = [0, 37, 37, 70, 96]                                  # rows of experts 0..3 (expert 1 empty)
+    M = seg[-1]
+    x = (torch.randn(M, D, generator=g)).to(BF16).to(dev)
+    st = torch.cuda.current_stream().cuda_stream
+    nd, nh = (D + 127) // 128, (H + 127) // 128
+    xq, x_inv = torch.empty(M, D, dtype=torch.uint8, device=dev), torch.empty(M, nd, dtype=torch.float32, device=dev)
+    _lib.check(lib.bwmoe_gather_quant_group(x.data_ptr(), None, M, D, 1, xq.data_ptr(), x_inv.data_ptr(), st))
+    packs = {}
+    for name, (a, b) in (("gate", (D, H)), ("up", (D, H)), ("down", (H, D))):
+        qs, ss = zip(*[oracle.quant_block_128((torch.randn(a, b, generator=g) * 0.05).to(BF16)) for _ in range(E_small)])
+        packs[name] = (torch.stack(qs).to(dev), torch.stack(ss).to(dev))
+    results = []
+    for E in (E_big, E_small):        # 24 rows per expert: 128-row tiles; 6 rows per expert: 32-token tiles
+        offsets = torch.tensor(seg + [M] * (E - 4), dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        hq = torch.full((M, H), 0x7f, dtype=torch.uint8, device=dev)
+        h_inv = torch.full((M, nh), -1.0, dtype=torch.float32, device=dev)
+        y = torch.full((M, D), float("nan"), dtype=BF16, device=dev)
+        (qg, ig), (qu, iu), (qd, idn) = packs["gate"], packs["up"], packs["down"]
+        _lib.check(lib.bwmoe_gateup_swiglu_block(xq.data_ptr(), x_inv.data_ptr(), offsets.data_ptr(), qg.data_ptr(),
+                                                 qu.data_ptr(), ig.data_ptr(), iu.data_ptr(), M, D, H, E,
+                                                 hq.data_ptr(), h_inv.data_ptr(), status.data_ptr(), st))
+        _lib.check(lib.bwmoe_down_block(hq.data_ptr(), h_inv.data_ptr(), offsets.data_ptr(), qd.data_ptr(),
+                                        idn.data_ptr(), M, D, H, E, y.data_ptr(), status.data_ptr(), st))
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        results.append((hq, h_inv, y))
+    (hq_a, inv_a, y_a), (hq_b, inv_b, y_b) = results
+    assert torch.equal(hq_a, hq_b)
+    assert torch.equal(inv_a, inv_b)
+    assert torch.equal(y_a.view(torch.int16), y_b.view(torch.int16))
+    assert torch.isfinite(y_a.float()).all()
