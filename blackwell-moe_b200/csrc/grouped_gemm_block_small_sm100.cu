@@ -6,10 +6,12 @@
 //
 //   D^T[128 output features (tensor-memory lanes), 32 tokens (columns)] += W^T[features, k] * X^T[k, tokens]
 //
-// A = the weight tile exactly as the large-batch kernel stages it ([128 k][128 features], feature-contiguous,
-// read MN-major), B = 32 activation rows (K-major).  One K block of a tile is 128 x 32 (gate/up: 2 x 32)
-// accumulators, so tensor memory holds a ring of eight K blocks and the fold is 32 (64) FMAs per thread per K
-// block with the same arithmetic as the large-batch kernel: acc += partial * (a_inv[row,kb] * w_inv[kb,nb]).
+// A = a weight tile exactly as the large-batch kernel stages it ([128 k][128 features], feature-contiguous,
+// read MN-major), B = 32 activation rows (K-major).  A tile has two weight tiles that share the activation
+// rows - the gate and the up tile of 128 h columns, or two neighbouring 128-feature tiles of the down
+// projection (256 contiguous bytes of every weight row) - so one K block is 2 x (128 x 32) accumulators, tensor
+// memory holds a ring of eight K blocks and the fold is 64 FMAs per thread per K block with the same
+// arithmetic as the large-batch kernel: acc += partial * (a_inv[row,kb] * w_inv[kb,nb]).
 // Same roles as there (reference: src/blackwell_moe/runtime/qwen_patch.py:108-129 computes these products
 // in bf16 after dequantising).
 //
@@ -28,16 +30,14 @@ constexpr int S_NT = 32;                          // token columns per tile
 constexpr int S_THREADS = 192;
 constexpr int S_FOLD_WARP0 = 2;
 constexpr int S_X_BYTES = S_NT * BK;              // 4 KiB: 32 rows x 128 K bytes
-constexpr int S_BUF_COLS = 64;                    // gate 32 | up 32 (down tiles use the first 32)
+constexpr int S_BUF_COLS = 64;                    // gate 32 | up 32, or the two feature tiles of a down tile
 constexpr int S_NBUF = TMEM_COLS / S_BUF_COLS;    // 8 K blocks in flight in tensor memory
 constexpr int S_KB_MAX = 32;                      // K blocks per tile (one weight scale per lane)
 constexpr float kSmallAmaxFloor = 1e-4f;
-template <bool GATE_UP>
-struct SmallShape {
-  static constexpr int kStageBytes = (GATE_UP ? 2 : 1) * B_HALF_BYTES + S_X_BYTES;   // 36 / 20 KiB
-  static constexpr int kStages = GATE_UP ? 5 : 8;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
-};
+constexpr int S_W_BYTES = 2 * B_HALF_BYTES;                   // two weight tiles per stage
+constexpr int S_STAGE_BYTES = S_W_BYTES + S_X_BYTES;          // 36 KiB
+constexpr int S_STAGES = 5;
+constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 // D=f32, A=B=e4m3, A MN-major (the weight tile), B K-major (the activation rows), N=32, M=128
 constexpr uint32_t IDESC_SMALL = (1u << 4) | (1u << 15) | ((uint32_t)(S_NT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
@@ -81,9 +81,10 @@ template <bool GATE_UP>
 __global__ void __launch_bounds__(S_THREADS, 1)
 block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
                         const __grid_constant__ CUtensorMap map_w1, const SmallParams p) {
-  constexpr int NSTAGE = SmallShape<GATE_UP>::kStages;
-  constexpr int STAGE_SZ = SmallShape<GATE_UP>::kStageBytes;
-  constexpr int W_BYTES = (GATE_UP ? 2 : 1) * B_HALF_BYTES;
+  constexpr int NSTAGE = S_STAGES;
+  constexpr int STAGE_SZ = S_STAGE_BYTES;
+  constexpr int W_BYTES = S_W_BYTES;
+  constexpr int FT_COLS = GATE_UP ? BN_HALF : 2 * BN_HALF;      // output columns a tile covers in its weight tensor(s)
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_cum[257];
   __shared__ int s_off[257];
@@ -164,8 +165,9 @@ block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
           const uint32_t sw = tiles_base + stage * STAGE_SZ;
           const uint32_t full = bar_full + 8 * stage;
           mbar_expect_tx(full, STAGE_SZ);
-          tma_load_3d(sw, &map_w0, full, ft * BN_HALF, kb * BK, e);
-          if (GATE_UP) tma_load_3d(sw + B_HALF_BYTES, &map_w1, full, ft * BN_HALF, kb * BK, e);
+          tma_load_3d(sw, &map_w0, full, ft * FT_COLS, kb * BK, e);
+          if (GATE_UP) tma_load_3d(sw + B_HALF_BYTES, &map_w1, full, ft * FT_COLS, kb * BK, e);
+          else         tma_load_3d(sw + B_HALF_BYTES, &map_w0, full, ft * FT_COLS + BN_HALF, kb * BK, e);
           tma_load_2d(sw + W_BYTES, &map_x, full, kb * BK, row0);
           if (++stage == NSTAGE) stage = 0, phase ^= 1u;
         }
@@ -190,12 +192,10 @@ block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)       // weights: +32 K rows = 4096 bytes; activations: +32 bytes along K
             mma_f8(d_tmem, da0 + (uint64_t)(k * 256), db + (uint64_t)(k * 2), IDESC_SMALL, k > 0 ? 1u : 0u);
-          if constexpr (GATE_UP) {
-            const uint64_t da1 = desc_nmajor(sw + B_HALF_BYTES);
+          const uint64_t da1 = desc_nmajor(sw + B_HALF_BYTES);
 #pragma unroll
-            for (int k = 0; k < BK / 32; ++k)
-              mma_f8(d_tmem + S_NT, da1 + (uint64_t)(k * 256), db + (uint64_t)(k * 2), IDESC_SMALL, k > 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 32; ++k)
+            mma_f8(d_tmem + S_NT, da1 + (uint64_t)(k * 256), db + (uint64_t)(k * 2), IDESC_SMALL, k > 0 ? 1u : 0u);
           mma_commit(bar_empty + 8 * stage);
           mma_commit(bar_tfull + 8 * buf);
           if (++stage == NSTAGE) stage = 0, phase ^= 1u;
@@ -232,30 +232,31 @@ block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
       // weight scales of the tile: lane kb holds K block kb's
       float w0_reg, w1_reg;
       {
-        const size_t at = ((size_t)e * k_blocks + min(lane, k_blocks - 1)) * p.nb + min(ft, p.nb - 1);
-        w0_reg = p.w0_inv[at];
-        w1_reg = GATE_UP ? p.w1_inv[at] : 0.f;
+        const size_t at = ((size_t)e * k_blocks + min(lane, k_blocks - 1)) * p.nb;
+        if (GATE_UP) {
+          w0_reg = p.w0_inv[at + min(ft, p.nb - 1)];
+          w1_reg = p.w1_inv[at + min(ft, p.nb - 1)];
+        } else {
+          w0_reg = p.w0_inv[at + min(2 * ft, p.nb - 1)];
+          w1_reg = p.w0_inv[at + min(2 * ft + 1, p.nb - 1)];
+        }
       }
       if (!(ok = fold_sync())) break;
-      float acc0[S_NT], acc1[GATE_UP ? S_NT : 1];
+      float acc0[S_NT], acc1[S_NT];
 #pragma unroll
-      for (int c = 0; c < S_NT; ++c) acc0[c] = 0.f;
-      if constexpr (GATE_UP) {
-#pragma unroll
-        for (int c = 0; c < S_NT; ++c) acc1[c] = 0.f;
-      }
+      for (int c = 0; c < S_NT; ++c) acc0[c] = 0.f, acc1[c] = 0.f;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const uint32_t buf = it % S_NBUF, use = it / S_NBUF;
         const float w0 = __shfl_sync(0xffffffffu, w0_reg, kb);
-        const float w1 = GATE_UP ? __shfl_sync(0xffffffffu, w1_reg, kb) : 0.f;
+        const float w1 = __shfl_sync(0xffffffffu, w1_reg, kb);
         ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * S_BUF_COLS;
-        uint32_t r0[32], r1[GATE_UP ? 32 : 1];
+        uint32_t r0[32], r1[32];
         tmem_ld32(t_row, r0);
-        if constexpr (GATE_UP) tmem_ld32(t_row + S_NT, r1);
+        tmem_ld32(t_row + S_NT, r1);
         tmem_ld_wait();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);      // the loads have landed: the buffer may be reused
         const float* xs = s_xinv[par][kb];
@@ -263,11 +264,11 @@ block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         for (int c = 0; c < S_NT; ++c) {
           const float a = xs[c];
           acc0[c] = fmaf(__uint_as_float(r0[c]), a * w0, acc0[c]);
-          if constexpr (GATE_UP) acc1[c] = fmaf(__uint_as_float(r1[c]), a * w1, acc1[c]);
+          acc1[c] = fmaf(__uint_as_float(r1[c]), a * w1, acc1[c]);
         }
       }
       if (!ok) break;
-      const int n0 = ft * BN_HALF;
+      const int n0 = ft * FT_COLS;
       const bool f_ok = n0 + f_in_tile < p.N_out;
       if constexpr (GATE_UP) {
         // h = silu(gate) * up with the recipe's bf16 rounding points; one quantisation group = this tile's
@@ -295,9 +296,14 @@ block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         }
       } else {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+        const bool f1_ok = n0 + BN_HALF + f_in_tile < p.N_out;
 #pragma unroll
         for (int c = 0; c < S_NT; ++c) {
-          if (c < n_valid && f_ok) out[(size_t)(row0 + c) * p.N_out + n0 + f_in_tile] = __float2bfloat16_rn(acc0[c]);
+          if (c < n_valid) {
+            __nv_bfloat16* row = out + (size_t)(row0 + c) * p.N_out + n0 + f_in_tile;
+            if (f_ok) row[0] = __float2bfloat16_rn(acc0[c]);
+            if (f1_ok) row[BN_HALF] = __float2bfloat16_rn(acc1[c]);
+          }
         }
       }
     }
@@ -333,10 +339,10 @@ template <bool GATE_UP>
 int launch_small(const CUtensorMap& mx, const CUtensorMap& mw0, const CUtensorMap& mw1, const SmallParams& p, int M,
                  cudaStream_t st) {
   static unsigned char smem_set[64] = {0};
-  BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_small_kernel<GATE_UP>, SmallShape<GATE_UP>::kSmemBytes, smem_set));
+  BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_small_kernel<GATE_UP>, S_SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, S_NT) + p.E) * p.n_ft;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  block_gemm_small_kernel<GATE_UP><<<grid, S_THREADS, SmallShape<GATE_UP>::kSmemBytes, counted(st)>>>(mx, mw0, mw1, p);
+  block_gemm_small_kernel<GATE_UP><<<grid, S_THREADS, S_SMEM_BYTES, counted(st)>>>(mx, mw0, mw1, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -365,7 +371,7 @@ int launch_down_block_small(const void* hq, const float* h_inv, const int32_t* o
   CUtensorMap mx, mw;
   if (int rc = make_map_x32(&mx, hq, M, H)) return rc;
   if (int rc = make_map_b(&mw, wd, E, H, D)) return rc;
-  SmallParams p{offsets, h_inv, inv_d, nullptr, y, nullptr, status, E, D, ceil_div(D, BN_HALF), ceil_div(H, BK),
+  SmallParams p{offsets, h_inv, inv_d, nullptr, y, nullptr, status, E, D, ceil_div(D, 2 * BN_HALF), ceil_div(H, BK),
                 ceil_div(D, 128)};
   return launch_small<false>(mx, mw, mw, p, M, st);
 }
