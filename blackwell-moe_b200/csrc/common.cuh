@@ -31,6 +31,34 @@ inline cudaStream_t counted(cudaStream_t st) {
   return st;
 }
 
+// Programmatic dependent launch: a kernel launched through launch_chained() may be scheduled while the kernel
+// before it in the stream is still draining (its launch latency and block start-up overlap that tail).
+// Such a kernel executes chain_wait() before it touches global memory: the instruction returns when every
+// kernel it depends on has completed and its writes are visible.  A kernel that calls chain_wait() may
+// also be launched the ordinary way (the instruction then returns at once), but a kernel launched through
+// launch_chained() MUST call it.
+__device__ __forceinline__ void chain_wait() {
+#if defined(__CUDA_ARCH__)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  note_launch();
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int sm_count();

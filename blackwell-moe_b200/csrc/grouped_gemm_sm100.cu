@@ -113,6 +113,7 @@ template <bool GATE_UP, bool RAW, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const GemmParams p) {
+  chain_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_cum[257];
   __shared__ uint32_t s_tmem_base;
@@ -467,6 +468,7 @@ __global__ void __launch_bounds__(256)
 swiglu_from_partials_kernel(const float* __restrict__ partial, int S, int M, int H, const int32_t* __restrict__ offsets,
                             int E, const float* __restrict__ sx, const float* __restrict__ sg,
                             const float* __restrict__ su, __nv_bfloat16* __restrict__ h, float* __restrict__ seg_amax) {
+  chain_wait();
   const int vec_per_row = H / 4;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   bool live = gid < (size_t)M * vec_per_row;
@@ -527,6 +529,7 @@ swiglu_requant_from_partials_kernel(const float* __restrict__ partial, int S, in
                                     uint8_t* __restrict__ hq, float* __restrict__ seg_amax,
                                     float* __restrict__ scale_h, unsigned int* __restrict__ arrivals,
                                     int32_t* __restrict__ status) {
+  chain_wait();
   __shared__ int s_ok;
   const int vec_per_row = H / 4;
   const int n_rows = min(M, offsets[E]);
@@ -622,6 +625,7 @@ __global__ void __launch_bounds__(256)
 down_from_partials_kernel(const float* __restrict__ partial, int S, int M, int D, const int32_t* __restrict__ offsets,
                           int E, const float* __restrict__ sh, const float* __restrict__ sd,
                           __nv_bfloat16* __restrict__ y) {
+  chain_wait();
   const int vec_per_row = D / 4;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)M * vec_per_row) return;
@@ -652,6 +656,7 @@ down_combine_from_partials_kernel(const float* __restrict__ partial, int S, int 
                                   const int32_t* __restrict__ pos, const float* __restrict__ weights, int T, int K,
                                   __nv_bfloat16* __restrict__ out, float scale,
                                   const __nv_bfloat16* __restrict__ residual, int n_tail) {
+  chain_wait();
   const int vec_per_row = D / 4;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)T * vec_per_row) return;
@@ -740,13 +745,15 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap
       cfg.blockDim = dim3(GEMM_THREADS);
       cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
       cfg.stream = st;
-      cudaLaunchAttribute attr[1];
+      cudaLaunchAttribute attr[2];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = 2;
       attr[0].val.clusterDim.y = 1;
       attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // the kernel starts with chain_wait()
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
-      cfg.numAttrs = 1;
+      cfg.numAttrs = 2;
       // pairs that can be resident at once (per device, asked once): the persistent loop needs no more
       static int resident_pairs[64] = {0};
       int dev = 0;
@@ -770,7 +777,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap
   BWMOE_CUDA_OK(ensure_dynamic_smem(grouped_gemm_kernel<GATE_UP, RAW, false>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles * p.split_k;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  grouped_gemm_kernel<GATE_UP, RAW, false><<<grid, GEMM_THREADS, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
+  BWMOE_CUDA_OK(launch_chained(grouped_gemm_kernel<GATE_UP, RAW, false>, dim3(grid), dim3(GEMM_THREADS), SMEM_BYTES, st, ma, mb0, mb1, p));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -815,15 +822,15 @@ int launch_gateup(const void* xq, const int32_t* offsets, const float* sx, const
   // per thread
   const size_t fused_blocks = std::min<size_t>((size_t)sm_count(), (n + 255) / 256);
   if (fr != nullptr && requant_done != nullptr && n <= fused_blocks * 256 * kFusedItems) {
-    swiglu_requant_from_partials_kernel<<<(unsigned)fused_blocks, 256, 0, counted(st)>>>(
+    BWMOE_CUDA_OK(launch_chained(swiglu_requant_from_partials_kernel, dim3((unsigned)fused_blocks), dim3(256), 0, st,
         p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<uint8_t*>(fr->hq), amax_h, fr->scale_h,
-        fr->arrivals, status);
+        fr->arrivals, status));
     BWMOE_CUDA_OK(cudaGetLastError());
     *requant_done = true;
     return BWMOE_OK;
   }
-  swiglu_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
-      p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<__nv_bfloat16*>(h), amax_h);
+  BWMOE_CUDA_OK(launch_chained(swiglu_from_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
+      p.partial, sp.split_k, M, H, offsets, E, sx, sg, su, static_cast<__nv_bfloat16*>(h), amax_h));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -874,17 +881,17 @@ int launch_down(const void* hq, const int32_t* offsets, const float* sh, const v
   if (int rc = launch_gemm<false, true>(ma, mb, mb, p, M, st)) return rc;
   if (combine != nullptr && combine_state != nullptr && combine->T * combine->K == M) {
     const size_t nt = (size_t)combine->T * (D / 4);
-    down_combine_from_partials_kernel<<<(unsigned)((nt + 255) / 256), 256, 0, counted(st)>>>(
+    BWMOE_CUDA_OK(launch_chained(down_combine_from_partials_kernel, dim3((unsigned)((nt + 255) / 256)), dim3(256), 0, st,
         p.partial, sp.split_k, M, D, offsets, E, sh, sd, static_cast<__nv_bfloat16*>(y), combine->pos,
         combine->weights, combine->T, combine->K, static_cast<__nv_bfloat16*>(combine->out), combine->scale,
-        static_cast<const __nv_bfloat16*>(combine->residual), combine->n_tail);
+        static_cast<const __nv_bfloat16*>(combine->residual), combine->n_tail));
     BWMOE_CUDA_OK(cudaGetLastError());
     *combine_state = kCombineDone;
     return BWMOE_OK;
   }
   const size_t n = (size_t)M * (D / 4);
-  down_from_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(p.partial, sp.split_k, M, D, offsets, E, sh,
-                                                                        sd, static_cast<__nv_bfloat16*>(y));
+  BWMOE_CUDA_OK(launch_chained(down_from_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, p.partial, sp.split_k, M, D, offsets, E, sh,
+                                                                        sd, static_cast<__nv_bfloat16*>(y)));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

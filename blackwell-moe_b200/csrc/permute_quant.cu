@@ -137,6 +137,7 @@ plan_small_kernel(const int32_t* __restrict__ indices, const float* __restrict__
                   int32_t* __restrict__ offsets, int32_t* __restrict__ pos, int32_t* __restrict__ row_slot,
                   int32_t* __restrict__ row_expert, float* __restrict__ seg_amax, float* __restrict__ scales_out,
                   int32_t* __restrict__ status) {
+  chain_wait();
   extern __shared__ int cnt[];            // [32 warps][E] per-warp counts -> exclusive prefixes
   __shared__ int start[kMaxE + 1];
   __shared__ unsigned int amax[kMaxE];
@@ -194,6 +195,7 @@ plan_small_kernel(const int32_t* __restrict__ indices, const float* __restrict__
 
 __global__ void segment_scales_kernel(const float* __restrict__ seg_amax, const int32_t* __restrict__ offsets,
                                       int E, float* __restrict__ scales) {
+  chain_wait();
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= E) return;
   const bool empty = offsets != nullptr && offsets[e + 1] <= offsets[e];
@@ -236,6 +238,7 @@ __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot,
                   const int32_t* __restrict__ row_expert, const float* __restrict__ scales,
                   float* __restrict__ scales_out, unsigned M, unsigned W, int K, uint8_t* __restrict__ dst) {
+  chain_wait();
   const unsigned per_row = W / 16;
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= M * per_row) return;
@@ -294,6 +297,7 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restr
                      const int32_t* __restrict__ indices, const float* __restrict__ scales, unsigned T,
                      unsigned W, int K, uint8_t* __restrict__ dst, const float* __restrict__ weights,
                      float* __restrict__ row_w) {
+  chain_wait();
   const unsigned per_row = W / 16;
   const unsigned p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= T * per_row) return;
@@ -436,6 +440,7 @@ __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ pos,
                const float* __restrict__ weights, int T, int D, int K, __nv_bfloat16* __restrict__ out,
                float scale, const __nv_bfloat16* __restrict__ residual, int n_tail) {
+  chain_wait();
   const int vec_per_row = D / 8;
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (size_t)T * vec_per_row) return;
@@ -503,6 +508,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ 
 // slots and gets S more with weight 1.
 __global__ void append_shared_slots_kernel(const int32_t* __restrict__ idx_r, const float* __restrict__ w_r, int T,
                                            int K, int E, int S, int32_t* __restrict__ idx, float* __restrict__ w) {
+  chain_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int KS = K + S;
   if (i >= T * KS) return;
@@ -513,6 +519,7 @@ __global__ void append_shared_slots_kernel(const int32_t* __restrict__ idx_r, co
 
 // amax[first .. first+count) <- their common maximum: groups that are pieces of one tensor share its scale
 __global__ void merge_amax_kernel(float* __restrict__ amax, int first, int count) {
+  chain_wait();
   float m = 0.f;
   for (int i = 0; i < count; ++i) m = fmaxf(m, amax[first + i]);
   for (int i = 0; i < count; ++i) amax[first + i] = m;
@@ -523,13 +530,13 @@ __global__ void merge_amax_kernel(float* __restrict__ amax, int first, int count
 int launch_append_shared_slots(const int32_t* idx_r, const float* w_r, int T, int K, int E, int S, int32_t* idx,
                                float* w, cudaStream_t st) {
   const int n = T * (K + S);
-  append_shared_slots_kernel<<<ceil_div(n, 256), 256, 0, counted(st)>>>(idx_r, w_r, T, K, E, S, idx, w);
+  BWMOE_CUDA_OK(launch_chained(append_shared_slots_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, st, idx_r, w_r, T, K, E, S, idx, w));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
 
 int launch_merge_amax(float* amax, int first, int count, cudaStream_t st) {
-  merge_amax_kernel<<<1, 1, 0, counted(st)>>>(amax, first, count);
+  BWMOE_CUDA_OK(launch_chained(merge_amax_kernel, dim3(1), dim3(1), 0, st, amax, first, count));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -552,8 +559,8 @@ int launch_plan(const int32_t* indices, const float* row_amax, int T, int E, int
                 "plan: null pointer");
   const int M = T * K;
   if (M <= kPlanThreads) {
-    plan_small_kernel<<<1, kPlanThreads, (size_t)32 * E * sizeof(int), counted(st)>>>(
-        indices, row_amax, M, E, K, offsets, pos, row_slot, row_expert, seg_amax, scales_out, status);
+    BWMOE_CUDA_OK(launch_chained(plan_small_kernel, dim3(1), dim3(kPlanThreads), (size_t)32 * E * sizeof(int), st,
+        indices, row_amax, M, E, K, offsets, pos, row_slot, row_expert, seg_amax, scales_out, status));
     BWMOE_CUDA_OK(cudaGetLastError());
     return BWMOE_OK;
   }
@@ -614,7 +621,7 @@ int launch_segment_scales(const float* seg_amax, const int32_t* offsets, int E, 
                           cudaStream_t st) {
   BWMOE_REQUIRE(E > 0, BWMOE_ERR_BAD_SHAPE, "segment_scales: E=%d", E);
   BWMOE_REQUIRE(seg_amax && scales, BWMOE_ERR_NULL, "segment_scales: null pointer");
-  segment_scales_kernel<<<ceil_div(E, 128), 128, 0, counted(st)>>>(seg_amax, offsets, E, scales);
+  BWMOE_CUDA_OK(launch_chained(segment_scales_kernel, dim3(ceil_div(E, 128)), dim3(128), 0, st, seg_amax, offsets, E, scales));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -624,8 +631,8 @@ int launch_gather_quant(const void* x, const int32_t* row_slot, const int32_t* r
   BWMOE_REQUIRE(M > 0 && D > 0 && K > 0 && D % 16 == 0, BWMOE_ERR_BAD_SHAPE, "gather_quant: M=%d D=%d K=%d", M, D, K);
   BWMOE_REQUIRE(x && row_slot && row_expert && scales && xq, BWMOE_ERR_NULL, "gather_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "gather_quant: pointers must be 16-byte aligned");
-  quant_rows_kernel<true, false><<<quant_grid(M, D), 256, 0, counted(st)>>>(
-      static_cast<const __nv_bfloat16*>(x), row_slot, row_expert, scales, nullptr, M, D, K, static_cast<uint8_t*>(xq));
+  BWMOE_CUDA_OK(launch_chained(quant_rows_kernel<true, false>, dim3(quant_grid(M, D)), dim3(256), 0, st,
+      static_cast<const __nv_bfloat16*>(x), row_slot, row_expert, scales, nullptr, M, D, K, static_cast<uint8_t*>(xq)));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -636,8 +643,8 @@ int launch_scatter_quant(const void* x, const int32_t* pos, const int32_t* indic
   BWMOE_REQUIRE(x && pos && indices && scales && xq, BWMOE_ERR_NULL, "scatter_quant: null pointer");
   BWMOE_REQUIRE(aligned16(x) && aligned16(xq), BWMOE_ERR_BAD_ALIGN, "scatter_quant: pointers must be 16-byte aligned");
   BWMOE_REQUIRE(row_w == nullptr || weights != nullptr, BWMOE_ERR_NULL, "scatter_quant: row weights without weights");
-  scatter_quant_kernel<<<quant_grid(T, D), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), pos, indices, scales,
-                                                         T, D, K, static_cast<uint8_t*>(xq), weights, row_w);
+  BWMOE_CUDA_OK(launch_chained(scatter_quant_kernel, dim3(quant_grid(T, D)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), pos, indices, scales,
+                                                         T, D, K, static_cast<uint8_t*>(xq), weights, row_w));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -648,13 +655,13 @@ int launch_requant(const void* h, const int32_t* row_expert, const float* scales
   BWMOE_REQUIRE(h && row_expert && scales_h && hq, BWMOE_ERR_NULL, "requant: null pointer");
   BWMOE_REQUIRE(aligned16(h) && aligned16(hq), BWMOE_ERR_BAD_ALIGN, "requant: pointers must be 16-byte aligned");
   if (scales_from_amax_out != nullptr)   // scales_h holds the segment amax; scales are derived and published
-    quant_rows_kernel<false, true><<<quant_grid(M, H), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
+    BWMOE_CUDA_OK(launch_chained(quant_rows_kernel<false, true>, dim3(quant_grid(M, H)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h), nullptr,
                                                                      row_expert, scales_h, scales_from_amax_out, M, H, 1,
-                                                                     static_cast<uint8_t*>(hq));
+                                                                     static_cast<uint8_t*>(hq)));
   else
-    quant_rows_kernel<false, false><<<quant_grid(M, H), 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(h), nullptr,
+    BWMOE_CUDA_OK(launch_chained(quant_rows_kernel<false, false>, dim3(quant_grid(M, H)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h), nullptr,
                                                                       row_expert, scales_h, nullptr, M, H, 1,
-                                                                      static_cast<uint8_t*>(hq));
+                                                                      static_cast<uint8_t*>(hq)));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -697,9 +704,9 @@ int launch_dense_prepare(const float* row_amax, int T, int32_t* offsets, float* 
 // rows in place (no gather), scale derived from the segment amax and published
 int launch_quant_rows_from_amax(const void* x, const int32_t* row_expert, const float* seg_amax, int M, int W,
                                 void* xq, float* scales_out, cudaStream_t st) {
-  quant_rows_kernel<false, true><<<quant_grid(M, W), 256, 0, counted(st)>>>(
+  BWMOE_CUDA_OK(launch_chained(quant_rows_kernel<false, true>, dim3(quant_grid(M, W)), dim3(256), 0, st,
       static_cast<const __nv_bfloat16*>(x), nullptr, row_expert, seg_amax, scales_out, M, W, 1,
-      static_cast<uint8_t*>(xq));
+      static_cast<uint8_t*>(xq)));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -712,13 +719,13 @@ int launch_combine(const void* y, const int32_t* pos, const float* weights, int 
   BWMOE_REQUIRE(aligned16(y) && aligned16(out), BWMOE_ERR_BAD_ALIGN, "combine: pointers must be 16-byte aligned");
   const size_t n = (size_t)T * (D / 8);
   if (preweighted)
-    combine_kernel<true><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
+    BWMOE_CUDA_OK(launch_chained(combine_kernel<true>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
         static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
-        static_cast<const __nv_bfloat16*>(residual), n_tail);
+        static_cast<const __nv_bfloat16*>(residual), n_tail));
   else
-    combine_kernel<false><<<(unsigned)((n + 255) / 256), 256, 0, counted(st)>>>(
+    BWMOE_CUDA_OK(launch_chained(combine_kernel<false>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
         static_cast<const __nv_bfloat16*>(y), pos, weights, T, D, K, static_cast<__nv_bfloat16*>(out), scale,
-        static_cast<const __nv_bfloat16*>(residual), n_tail);
+        static_cast<const __nv_bfloat16*>(residual), n_tail));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
