@@ -42,6 +42,8 @@ SIGNATURES = {
     "bwmoe_read_status": (_i, [_vp, _vp, C.POINTER(C.c_int32)]),
     "bwmoe_router_scratch_bytes": (_sz, [_i] * 4),
     "bwmoe_router": (_i, [_vp, _vp, _i, _i, _i, _i, _fp, _ip, _fp, _vp, _sz, _vp]),
+    "bwmoe_router_scratch_bytes_as": (_sz, [_i] * 5),
+    "bwmoe_router_as": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _fp, _ip, _fp, _vp, _sz, _vp]),
     "bwmoe_moe_forward": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp]),
     "bwmoe_moe_forward_flags": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [_vp, _vp, _sz, _vp, C.c_uint]),
     "bwmoe_moe_forward_ex": (_i, [_vp] * 5 + [_fp] * 3 + [_i] * 5 + [C.c_float, _vp, _vp, _vp, _sz, _vp]),

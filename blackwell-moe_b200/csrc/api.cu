@@ -409,6 +409,17 @@ int bwmoe_router(const void* x, const void* wg, int T, int D, int E, int K, floa
                        scratch_bytes, nullptr);
 }
 
+size_t bwmoe_router_scratch_bytes_as(int T, int D, int E, int K, int T_as) {
+  if (T <= 0 || D <= 0 || E <= 0 || K <= 0) return 0;
+  return router_scratch_bytes(T, D, E, K, T_as);
+}
+
+int bwmoe_router_as(const void* x, const void* wg, int T, int D, int E, int K, int T_as, float* weights,
+                    int32_t* indices, float* row_amax, void* scratch, size_t scratch_bytes, void* stream) {
+  return launch_router(x, wg, T, D, E, K, weights, indices, row_amax, static_cast<cudaStream_t>(stream), scratch,
+                       scratch_bytes, nullptr, T_as);
+}
+
 int bwmoe_moe_forward(const void* x, const void* w_gate, const void* wg, const void* wu, const void* wd,
                       const float* sg, const float* su, const float* sd, int T, int D, int H, int E, int K,
                       void* out, void* ws, size_t ws_bytes, void* stream) {

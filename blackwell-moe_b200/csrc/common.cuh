@@ -111,10 +111,13 @@ __device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
 
 // ---- launchers implemented in the individual .cu files ---------------------
 // scratch (optional): enables the tensor-core router where it applies; needs router_scratch_bytes()
-size_t router_scratch_bytes(int T, int D, int E, int K);
+// T_as > 0: choose the routing kernel a batch of T_as tokens would get (the kernels agree on the selected
+// experts always, but their fp32 weights differ in the last bits: a rank that routes a slice of a larger batch
+// passes the size of the whole batch to obtain the weights the whole batch would have got).
+size_t router_scratch_bytes(int T, int D, int E, int K, int T_as = 0);
 int launch_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
                   int32_t* indices, float* row_amax, cudaStream_t st, void* scratch = nullptr,
-                  size_t scratch_bytes = 0, int32_t* status = nullptr);
+                  size_t scratch_bytes = 0, int32_t* status = nullptr, int T_as = 0);
 bool router_tc_applicable(int T, int D, int E, int K);
 size_t router_tc_scratch_bytes(int T, int D, int E);
 int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, float* weights, int32_t* indices,

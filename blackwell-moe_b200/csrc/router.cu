@@ -607,18 +607,19 @@ int launch_router_fallback(const void* x, const void* wg, int T, int D, int E, i
   return BWMOE_OK;
 }
 
-size_t router_scratch_bytes(int T, int D, int E, int K) {
-  return router_tc_applicable(T, D, E, K) ? router_tc_scratch_bytes(T, D, E) : 0;
+size_t router_scratch_bytes(int T, int D, int E, int K, int T_as) {
+  return router_tc_applicable(T_as > 0 ? T_as : T, D, E, K) ? router_tc_scratch_bytes(T, D, E) : 0;
 }
 
 int launch_router(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
                   int32_t* indices, float* row_amax, cudaStream_t st, void* scratch, size_t scratch_bytes,
-                  int32_t* status) {
+                  int32_t* status, int T_as) {
+  const int Tc = T_as > 0 ? T_as : T;       // the batch size that picks the kernel (launch sizes follow T)
   BWMOE_REQUIRE(T > 0 && D > 0 && E > 0 && K > 0, BWMOE_ERR_BAD_SHAPE, "router: T=%d D=%d E=%d K=%d", T, D, E, K);
   BWMOE_REQUIRE(E <= 256, BWMOE_ERR_UNSUPPORTED, "router: E=%d > 256", E);
   BWMOE_REQUIRE(K <= E && K <= 32, BWMOE_ERR_UNSUPPORTED, "router: K=%d must be <= min(E,32)", K);
   BWMOE_REQUIRE(x && wg && weights && indices, BWMOE_ERR_NULL, "router: null pointer");
-  if (router_tc_applicable(T, D, E, K) && scratch != nullptr && scratch_bytes >= router_tc_scratch_bytes(T, D, E) &&
+  if (router_tc_applicable(Tc, D, E, K) && scratch != nullptr && scratch_bytes >= router_tc_scratch_bytes(T, D, E) &&
       aligned16(x) && aligned16(wg))
     return launch_router_tc(x, wg, T, D, E, K, weights, indices, row_amax, status, scratch, st);
   int Epad = 8;
@@ -627,10 +628,10 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
   auto wp = static_cast<const __nv_bfloat16*>(wg);
   const bool vec_gate = (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) & 15u) == 0);
   const bool vec_x = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
-  if (vec_gate && vec_x && E <= 16 && T >= 1024) {
+  if (vec_gate && vec_x && E <= 16 && Tc >= 1024) {
     router_warp_kernel<<<ceil_div(T, kWarpTokWarps), kWarpTokWarps * 32, 0, counted(st)>>>(xp, wp, T, D, E, K, weights,
                                                                                  indices, row_amax);
-  } else if (vec_gate && T < 1024 && (long long)T * E * D <= (1ll << 26)) {      // fp64 sums: small batches only
+  } else if (vec_gate && Tc < 1024 && (long long)Tc * E * D <= (1ll << 26)) {    // fp64 sums: small batches only
     // Few tokens: a cluster of up to 8 CTAs per token (as many as keep the grid within the SMs), and enough
     // threads that every (expert octet, 8 consecutive d) pair has a thread of its own where that fits.
     static unsigned char smem_set[64] = {0};
@@ -656,7 +657,7 @@ int launch_router(const void* x, const void* wg, int T, int D, int E, int K, flo
     cfg.numAttrs = 1;
     note_launch();
     BWMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, router_token_kernel, xp, wp, T, D, E, K, weights, indices, row_amax));
-  } else if (T >= 2048) {
+  } else if (Tc >= 2048) {       // both token tilings run the same arithmetic per token
     constexpr int TOK = 16;
     router_kernel<TOK><<<ceil_div(T, TOK), kThreads, 0, counted(st)>>>(xp, wp, T, D, E, K, Epad, weights, indices, row_amax);
   } else {

@@ -30,6 +30,7 @@ constexpr int R_BK = 64;                   // bf16 K elements per stage (128 byt
 constexpr int R_A_BYTES = BM * R_BK * 2;   // 16 KiB
 constexpr int R_BCHUNK_BYTES = R_BK * 128; // 64 K rows x 64 experts x 2 B = 8 KiB
 constexpr int R_STAGE_BYTES = R_A_BYTES + 4 * R_BCHUNK_BYTES;   // 48 KiB (up to 256 experts)
+constexpr int R_MAX_STAGES = 2 * STAGES;   // ring depth when a stage holds one expert chunk only
 constexpr int R_SMEM_BYTES = STAGES * R_STAGE_BYTES + 1024 + 256;
 constexpr float kTcTrust = 6.103515625e-05f;   // 2^-14
 
@@ -61,6 +62,7 @@ struct TcParams {
   float* logits;        // [T, n_mma] fp32
   int32_t* status;
   int T, D, E, n_chunks, n_mma;   // n_chunks = ceil(E/64) weight boxes; n_mma = MMA N (multiple of 16)
+  int split_n;                    // 1: a work item is (row tile, one 64-expert chunk) - few row tiles, many SMs
 };
 
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -85,17 +87,21 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  // With one expert chunk per item a stage is half the size and the ring twice as deep.
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   const uint32_t bars = tiles_base + STAGES * R_STAGE_BYTES;
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES;
-  const uint32_t bar_tfull = bars + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * R_MAX_STAGES;
+  const uint32_t bar_tfull = bars + 16 * R_MAX_STAGES, bar_tempty = bar_tfull + 16;
+  const uint32_t n_stages = p.split_n ? R_MAX_STAGES : STAGES;
+  const uint32_t stage_bytes = p.split_n ? R_A_BYTES + R_BCHUNK_BYTES : R_STAGE_BYTES;
+  const int chunks_per_item = p.split_n ? 1 : p.n_chunks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < R_MAX_STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
@@ -110,27 +116,34 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
-  const int total_tiles = (p.T + BM - 1) / BM;
+  const int total_tiles = ((p.T + BM - 1) / BM) * (p.split_n ? p.n_chunks : 1);      // work items
   const int k_blocks = (p.D + R_BK - 1) / R_BK;
-  const uint32_t stage_tx = R_A_BYTES + p.n_chunks * R_BCHUNK_BYTES;
-  // D=f32, A=B=bf16, A K-major, B MN-major, N=n_mma, M=128
-  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(p.n_mma >> 3) << 17) |
-                         ((uint32_t)(BM >> 4) << 24);
+  const uint32_t stage_tx = R_A_BYTES + chunks_per_item * R_BCHUNK_BYTES;
+  // item -> (row tile, first expert chunk, experts of the item rounded up to the MMA's N granularity)
+  auto item_of = [&](int item, int& tile, int& c0, int& n_cols) {
+    tile = p.split_n ? item / p.n_chunks : item;
+    c0 = p.split_n ? item % p.n_chunks : 0;
+    n_cols = p.split_n ? min(64, p.n_mma - 64 * c0) : p.n_mma;
+  };
+  // D=f32, A=B=bf16, A K-major, B MN-major, M=128; N is set per item
+  const uint32_t idesc0 = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(BM >> 4) << 24);
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < total_tiles; item += gridDim.x) {
+        int tile, c0, n_cols;
+        item_of(item, tile, c0, n_cols);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status))) break;
-          const uint32_t sa = tiles_base + stage * R_STAGE_BYTES;
+          const uint32_t sa = tiles_base + stage * stage_bytes;
           const uint32_t full = bar_full + 8 * stage;
           mbar_expect_tx(full, stage_tx);
           tma_load_2d(sa, &map_x, full, kb * R_BK, tile * BM);
-          for (int c = 0; c < p.n_chunks; ++c)
-            tma_load_2d(sa + R_A_BYTES + c * R_BCHUNK_BYTES, &map_w, full, c * 64, kb * R_BK);
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
+          for (int c = 0; c < chunks_per_item; ++c)
+            tma_load_2d(sa + R_A_BYTES + c * R_BCHUNK_BYTES, &map_w, full, (c0 + c) * 64, kb * R_BK);
+          if (++stage == n_stages) stage = 0, phase ^= 1u;
         }
       }
     }
@@ -139,7 +152,10 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      for (int item = blockIdx.x; ok && item < total_tiles; item += gridDim.x, ++local) {
+        int tile, c0, n_cols;
+        item_of(item, tile, c0, n_cols);
+        const uint32_t idesc = idesc0 | ((uint32_t)(n_cols >> 3) << 17);
         const uint32_t buf = local & 1u, use = local >> 1;
         if (!(ok = mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status))) break;
         tc_fence_after();
@@ -147,13 +163,13 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status))) break;
           tc_fence_after();
-          const uint32_t sa = tiles_base + stage * R_STAGE_BYTES;
+          const uint32_t sa = tiles_base + stage * stage_bytes;
           const uint64_t da = desc_kmajor(sa), db = desc_nmajor_bf16(sa + R_A_BYTES);
 #pragma unroll
           for (int k = 0; k < R_BK / 16; ++k)   // A: +32 bytes per 16 K; B: +16 K rows = 2048 bytes
             mma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 128), idesc, (kb | k) != 0 ? 1u : 0u);
           mma_commit(bar_empty + 8 * stage);
-          if (++stage == STAGES) stage = 0, phase ^= 1u;
+          if (++stage == n_stages) stage = 0, phase ^= 1u;
         }
         if (ok) mma_commit(bar_tfull + 8 * buf);
       }
@@ -164,7 +180,9 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int r_in_tile = quarter * 32 + lane;
     uint32_t local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+    for (int item = blockIdx.x; ok && item < total_tiles; item += gridDim.x, ++local) {
+      int tile, c0, n_cols;
+      item_of(item, tile, c0, n_cols);
       const uint32_t buf = local & 1u, use = local >> 1;
       ok = mbar_wait(bar_tfull + 8 * buf, use & 1u, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
@@ -172,15 +190,15 @@ tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
       const int row = tile * BM + r_in_tile;
-      float* dst = p.logits + (size_t)row * p.n_mma;
-      for (int c = 0; c < p.n_mma; c += 32) {
+      float* dst = p.logits + (size_t)row * p.n_mma + c0 * 64;
+      for (int c = 0; c < n_cols; c += 32) {
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         tmem_ld_wait();
         if (row < p.T) {
 #pragma unroll
           for (int v = 0; v < 8; ++v)
-            if (c + 4 * v < p.n_mma)
+            if (c + 4 * v < n_cols)
               reinterpret_cast<uint4*>(dst + c)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
         }
       }
@@ -438,8 +456,10 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   if (int rc = make_map_bf16(&mw, wg, D, E, 64, R_BK)) return rc;
   static unsigned char smem_set[64] = {0};
   BWMOE_CUDA_OK(ensure_dynamic_smem(tc_logits_kernel, R_SMEM_BYTES, smem_set));
-  TcParams p{logits, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16};
-  const int grid = std::min(sm_count(), ceil_div(T, BM));
+  TcParams p{logits, status, T, D, E, ceil_div(E, 64), ceil_div(E, 16) * 16, 0};
+  // few row tiles: one 64-expert chunk per CTA, so that a small batch is spread over several SMs
+  p.split_n = (p.n_chunks > 1 && ceil_div(T, BM) * p.n_chunks * 2 <= sm_count()) ? 1 : 0;
+  const int grid = std::min(sm_count(), ceil_div(T, BM) * (p.split_n ? p.n_chunks : 1));
   tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, counted(st)>>>(mx, mw, p);
   BWMOE_CUDA_OK(cudaGetLastError());
   auto xb = static_cast<const __nv_bfloat16*>(x);

@@ -426,10 +426,14 @@ class ExpertParallelMoE:
         i32, f32, u8 = torch.int32, torch.float32, torch.uint8
         new = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         weights, indices, row_amax = new(T, K, dtype=f32), new(T, K, dtype=i32), new(T, dtype=f32)
-        need = lib.bwmoe_router_scratch_bytes(T, D, E, K)
+        # routed by the kernel the concatenated batch of all ranks would get on one GPU (equal batches per rank
+        # assumed for the size), so that the routing weights, and with them the output, equal the single-GPU ones
+        t_as = self.world * T
+        need = lib.bwmoe_router_scratch_bytes_as(T, D, E, K, t_as)
         rs = new(need, dtype=u8) if need else None
-        _lib.check(lib.bwmoe_router(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, weights.data_ptr(),
-                                    indices.data_ptr(), row_amax.data_ptr(), rs.data_ptr() if need else None, need, st))
+        _lib.check(lib.bwmoe_router_as(x.data_ptr(), self.w_gate.data_ptr(), T, D, E, K, t_as, weights.data_ptr(),
+                                       indices.data_ptr(), row_amax.data_ptr(), rs.data_ptr() if need else None,
+                                       need, st))
         peers = self._use_peers(T)
         if self.block:
             if peers:

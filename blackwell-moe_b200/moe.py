@@ -56,9 +56,14 @@ def release_workspaces() -> None:
     _workspaces.clear()
 
 
-def top_k_router(hidden: torch.Tensor, gate_w: torch.Tensor, k: int):
+def top_k_router(hidden: torch.Tensor, gate_w: torch.Tensor, k: int, *, as_batch: int = None):
     """Return ``(weights[T,k] fp32, indices[T,k] int32)``: softmax over all
-    experts, top-k, renormalised; equal logits go to the lower expert id."""
+    experts, top-k, renormalised; equal logits go to the lower expert id.
+
+    ``as_batch``: route these tokens with the kernel a batch of that many tokens would get.  The kernels
+    (picked by batch size) always select the same experts, but their fp32 weights may differ in the last
+    bits; a caller that routes a slice of a larger batch passes the size of the whole batch and obtains
+    exactly the weights the whole batch would get in one call."""
     assert hidden.dim() == 2 and gate_w.dim() == 2 and hidden.shape[1] == gate_w.shape[0], \
         (hidden.shape, gate_w.shape)
     assert hidden.dtype == torch.bfloat16 and gate_w.dtype == torch.bfloat16, (hidden.dtype, gate_w.dtype)
@@ -70,10 +75,12 @@ def top_k_router(hidden: torch.Tensor, gate_w: torch.Tensor, k: int):
     with torch.cuda.device(dev):
         w_out = torch.empty((T, k), device=dev, dtype=torch.float32)
         i_out = torch.empty((T, k), device=dev, dtype=torch.int32)
-        need = lib.bwmoe_router_scratch_bytes(T, D, E, k)
+        t_as = int(as_batch) if as_batch else 0
+        need = lib.bwmoe_router_scratch_bytes_as(T, D, E, k, t_as)
         scratch = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
-        _lib.check(lib.bwmoe_router(hidden.data_ptr(), gate_w.data_ptr(), T, D, E, k, w_out.data_ptr(),
-                                    i_out.data_ptr(), None, scratch.data_ptr() if need else None, need, _stream(dev)))
+        _lib.check(lib.bwmoe_router_as(hidden.data_ptr(), gate_w.data_ptr(), T, D, E, k, t_as, w_out.data_ptr(),
+                                       i_out.data_ptr(), None, scratch.data_ptr() if need else None, need,
+                                       _stream(dev)))
     return w_out, i_out
 
 

@@ -127,6 +127,17 @@ size_t bwmoe_router_scratch_bytes(int T, int D, int E, int K);
 int bwmoe_router(const void* d_x, const void* d_w_gate, int T, int D, int E, int K,
                  float* d_weights, int32_t* d_indices, float* d_row_amax,
                  void* d_scratch, size_t scratch_bytes, void* stream);
+/*
+ * The same for T tokens that are a slice of a batch of T_as tokens routed elsewhere (expert parallelism: every
+ * rank routes its own tokens).  The routing kernels - chosen by batch size - select the same experts always,
+ * but their fp32 weights can differ in the last bits; with T_as the slice is routed by the kernel the whole
+ * batch would get, so that its weights equal, bit for bit, those of the whole batch routed in one call.
+ * No counterpart in the reference (single GPU).
+ */
+size_t bwmoe_router_scratch_bytes_as(int T, int D, int E, int K, int T_as);
+int bwmoe_router_as(const void* d_x, const void* d_w_gate, int T, int D, int E, int K, int T_as,
+                    float* d_weights, int32_t* d_indices, float* d_row_amax,
+                    void* d_scratch, size_t scratch_bytes, void* stream);
 
 /*
  * Whole block: router -> permute + segment-amax + E4M3 quant -> grouped gate+up

@@ -120,3 +120,22 @@ def test_wide_hidden_sizes_take_the_simt_router():
     _, idx = _route(x, w, K)
     _, ref = oracle.router_canonical(x, w, K)
     assert torch.equal(idx, ref)
+
+
+def test_a_slice_routed_as_the_whole_batch_gets_the_whole_batch_weights():
+    """The routing kernels are picked by batch size and agree on the experts, not on the last bits of the fp32
+    weights.  A slice routed with as_batch = size of the whole batch must reproduce the whole batch's rows
+    bit for bit (what expert parallelism relies on: every rank routes its own tokens)."""
+    import blackwell_moe_b200 as bw
+    g = torch.Generator().manual_seed(21)
+    for (T, D, E, K, part) in ((4096, 4096, 8, 2, 512), (2048, 2048, 64, 6, 64), (1536, 1024, 16, 4, 96)):
+        x = torch.randn(T, D, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(D, E, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        w_all, i_all = bw.top_k_router(x, w, K)
+        for s0 in (0, T - part):
+            w_s, i_s = bw.top_k_router(x[s0:s0 + part].contiguous(), w, K, as_batch=T)
+            assert torch.equal(i_s, i_all[s0:s0 + part])
+            assert torch.equal(w_s, w_all[s0:s0 + part])
+            w_own, i_own = bw.top_k_router(x[s0:s0 + part].contiguous(), w, K)      # its own kernel: same experts
+            assert torch.equal(i_own, i_all[s0:s0 + part])
+            torch.testing.assert_close(w_own, w_all[s0:s0 + part], rtol=1e-4, atol=1e-6)
