@@ -14,6 +14,7 @@ Rank 0 prints ONE JSON line.  Beside the headline it carries:
                 peak for decode-sized batches
   sweep         (one GPU) every (configuration, T) pair of the benchmark suite: time, roofline fraction
   extra         (N > 1) the E=256 block-scale shape, expert parallel, at T=32768 and T=128 per rank
+  ep_load       (N > 1) rows received per rank in the last step, max over mean: the slowest rank sets the time
   ep_parity     (N > 1) one small expert-parallel step compared bit for bit with the single-GPU forward
   cpu_baseline  the bf16 CPU path on the host cores, same T
 """
@@ -488,6 +489,11 @@ def run_ours(args):
     launches = lib.bwmoe_launch_count() - launches0
     (secs,) = max_over_ranks(secs)
     exchange = None if ep is None else ("peer memory" if getattr(ep, "_peer", None) else "NCCL all-to-all")
+    # rows each rank's experts received in the last step: the slowest rank sets the step time
+    ep_load = None
+    if ep is not None and getattr(ep, "last_counts", None) is not None:
+        per_rank = ep.last_counts.sum(0).view(world, -1).sum(1).float()
+        ep_load = {"rows_per_rank_max_over_mean": round(float(per_rank.max() / per_rank.mean()), 4)}
     tokens_total = T * world * args.steps
     value = tokens_total / secs
 
@@ -711,6 +717,8 @@ def run_ours(args):
         line["sweep"] = sweep
     if extra is not None:
         line["extra"] = extra
+    if ep_load is not None:
+        line["ep_load"] = ep_load
     if ep_parity is not None:
         line["ep_parity"] = {"bit_exact": all(p["bit_exact"] for p in ep_parity), "tokens": sum(p["tokens"] for p in ep_parity),
                              "cases": ep_parity}

@@ -159,6 +159,8 @@ class ExpertParallelMoE:
         return self.way_back != "pull"
 
     _peer = None
+    #: [ranks, experts] row counts of the last peer-memory step (device tensor; None before the first step)
+    last_counts = None
     #: when True, the peer-memory forward records a CUDA event at every phase boundary;
     #: :meth:`phase_times` turns the last step's events into milliseconds
     profile = False
@@ -283,6 +285,7 @@ class ExpertParallelMoE:
         counts = new(G * E, dtype=i32)
         dist.all_gather_into_tensor(counts, (offsets[1:] - offsets[:-1]).contiguous(), group=self.group)
         counts = counts.view(G, E)
+        self.last_counts = counts                    # [G, E] rows rank s sent to expert e (device tensor)
         delta, offsets_l, home_counts, home_first = self._peer_maps(counts, offsets)
         # No host synchronisation: the number of rows this rank receives stays on the device.  The GEMMs take
         # their tiles from the device-side segment offsets, the buffers are sized for the agreed worst case,
@@ -362,6 +365,7 @@ class ExpertParallelMoE:
         gathered = gathered.view(G, 2 * E)
         amax = gathered[:, :E].amax(0).contiguous()
         counts = gathered[:, E:].contiguous().view(i32)                 # [G, E] rows rank s has for expert e
+        self.last_counts = counts
         scale_x = new(E, dtype=f32)
         _lib.check(lib.bwmoe_segment_scales(amax.data_ptr(), None, E, scale_x.data_ptr(), st))
         sx_local = scale_x[rank * el:(rank + 1) * el].contiguous()
