@@ -32,7 +32,8 @@ def test_router_matches_reference_fixtures(golden):
 @pytest.mark.parametrize("T,D,E,K", [(1, 4096, 8, 2), (7, 2048, 64, 6), (300, 2048, 128, 8), (2500, 2048, 256, 8),
                                      (33, 1024, 12, 12), (64, 512, 1, 1), (5000, 4096, 8, 2), (129, 272, 200, 32),
                                      (4096, 2048, 64, 6), (3000, 1024, 128, 8), (1500, 512, 24, 4),
-                                     (1100, 2048, 256, 8), (2048, 1024, 16, 2), (1024, 320, 40, 8)])
+                                     (1100, 2048, 256, 8), (2048, 1024, 16, 2), (1024, 320, 40, 8),
+                                     (50, 100, 16, 4), (3, 36, 8, 3)])
 def test_router_bit_exact_vs_canonical(T, D, E, K):
     g = torch.Generator().manual_seed(T + E)
     x = torch.randn(T, D, generator=g).to(BF16)
