@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kPlanThreads)
 plan_rank_kernel(const int32_t* __restrict__ indices, int M, int E, const int32_t* __restrict__ block_base,
                  const int32_t* __restrict__ offsets, int32_t* __restrict__ pos, int32_t* __restrict__ row_slot,
                  int32_t* __restrict__ row_expert) {
-  extern __shared__ int cnt[];            // [32 warps][E] counts of this round, then exclusive prefixes
+  extern __shared__ int cnt[];            // [32 warps][E] counts of this pass, then exclusive prefixes
   __shared__ int round_base[kMaxE];       // slots of earlier rounds in this block, per expert
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n_rows = offsets[E];          // rows that exist (slots with a valid expert id)
@@ -109,7 +109,7 @@ plan_rank_kernel(const int32_t* __restrict__ indices, int M, int E, const int32_
         cnt[w * E + ee] = run;
         run += c;
       }
-      // total of this round is added to round_base after everyone has read it
+      // total of this pass is added to round_base after everyone has read it
       cnt[32 * E + ee] = run;
     }
     __syncthreads();
