@@ -117,6 +117,7 @@ template <bool GATE_UP>
 __global__ void __launch_bounds__(NUM_THREADS_BLK, 1)
 block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                   const __grid_constant__ CUtensorMap map_b1, const BlockGemmParams p) {
+  chain_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_cum[257];
   __shared__ int s_off[257];              // segment offsets: every role looks tiles up without touching global memory
@@ -533,8 +534,8 @@ int launch_block_gemm(const CUtensorMap& ma, const CUtensorMap& mb0, const CUten
   BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_kernel<GATE_UP>, SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, BM) + p.E) * p.n_tiles;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  block_gemm_kernel<GATE_UP><<<grid, NUM_THREADS_BLK, SMEM_BYTES, counted(st)>>>(ma, mb0, mb1, p);
-  BWMOE_CUDA_OK(cudaGetLastError());
+  BWMOE_CUDA_OK(launch_chained(block_gemm_kernel<GATE_UP>, dim3(grid), dim3(NUM_THREADS_BLK), SMEM_BYTES, st, ma, mb0, mb1,
+                               p));
   return BWMOE_OK;
 }
 
@@ -550,6 +551,7 @@ __global__ void __launch_bounds__(256)
 quant_group_rows_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ row_slot, int M, int W,
                         int K, uint8_t* __restrict__ dst, float* __restrict__ inv_out,
                         const int32_t* __restrict__ pos) {
+  chain_wait();
   const int groups = (W + 127) / 128;
   const unsigned per_block = blockDim.x * kGroupVecs;
   const unsigned chunks_per_row = (groups * 16 + per_block - 1) / per_block;
@@ -647,8 +649,9 @@ int launch_gather_quant_group(const void* x, const int32_t* row_slot, int M, int
   int threads = 32;
   while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
   const unsigned grid = (unsigned)((size_t)M * ceil_div(vecs_per_row, threads * kGroupVecs));
-  quant_group_rows_kernel<false><<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K,
-                                                           static_cast<uint8_t*>(xq), x_inv, nullptr);
+  BWMOE_CUDA_OK(launch_chained(quant_group_rows_kernel<false>, dim3(grid), dim3(threads), 0, st,
+                               static_cast<const __nv_bfloat16*>(x), row_slot, M, D, K, static_cast<uint8_t*>(xq), x_inv,
+                               nullptr));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }
@@ -664,8 +667,8 @@ int launch_quant_scatter_group(const void* x, const int32_t* pos, int T, int D, 
   int threads = 32;
   while (threads < 256 && threads * kGroupVecs < vecs_per_row) threads <<= 1;
   const unsigned grid = (unsigned)((size_t)T * ceil_div(vecs_per_row, threads * kGroupVecs));
-  quant_group_rows_kernel<true><<<grid, threads, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x), nullptr, T, D, K,
-                                                          static_cast<uint8_t*>(xq), x_inv, pos);
+  BWMOE_CUDA_OK(launch_chained(quant_group_rows_kernel<true>, dim3(grid), dim3(threads), 0, st,
+                               static_cast<const __nv_bfloat16*>(x), nullptr, T, D, K, static_cast<uint8_t*>(xq), x_inv, pos));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

@@ -81,6 +81,7 @@ template <bool GATE_UP>
 __global__ void __launch_bounds__(S_THREADS, 1)
 block_gemm_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
                         const __grid_constant__ CUtensorMap map_w1, const SmallParams p) {
+  chain_wait();
   constexpr int NSTAGE = S_STAGES;
   constexpr int STAGE_SZ = S_STAGE_BYTES;
   constexpr int W_BYTES = S_W_BYTES;
@@ -342,8 +343,8 @@ int launch_small(const CUtensorMap& mx, const CUtensorMap& mw0, const CUtensorMa
   BWMOE_CUDA_OK(ensure_dynamic_smem(block_gemm_small_kernel<GATE_UP>, S_SMEM_BYTES, smem_set));
   const long long max_tiles = (long long)(ceil_div(M, S_NT) + p.E) * p.n_ft;
   const int grid = (int)std::min<long long>(gemm_sm_budget(), max_tiles);
-  block_gemm_small_kernel<GATE_UP><<<grid, S_THREADS, S_SMEM_BYTES, counted(st)>>>(mx, mw0, mw1, p);
-  BWMOE_CUDA_OK(cudaGetLastError());
+  BWMOE_CUDA_OK(launch_chained(block_gemm_small_kernel<GATE_UP>, dim3(grid), dim3(S_THREADS), S_SMEM_BYTES, st, mx, mw0,
+                               mw1, p));
   return BWMOE_OK;
 }
 
