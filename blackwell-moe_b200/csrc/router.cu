@@ -583,6 +583,7 @@ __global__ void __launch_bounds__(256)
 router_fallback_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, int D, int E,
                        int K, float* __restrict__ weights, int32_t* __restrict__ indices,
                        const int32_t* __restrict__ list, const int32_t* __restrict__ count) {
+  chain_wait();
   __shared__ float lg[256];
   __shared__ double dsum[256];
   const int n = *count;
@@ -600,9 +601,9 @@ router_fallback_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 int launch_router_fallback(const void* x, const void* wg, int T, int D, int E, int K, float* weights,
                            int32_t* indices, const int32_t* list, const int32_t* count, cudaStream_t st) {
   (void)T;
-  router_fallback_kernel<<<64, 256, 0, counted(st)>>>(static_cast<const __nv_bfloat16*>(x),
+  BWMOE_CUDA_OK(launch_chained(router_fallback_kernel, dim3(64), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x),
                                              static_cast<const __nv_bfloat16*>(wg), D, E, K, weights, indices, list,
-                                             count);
+                                             count));
   BWMOE_CUDA_OK(cudaGetLastError());
   return BWMOE_OK;
 }

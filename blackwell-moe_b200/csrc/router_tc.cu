@@ -38,6 +38,7 @@ constexpr float kTcTrust = 6.103515625e-05f;   // 2^-14
 __global__ void __launch_bounds__(256)
 transpose_gate_kernel(const __nv_bfloat16* __restrict__ wg, int D, int E, __nv_bfloat16* __restrict__ wgt,
                       float* __restrict__ wnorm2) {
+  chain_wait();
   __shared__ __nv_bfloat16 tile[32][33];
   const int d0 = blockIdx.x * 32, e0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8
@@ -84,6 +85,7 @@ __device__ __forceinline__ uint64_t desc_nmajor_bf16(uint32_t saddr) {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_logits_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const TcParams p) {
+  chain_wait();
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -232,6 +234,7 @@ refine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
               int E, int K, float* __restrict__ weights, int32_t* __restrict__ indices,
               float* __restrict__ row_amax, int32_t* __restrict__ fallback_count,
               int32_t* __restrict__ fallback_list) {
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (tok >= T) return;
@@ -447,8 +450,8 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   auto* fb_list = reinterpret_cast<int32_t*>(base + L.fb_list);
   BWMOE_CUDA_OK(cudaMemsetAsync(base, 0, L.wgt, st));        // column norms, fallback counter, private status word
   if (status == nullptr) status = fb_count + 1;
-  transpose_gate_kernel<<<dim3(ceil_div(D, 32), ceil_div(E, 32)), 256, 0, counted(st)>>>(
-      static_cast<const __nv_bfloat16*>(wg), D, E, wgt, wnorm2);
+  BWMOE_CUDA_OK(launch_chained(transpose_gate_kernel, dim3(ceil_div(D, 32), ceil_div(E, 32)), dim3(256), 0, st,
+                               static_cast<const __nv_bfloat16*>(wg), D, E, wgt, wnorm2));
   BWMOE_CUDA_OK(cudaGetLastError());
 
   CUtensorMap mx, mw;
@@ -460,22 +463,22 @@ int launch_router_tc(const void* x, const void* wg, int T, int D, int E, int K, 
   // few row tiles: one 64-expert chunk per CTA, so that a small batch is spread over several SMs
   p.split_n = (p.n_chunks > 1 && ceil_div(T, BM) * p.n_chunks * 2 <= sm_count()) ? 1 : 0;
   const int grid = std::min(sm_count(), ceil_div(T, BM) * (p.split_n ? p.n_chunks : 1));
-  tc_logits_kernel<<<grid, NUM_THREADS, R_SMEM_BYTES, counted(st)>>>(mx, mw, p);
+  BWMOE_CUDA_OK(launch_chained(tc_logits_kernel, dim3(grid), dim3(NUM_THREADS), R_SMEM_BYTES, st, mx, mw, p));
   BWMOE_CUDA_OK(cudaGetLastError());
   auto xb = static_cast<const __nv_bfloat16*>(x);
   const unsigned rgrid = (unsigned)ceil_div(T, 8);
   if (E <= 32)
-    refine_kernel<1><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
-                                            fb_count, fb_list);
+    BWMOE_CUDA_OK(launch_chained(refine_kernel<1>, dim3(rgrid), dim3(256), 0, st, xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list));
   else if (E <= 64)
-    refine_kernel<2><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
-                                            fb_count, fb_list);
+    BWMOE_CUDA_OK(launch_chained(refine_kernel<2>, dim3(rgrid), dim3(256), 0, st, xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list));
   else if (E <= 128)
-    refine_kernel<4><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
-                                            fb_count, fb_list);
+    BWMOE_CUDA_OK(launch_chained(refine_kernel<4>, dim3(rgrid), dim3(256), 0, st, xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list));
   else
-    refine_kernel<8><<<rgrid, 256, 0, counted(st)>>>(xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
-                                            fb_count, fb_list);
+    BWMOE_CUDA_OK(launch_chained(refine_kernel<8>, dim3(rgrid), dim3(256), 0, st, xb, wgt, wnorm2, logits, p.n_mma, T, D, E, K, weights, indices, row_amax,
+                                            fb_count, fb_list));
   BWMOE_CUDA_OK(cudaGetLastError());
   return launch_router_fallback(x, wg, T, D, E, K, weights, indices, fb_list, fb_count, st);
 }
